@@ -1,0 +1,199 @@
+/*
+ * dsa_v32.h - C ABI of the B200 (sm_100a) sparse-MLA attention library.
+ *
+ * The library replaces, for NVIDIA B200, the host launcher layer of the reference lab
+ * opus_attn/dsa_v32 (kaiyang-1/OpFoundry): metadata -> decode kernel -> split-KV reduce.
+ * Every entry point is extern "C", takes plain pointers and sizes, returns an int status
+ * (0 = ok, < 0 = argument error, > 0 = a cudaError_t or a device-side status), never exits
+ * the process and never allocates device memory: the caller owns every buffer, including the
+ * split workspace, exactly as the reference's caller owns `mla_decode_plan`
+ * (common/host.cc:69-88, :151-189).
+ *
+ * Shapes (one shared latent KV head):
+ *   q        bf16 [total_q, H, 576]        576 = 512 latent + 64 rope; element strides given
+ *   kv       bf16 rows of 576 values (1152 bytes), or
+ *            fp8 rows of 656 bytes: 512 e4m3 | 4 x fp32 scale (one per 128 values) | 64 bf16 rope
+ *   indices  int32 [total_q, topk]         token position inside the query's sequence, -1 = padding
+ *   block_table int32 [num_seqs, block_table_stride] or NULL
+ *            NULL : physical row = (query / s_q) * kv_batch_stride_rows + position
+ *            else : physical row = block_table[query / s_q][position / page_block_size]
+ *                                  * page_block_size + position % page_block_size
+ *   out      bf16 [total_q, H, 512]        V = the first 512 values of the same KV row
+ *   lse      fp32 [total_q, H]             natural log; may be NULL
+ * A query whose list holds no valid position yields out = 0 and lse = +inf
+ * (common/host.cc:486-490).  A position that is negative is treated as padding; a position
+ * whose physical row lies outside [0, num_kv_rows) is never dereferenced and is masked too.
+ */
+#ifndef DSA_V32_H
+#define DSA_V32_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DSA_V32_D_QK 576
+#define DSA_V32_D_V 512
+#define DSA_V32_D_ROPE 64
+#define DSA_V32_BF16_ROW_BYTES 1152
+#define DSA_V32_FP8_ROW_BYTES 656
+
+#define DSA_V32_KV_BF16 0
+#define DSA_V32_KV_FP8 1
+
+/* status codes (< 0: rejected before any launch) */
+#define DSA_V32_OK 0
+#define DSA_V32_ERR_NULL (-1)        /* a required pointer is NULL */
+#define DSA_V32_ERR_SHAPE (-2)       /* H, topk, total_q, s_q or a stride is out of range */
+#define DSA_V32_ERR_ALIGN (-3)       /* a pointer or stride breaks the 16-byte rule of the TMA engine */
+#define DSA_V32_ERR_WORKSPACE (-4)   /* workspace missing, too small, or not planned for this shape */
+#define DSA_V32_ERR_DTYPE (-5)       /* kv_dtype does not match the entry point */
+#define DSA_V32_ERR_DRIVER (-6)      /* tensor-map creation failed or the driver entry point is missing */
+#define DSA_V32_ERR_DEVICE_WAIT 1001 /* a bounded device-side wait ran out; results are invalid */
+
+/*
+ * One unit of work for one CTA pair: a contiguous slice [k_begin, k_end) of the top-k list of
+ * one query row and one block of 128 heads.  Same role and size as the reference's
+ * opus_mla_decode_work_info (common/defs.h:64-73).
+ *   partial_slot < 0 : the slice is the whole list; out/lse are written directly.
+ *   partial_slot >= 0: normalised fp32 partial output and its lse go to the workspace slot and are
+ *                      merged by dsa_v32_combine.
+ */
+typedef struct dsa_v32_work_info {
+    int32_t q_row;
+    int32_t partial_slot;
+    int32_t k_begin;
+    int32_t k_end;
+    int32_t head_block;
+    int32_t reduce_row; /* index into the reduce tables, -1 when not split */
+    int32_t _pad[2];
+} dsa_v32_work_info;
+
+/* Problem shape the planner needs (no data pointers). */
+typedef struct dsa_v32_shape {
+    int32_t total_q;   /* number of query rows = batches * s_q */
+    int32_t H;         /* heads handled by this device */
+    int32_t topk;      /* slots per query row */
+    int32_t s_q;       /* query rows per sequence (1 = plain decode, 2 = one MTP token, ...) */
+    int32_t num_sms;   /* 0 = ask the device */
+    int32_t _pad;
+    const int32_t* valid_len_hint; /* optional host array [total_q]: slots >= this are known to be -1 */
+} dsa_v32_shape;
+
+/* What dsa_v32_plan_info reports; all byte counts refer to the caller's workspace. */
+typedef struct dsa_v32_plan_info {
+    int64_t workspace_bytes;
+    int32_t num_lists;    /* CTA pairs = work lists */
+    int32_t num_works;
+    int32_t num_partials; /* partial slots (each H_block x 128 heads x 512 fp32 + lse) */
+    int32_t num_reduce_rows;
+} dsa_v32_plan_info;
+
+/*
+ * Arguments of the attention kernels; the analogue of opus_mla_decode_kargs
+ * (common/defs.h:109-131) with the per-query index list, block table and softmax scale the
+ * reference keeps outside (CSR page table, scale fixed at 1/sqrt(576): common/host.cc:437).
+ */
+typedef struct dsa_v32_attn_args {
+    const void* q;
+    const void* kv;
+    void* out;
+    float* lse;
+    const int32_t* indices;
+    const int32_t* block_table;
+    void* workspace;
+    int64_t workspace_bytes;
+    int64_t num_kv_rows;
+    int64_t kv_batch_stride_rows;
+    int64_t stride_q_row; /* elements */
+    int64_t stride_q_head;
+    int64_t stride_o_row;
+    int64_t stride_o_head;
+    int32_t total_q;
+    int32_t H;
+    int32_t topk;
+    int32_t s_q;
+    int32_t block_table_stride;
+    int32_t page_block_size;
+    int32_t kv_dtype; /* DSA_V32_KV_BF16 or DSA_V32_KV_FP8 */
+    float sm_scale;
+} dsa_v32_attn_args;
+
+/* Library / build identification. */
+int dsa_v32_abi_version(void);
+const char* dsa_v32_error_string(int status);
+
+/*
+ * Sizes the workspace and the work list for a shape.  Host only.  Replaces the sizing half of
+ * mla_decode_plan_create (common/host.cc:151-163).
+ */
+int dsa_v32_plan_info_get(const dsa_v32_shape* shape, dsa_v32_plan_info* info);
+
+/*
+ * Builds the work list and the reduce tables on the host and uploads them into the workspace
+ * on `stream` (cudaStream_t passed as void*).  This is the metadata stage: it replaces
+ * get_mla_metadata_kernel (common/get_mla_metadata.hpp:17-158) and, like it, depends only on
+ * shapes, so it is run once per shape and kept out of timed loops (common/host.cc:266-283).
+ */
+int dsa_v32_plan(const dsa_v32_shape* shape, void* workspace, int64_t workspace_bytes, void* stream);
+
+/*
+ * Host-only form of the planner: serialises the plan header and tables (everything the device
+ * needs except the partial buffers) into host memory.  `blob` may be NULL to query `needed`.
+ * Needs no GPU when shape->num_sms is given; used by CPU tests of the planner.
+ */
+int dsa_v32_plan_host(const dsa_v32_shape* shape, void* blob, int64_t blob_bytes, int64_t* needed);
+
+/* Copies the planned work list back to host memory (tests, debugging). */
+int dsa_v32_plan_read(const void* workspace, int64_t workspace_bytes, dsa_v32_work_info* works_out, int32_t max_works,
+                      int32_t* list_indptr_out, int32_t max_lists_plus1, void* stream);
+
+/*
+ * The attention kernel alone (final rows written directly, split rows as fp32 partials).
+ * Replaces mla_decode_launch for the bf16 traits (common/host.cc:39-65) / the mxfp8 traits
+ * (common/host.cc:32-37).  Prefill is the same kernel with one query row per token and no
+ * splitting; it has no counterpart in dsa_v32 and follows the launch shape of
+ * opus_attn/dsa_v4/common/mla_v4_host.cc:629-631 (one work item per token and head block).
+ */
+int dsa_v32_decode_bf16(const dsa_v32_attn_args* args, void* stream);
+int dsa_v32_decode_fp8(const dsa_v32_attn_args* args, void* stream);
+int dsa_v32_prefill_bf16(const dsa_v32_attn_args* args, void* stream);
+
+/* Merges split partials into out/lse.  Replaces mla_reduce_kernel (common/mla_reduce.hpp:158-184). */
+int dsa_v32_combine(const dsa_v32_attn_args* args, void* stream);
+
+/*
+ * plan (optional) -> attention -> combine on one stream: the drop-in for
+ * mla_decode_launch_pipeline (common/host.cc:114-138).
+ */
+int dsa_v32_decode_pipeline(const dsa_v32_attn_args* args, int run_plan, void* stream);
+
+/*
+ * Reads (and clears) the device status word of the workspace after synchronising `stream`:
+ * 0, or DSA_V32_ERR_DEVICE_WAIT when a bounded wait inside a kernel ran out.
+ */
+int dsa_v32_device_status(const dsa_v32_attn_args* args, void* stream);
+
+/*
+ * Debug entry point for index parity: writes, for every (query row, slot), the physical KV row
+ * the kernel's translation resolves to (-1 for padding or an out-of-range row), using the
+ * same device function as the attention kernel's producer warp.
+ */
+int dsa_v32_debug_rows(const dsa_v32_attn_args* args, int32_t* rows_out, void* stream);
+
+/*
+ * KV-cache write path: quantises [num_rows, 512] fp32 latent values and [num_rows, 64] bf16
+ * rope values (device pointers) into 656-byte fp8 cache rows at the given physical rows
+ * (dst_rows == NULL: row i -> i).  Per 128 values: scale = amax / 448 (1.0 for an all-zero
+ * group), byte = e4m3(x / scale) with round-to-nearest-even and saturation, the codec of
+ * common/defs.h:11-38.  The reference only has a host-side generator (common/host.cc:207-237).
+ */
+int dsa_v32_pack_fp8_rows(const float* latent, const void* rope_bf16, const int64_t* dst_rows, void* kv_rows_out,
+                          int64_t num_rows, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DSA_V32_H */

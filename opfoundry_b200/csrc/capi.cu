@@ -1,0 +1,343 @@
+// extern "C" entry points declared in include/dsa_v32.h: argument checks, tensor-map creation,
+// the plan registry and the launches.  Nothing here allocates device memory.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <vector>
+#include "defs.h"
+#include "plan.h"
+#include "tmap.h"
+
+namespace dsa {
+int smem_bytes_attn(bool fp8);
+cudaError_t launch_attn(bool fp8, int num_lists, const CUtensorMap& tq, const CUtensorMap& tkv, const CUtensorMap& ttail,
+                        const AttnParams& p, cudaStream_t stream);
+cudaError_t launch_combine(const float* o_accum, const float* lse_accum, const int32_t* reduce_indptr,
+                           const int32_t* reduce_slots, const ReduceDst* reduce_dst, int num_reduce_rows, void* out, float* lse,
+                           int64_t stride_o_row, int64_t stride_o_head, int H, cudaStream_t stream);
+cudaError_t launch_debug_rows(const AttnParams& p, int total_q, int32_t* rows_out, cudaStream_t stream);
+cudaError_t launch_pack_fp8(const float* latent, const void* rope, const int64_t* dst_rows, void* out, int64_t num_rows,
+                            cudaStream_t stream);
+
+namespace {
+
+// The host keeps the header of every planned workspace so a launch needs no device read-back.
+// (The reference keeps the same facts in its host-side mla_decode_plan struct.)
+struct Registry {
+    std::mutex mu;
+    struct Entry {
+        const void* ws;
+        WorkspaceHeader hdr;
+    };
+    std::vector<Entry> entries;
+    void put(const void* ws, const WorkspaceHeader& h) {
+        std::lock_guard<std::mutex> g(mu);
+        for (auto& e : entries)
+            if (e.ws == ws) {
+                e.hdr = h;
+                return;
+            }
+        if (entries.size() >= 256) entries.erase(entries.begin());
+        entries.push_back(Entry{ws, h});
+    }
+    bool get(const void* ws, WorkspaceHeader* h) {
+        std::lock_guard<std::mutex> g(mu);
+        for (auto& e : entries)
+            if (e.ws == ws) {
+                *h = e.hdr;
+                return true;
+            }
+        return false;
+    }
+};
+Registry& registry() {
+    static Registry r;
+    return r;
+}
+
+int device_sm_count(int* out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    int n = 0;
+    e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return (int)e;
+    *out = n;
+    return 0;
+}
+
+int resolve_sms(const dsa_v32_shape* shape, int* sms) {
+    if (shape->num_sms > 0) {
+        *sms = shape->num_sms;
+        return 0;
+    }
+    return device_sm_count(sms);
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_args(const dsa_v32_attn_args* a, int want_dtype, WorkspaceHeader* hdr) {
+    if (!a || !a->q || !a->kv || !a->out || !a->indices || !a->workspace) return DSA_V32_ERR_NULL;
+    if (a->kv_dtype != want_dtype) return DSA_V32_ERR_DTYPE;
+    if (a->total_q <= 0 || a->H <= 0 || a->topk <= 0 || a->s_q <= 0 || a->total_q % a->s_q != 0) return DSA_V32_ERR_SHAPE;
+    if (a->num_kv_rows <= 0 || a->num_kv_rows >= (int64_t(1) << 31) - 1) return DSA_V32_ERR_SHAPE;
+    if (a->block_table != nullptr && (a->page_block_size <= 0 || a->block_table_stride <= 0)) return DSA_V32_ERR_SHAPE;
+    if (a->block_table == nullptr && a->kv_batch_stride_rows < 0) return DSA_V32_ERR_SHAPE;
+    if (a->stride_q_head < kDQK || a->stride_q_row < int64_t(a->H - 1) * a->stride_q_head + kDQK) return DSA_V32_ERR_SHAPE;
+    if (a->stride_o_head < kDV || a->stride_o_row < int64_t(a->H - 1) * a->stride_o_head + kDV) return DSA_V32_ERR_SHAPE;
+    if (!(a->sm_scale > 0.0f) || !std::isfinite(a->sm_scale)) return DSA_V32_ERR_SHAPE;
+    // TMA: 16-byte aligned bases and strides; the epilogue stores 16-byte vectors
+    if (!aligned16(a->q) || !aligned16(a->kv) || !aligned16(a->out)) return DSA_V32_ERR_ALIGN;
+    if ((a->stride_q_head % 8) || (a->stride_q_row % 8) || (a->stride_o_head % 8) || (a->stride_o_row % 8)) return DSA_V32_ERR_ALIGN;
+    if (reinterpret_cast<uintptr_t>(a->workspace) & 255u) return DSA_V32_ERR_ALIGN;
+    if (!registry().get(a->workspace, hdr)) return DSA_V32_ERR_WORKSPACE;
+    if (hdr->total_q != a->total_q || hdr->H != a->H || hdr->topk != a->topk || hdr->s_q != a->s_q) return DSA_V32_ERR_WORKSPACE;
+    if (hdr->total_bytes > a->workspace_bytes) return DSA_V32_ERR_WORKSPACE;
+    return DSA_V32_OK;
+}
+
+void fill_params(const dsa_v32_attn_args* a, const WorkspaceHeader& h, AttnParams* p) {
+    uint8_t* ws = reinterpret_cast<uint8_t*>(a->workspace);
+    p->indices = a->indices;
+    p->block_table = a->block_table;
+    p->out = a->out;
+    p->lse = a->lse;
+    p->o_accum = reinterpret_cast<float*>(ws + h.off_o_accum);
+    p->lse_accum = reinterpret_cast<float*>(ws + h.off_lse_accum);
+    p->list_indptr = reinterpret_cast<const int32_t*>(ws + h.off_list_indptr);
+    p->works = reinterpret_cast<const dsa_v32_work_info*>(ws + h.off_works);
+    p->status = reinterpret_cast<int32_t*>(ws + offsetof(WorkspaceHeader, status));
+    p->stride_o_row = a->stride_o_row;
+    p->stride_o_head = a->stride_o_head;
+    p->kv_batch_stride_rows = a->kv_batch_stride_rows;
+    p->num_kv_rows = a->num_kv_rows;
+    p->H = a->H;
+    p->topk = a->topk;
+    p->s_q = a->s_q;
+    p->block_table_stride = a->block_table_stride;
+    p->page_block_size = a->page_block_size > 0 ? a->page_block_size : 1;
+    p->scale_log2 = a->sm_scale * 1.4426950408889634f;
+}
+
+int launch_attention(const dsa_v32_attn_args* a, int want_dtype, cudaStream_t stream) {
+    WorkspaceHeader h;
+    int rc = check_args(a, want_dtype, &h);
+    if (rc) return rc;
+    AttnParams p;
+    fill_params(a, h, &p);
+    CUtensorMap tq, tkv, ttail;
+    {
+        const uint64_t dims[3] = {uint64_t(kDQK), uint64_t(a->H), uint64_t(a->total_q)};
+        const uint64_t str[2] = {uint64_t(a->stride_q_head) * 2, uint64_t(a->stride_q_row) * 2};
+        const uint32_t box[3] = {64, uint32_t(kHeadsPerBlock), 1};
+        if (make_tmap(&tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a->q, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+            return DSA_V32_ERR_DRIVER;
+    }
+    const bool fp8 = want_dtype == DSA_V32_KV_FP8;
+    if (!fp8) {
+        const uint64_t dims[2] = {uint64_t(kDQK), uint64_t(a->num_kv_rows)};
+        const uint64_t str[1] = {uint64_t(DSA_V32_BF16_ROW_BYTES)};
+        const uint32_t box[2] = {64, 1};
+        if (make_tmap(&tkv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a->kv, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+            return DSA_V32_ERR_DRIVER;
+        ttail = tkv;
+    } else {
+        const uint64_t dims[2] = {uint64_t(kFp8RowBytes), uint64_t(a->num_kv_rows)};
+        const uint64_t str[1] = {uint64_t(kFp8RowBytes)};
+        const uint32_t box_a[2] = {256, 1};
+        const uint32_t box_b[2] = {144, 1};
+        if (make_tmap(&tkv, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a->kv, dims, str, box_a, CU_TENSOR_MAP_SWIZZLE_NONE))
+            return DSA_V32_ERR_DRIVER;
+        if (make_tmap(&ttail, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a->kv, dims, str, box_b, CU_TENSOR_MAP_SWIZZLE_NONE))
+            return DSA_V32_ERR_DRIVER;
+    }
+    cudaError_t e = launch_attn(fp8, h.num_lists, tq, tkv, ttail, p, stream);
+    return e == cudaSuccess ? DSA_V32_OK : (int)e;
+}
+
+}  // namespace
+}  // namespace dsa
+
+using namespace dsa;
+
+extern "C" {
+
+int dsa_v32_abi_version(void) { return 1; }
+
+const char* dsa_v32_error_string(int status) {
+    switch (status) {
+        case DSA_V32_OK: return "ok";
+        case DSA_V32_ERR_NULL: return "a required pointer is NULL";
+        case DSA_V32_ERR_SHAPE: return "shape or stride out of range";
+        case DSA_V32_ERR_ALIGN: return "pointer or stride not 16-byte aligned (workspace: 256)";
+        case DSA_V32_ERR_WORKSPACE: return "workspace missing, too small, or not planned for this shape";
+        case DSA_V32_ERR_DTYPE: return "kv_dtype does not match the entry point";
+        case DSA_V32_ERR_DRIVER: return "tensor-map creation failed";
+        case DSA_V32_ERR_DEVICE_WAIT: return "a bounded device-side wait ran out";
+        default: return status > 0 ? cudaGetErrorString((cudaError_t)status) : "unknown status";
+    }
+}
+
+int dsa_v32_plan_info_get(const dsa_v32_shape* shape, dsa_v32_plan_info* info) {
+    if (!shape || !info) return DSA_V32_ERR_NULL;
+    int sms = 0;
+    int rc = resolve_sms(shape, &sms);
+    if (rc) return rc;
+    HostPlan P;
+    rc = build_plan(*shape, sms, P);
+    if (rc) return rc;
+    info->workspace_bytes = P.hdr.total_bytes;
+    info->num_lists = P.hdr.num_lists;
+    info->num_works = P.hdr.num_works;
+    info->num_partials = P.hdr.num_partials;
+    info->num_reduce_rows = P.hdr.num_reduce_rows;
+    return DSA_V32_OK;
+}
+
+// Host-only variant used by the CPU tests: serialises header + tables into host memory.
+int dsa_v32_plan_host(const dsa_v32_shape* shape, void* blob, int64_t blob_bytes, int64_t* needed) {
+    if (!shape) return DSA_V32_ERR_NULL;
+    int sms = 0;
+    int rc = resolve_sms(shape, &sms);
+    if (rc) return rc;
+    HostPlan P;
+    rc = build_plan(*shape, sms, P);
+    if (rc) return rc;
+    if (needed) *needed = plan_meta_bytes(P);
+    if (!blob) return DSA_V32_OK;
+    if (blob_bytes < plan_meta_bytes(P)) return DSA_V32_ERR_WORKSPACE;
+    serialize_plan(P, reinterpret_cast<uint8_t*>(blob));
+    return DSA_V32_OK;
+}
+
+int dsa_v32_plan(const dsa_v32_shape* shape, void* workspace, int64_t workspace_bytes, void* stream) {
+    if (!shape || !workspace) return DSA_V32_ERR_NULL;
+    if (reinterpret_cast<uintptr_t>(workspace) & 255u) return DSA_V32_ERR_ALIGN;
+    int sms = 0;
+    int rc = resolve_sms(shape, &sms);
+    if (rc) return rc;
+    HostPlan P;
+    rc = build_plan(*shape, sms, P);
+    if (rc) return rc;
+    if (workspace_bytes < P.hdr.total_bytes) return DSA_V32_ERR_WORKSPACE;
+    std::vector<uint8_t> blob((size_t)plan_meta_bytes(P));
+    serialize_plan(P, blob.data());
+    // pageable source: the runtime stages the bytes before returning, so `blob` may go away
+    cudaError_t e = cudaMemcpyAsync(workspace, blob.data(), blob.size(), cudaMemcpyHostToDevice, (cudaStream_t)stream);
+    if (e != cudaSuccess) return (int)e;
+    registry().put(workspace, P.hdr);
+    return DSA_V32_OK;
+}
+
+int dsa_v32_plan_read(const void* workspace, int64_t workspace_bytes, dsa_v32_work_info* works_out, int32_t max_works,
+                      int32_t* list_indptr_out, int32_t max_lists_plus1, void* stream) {
+    if (!workspace) return DSA_V32_ERR_NULL;
+    WorkspaceHeader h;
+    if (!registry().get(workspace, &h)) return DSA_V32_ERR_WORKSPACE;
+    if (h.total_bytes > workspace_bytes) return DSA_V32_ERR_WORKSPACE;
+    const uint8_t* ws = reinterpret_cast<const uint8_t*>(workspace);
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e = cudaSuccess;
+    if (works_out) {
+        if (max_works < h.num_works) return DSA_V32_ERR_SHAPE;
+        e = cudaMemcpyAsync(works_out, ws + h.off_works, size_t(h.num_works) * sizeof(dsa_v32_work_info), cudaMemcpyDeviceToHost, st);
+        if (e != cudaSuccess) return (int)e;
+    }
+    if (list_indptr_out) {
+        if (max_lists_plus1 < h.num_lists + 1) return DSA_V32_ERR_SHAPE;
+        e = cudaMemcpyAsync(list_indptr_out, ws + h.off_list_indptr, size_t(h.num_lists + 1) * 4, cudaMemcpyDeviceToHost, st);
+        if (e != cudaSuccess) return (int)e;
+    }
+    e = cudaStreamSynchronize(st);
+    return e == cudaSuccess ? DSA_V32_OK : (int)e;
+}
+
+int dsa_v32_decode_bf16(const dsa_v32_attn_args* args, void* stream) {
+    return launch_attention(args, DSA_V32_KV_BF16, (cudaStream_t)stream);
+}
+int dsa_v32_decode_fp8(const dsa_v32_attn_args* args, void* stream) {
+    return launch_attention(args, DSA_V32_KV_FP8, (cudaStream_t)stream);
+}
+int dsa_v32_prefill_bf16(const dsa_v32_attn_args* args, void* stream) {
+    return launch_attention(args, DSA_V32_KV_BF16, (cudaStream_t)stream);
+}
+
+int dsa_v32_combine(const dsa_v32_attn_args* a, void* stream) {
+    WorkspaceHeader h;
+    if (!a) return DSA_V32_ERR_NULL;
+    int rc = check_args(a, a->kv_dtype, &h);
+    if (rc) return rc;
+    uint8_t* ws = reinterpret_cast<uint8_t*>(a->workspace);
+    cudaError_t e = launch_combine(reinterpret_cast<const float*>(ws + h.off_o_accum),
+                                   reinterpret_cast<const float*>(ws + h.off_lse_accum),
+                                   reinterpret_cast<const int32_t*>(ws + h.off_reduce_indptr),
+                                   reinterpret_cast<const int32_t*>(ws + h.off_reduce_slots),
+                                   reinterpret_cast<const ReduceDst*>(ws + h.off_reduce_dst), h.num_reduce_rows, a->out, a->lse,
+                                   a->stride_o_row, a->stride_o_head, a->H, (cudaStream_t)stream);
+    return e == cudaSuccess ? DSA_V32_OK : (int)e;
+}
+
+int dsa_v32_decode_pipeline(const dsa_v32_attn_args* a, int run_plan, void* stream) {
+    if (!a) return DSA_V32_ERR_NULL;
+    if (run_plan) {
+        dsa_v32_shape sh;
+        std::memset(&sh, 0, sizeof(sh));
+        sh.total_q = a->total_q;
+        sh.H = a->H;
+        sh.topk = a->topk;
+        sh.s_q = a->s_q;
+        int rc = dsa_v32_plan(&sh, a->workspace, a->workspace_bytes, stream);
+        if (rc) return rc;
+    }
+    int rc = launch_attention(a, a->kv_dtype, (cudaStream_t)stream);
+    if (rc) return rc;
+    return dsa_v32_combine(a, stream);
+}
+
+int dsa_v32_device_status(const dsa_v32_attn_args* a, void* stream) {
+    if (!a || !a->workspace) return DSA_V32_ERR_NULL;
+    cudaStream_t st = (cudaStream_t)stream;
+    int32_t* dev = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(a->workspace) + offsetof(WorkspaceHeader, status));
+    int32_t v = 0;
+    cudaError_t e = cudaMemcpyAsync(&v, dev, 4, cudaMemcpyDeviceToHost, st);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return (int)e;
+    if (v != 0) {
+        e = cudaMemsetAsync(dev, 0, 4, st);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return v;
+}
+
+int dsa_v32_debug_rows(const dsa_v32_attn_args* a, int32_t* rows_out, void* stream) {
+    if (!a || !rows_out || !a->indices) return DSA_V32_ERR_NULL;
+    if (a->total_q <= 0 || a->topk <= 0 || a->s_q <= 0) return DSA_V32_ERR_SHAPE;
+    AttnParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.indices = a->indices;
+    p.block_table = a->block_table;
+    p.kv_batch_stride_rows = a->kv_batch_stride_rows;
+    p.num_kv_rows = a->num_kv_rows;
+    p.topk = a->topk;
+    p.s_q = a->s_q;
+    p.block_table_stride = a->block_table_stride;
+    p.page_block_size = a->page_block_size > 0 ? a->page_block_size : 1;
+    cudaError_t e = launch_debug_rows(p, a->total_q, rows_out, (cudaStream_t)stream);
+    return e == cudaSuccess ? DSA_V32_OK : (int)e;
+}
+
+int dsa_v32_pack_fp8_rows(const float* latent, const void* rope_bf16, const int64_t* dst_rows, void* kv_rows_out,
+                          int64_t num_rows, void* stream) {
+    if (!latent || !rope_bf16 || !kv_rows_out) return DSA_V32_ERR_NULL;
+    if (num_rows < 0) return DSA_V32_ERR_SHAPE;
+    if (!aligned16(latent) || (reinterpret_cast<uintptr_t>(rope_bf16) & 3u) || (reinterpret_cast<uintptr_t>(kv_rows_out) & 3u))
+        return DSA_V32_ERR_ALIGN;
+    cudaError_t e = launch_pack_fp8(latent, rope_bf16, dst_rows, kv_rows_out, num_rows, (cudaStream_t)stream);
+    return e == cudaSuccess ? DSA_V32_OK : (int)e;
+}
+
+}  // extern "C"

@@ -1,0 +1,55 @@
+// Internal definitions shared by the host launcher, the planner and the kernels.
+#pragma once
+#include <cstdint>
+#include "../../include/dsa_v32.h"
+
+namespace dsa {
+
+constexpr int kDQK = DSA_V32_D_QK;      // 576
+constexpr int kDV = DSA_V32_D_V;        // 512
+constexpr int kDRope = DSA_V32_D_ROPE;  // 64
+constexpr int kHeadsPerBlock = 128;     // MMA M: one head per TMEM lane
+constexpr int kDvHalf = 256;            // output columns accumulated by one CTA of a pair
+constexpr int kTileRows = 32;           // top-k slots per pipeline step
+constexpr int kFp8RowBytes = DSA_V32_FP8_ROW_BYTES;
+
+constexpr uint32_t kWorkspaceMagic = 0x44534133u;  // "DSA3"
+
+// First 256 bytes of the caller's workspace (device memory); everything else is addressed by
+// the byte offsets stored here.
+struct WorkspaceHeader {
+    uint32_t magic;
+    int32_t total_q, H, topk, s_q;
+    int32_t num_lists, num_works, num_partials, num_reduce_rows, num_head_blocks;
+    int32_t status;  // device status word, 0 = ok
+    int32_t _pad0;
+    int64_t off_list_indptr, off_works, off_reduce_indptr, off_reduce_slots, off_reduce_dst;
+    int64_t off_o_accum, off_lse_accum, total_bytes;
+};
+static_assert(sizeof(WorkspaceHeader) <= 256, "header must fit its slot");
+
+// Where a merged row goes: query row and head block of a split unit.
+struct ReduceDst {
+    int32_t q_row;
+    int32_t head_block;
+};
+
+// Kernel parameters (passed by value next to the tensor maps).
+struct AttnParams {
+    const int32_t* indices;
+    const int32_t* block_table;
+    void* out;     // bf16
+    float* lse;
+    float* o_accum;    // [num_partials][128][512] fp32, normalised partial outputs
+    float* lse_accum;  // [num_partials][128]      fp32, natural-log lse or -FLT_MAX when empty
+    const int32_t* list_indptr;
+    const dsa_v32_work_info* works;
+    int32_t* status;
+    int64_t stride_o_row, stride_o_head;
+    int64_t kv_batch_stride_rows;
+    int64_t num_kv_rows;
+    int32_t H, topk, s_q, block_table_stride, page_block_size;
+    float scale_log2;  // sm_scale * log2(e)
+};
+
+}  // namespace dsa

@@ -1,0 +1,176 @@
+// Host-side work planner: the metadata stage of the pipeline.
+//
+// Same job as the reference's get_mla_metadata_kernel (opus_attn/dsa_v32/common/
+// get_mla_metadata.hpp:17-158): cut the KV work of every query into contiguous pieces so that
+// all processors finish together, give every piece of a split unit a partial slot, and emit
+// the tables the merge kernel walks.  The unit of cost here is one pipeline step of
+// kTileRows top-k slots plus a fixed per-piece overhead (query load + epilogue), mirroring the
+// reference's "kv blocks + fixed_overhead" cost (get_mla_metadata.hpp:27-37).  A work list
+// belongs to one CTA pair (the two CTAs of a pair each accumulate one 256-column half of the
+// output), so there are num_sms / 2 lists instead of the reference's 256 compute units.
+//
+// The plan depends only on shapes (and the optional per-query valid-length hint), never on the
+// index values, so it is computed on the host and uploaded once per shape.
+#pragma once
+#include <algorithm>
+#include <cstring>
+#include <vector>
+#include "defs.h"
+
+namespace dsa {
+
+constexpr int kPieceOverheadTiles = 6;  // cost of loading Q and writing the result, in tile steps
+constexpr int kMinPieceTiles = 4;       // never cut a piece shorter than this
+
+struct HostPlan {
+    WorkspaceHeader hdr;
+    std::vector<int32_t> list_indptr;
+    std::vector<dsa_v32_work_info> works;
+    std::vector<int32_t> reduce_indptr;
+    std::vector<int32_t> reduce_slots;
+    std::vector<ReduceDst> reduce_dst;
+};
+
+inline int64_t align256(int64_t x) { return (x + 255) & ~int64_t(255); }
+
+inline int build_plan(const dsa_v32_shape& sh, int num_sms, HostPlan& P) {
+    if (sh.total_q <= 0 || sh.H <= 0 || sh.topk <= 0 || sh.s_q <= 0) return DSA_V32_ERR_SHAPE;
+    if (sh.total_q % sh.s_q != 0) return DSA_V32_ERR_SHAPE;
+    if (num_sms < 2) return DSA_V32_ERR_SHAPE;
+    const int L = num_sms / 2;
+    const int n_hb = (sh.H + kHeadsPerBlock - 1) / kHeadsPerBlock;
+    const int64_t n_units = int64_t(sh.total_q) * n_hb;
+
+    auto unit_len = [&](int64_t u) -> int {
+        const int q = int(u / n_hb);
+        int len = sh.topk;
+        if (sh.valid_len_hint) len = std::max(0, std::min(sh.topk, sh.valid_len_hint[q]));
+        return len;
+    };
+    auto unit_tiles = [&](int64_t u) -> int { return std::max(1, (unit_len(u) + kTileRows - 1) / kTileRows); };
+
+    int64_t total_cost = 0;
+    for (int64_t u = 0; u < n_units; ++u) total_cost += unit_tiles(u) + kPieceOverheadTiles;
+    const int64_t payload = (total_cost + L - 1) / L + kPieceOverheadTiles;
+
+    P.list_indptr.assign(L + 1, 0);
+    P.works.clear();
+    P.reduce_indptr.assign(1, 0);
+    P.reduce_slots.clear();
+    P.reduce_dst.clear();
+
+    int64_t u = 0;
+    int cur_tile = 0;       // tiles of unit u already handed out
+    int pieces_of_unit = 0; // pieces of unit u emitted so far
+    int next_slot = 0;
+    std::vector<int> open_piece_ids;  // work indices of the pieces of the unit being split
+
+    auto emit = [&](int tile_begin, int tile_end, bool last_piece) {
+        const int q = int(u / n_hb), hb = int(u % n_hb);
+        const int len = std::max(unit_len(u), 1);
+        dsa_v32_work_info w;
+        std::memset(&w, 0, sizeof(w));
+        w.q_row = q;
+        w.head_block = hb;
+        w.k_begin = tile_begin * kTileRows;
+        w.k_end = last_piece ? std::min(std::max(len, w.k_begin + 1), sh.topk) : tile_end * kTileRows;
+        w.partial_slot = -1;
+        w.reduce_row = -1;
+        open_piece_ids.push_back(int(P.works.size()));
+        P.works.push_back(w);
+        ++pieces_of_unit;
+        if (last_piece) {
+            if (pieces_of_unit > 1) {
+                const int rr = int(P.reduce_dst.size());
+                for (int id : open_piece_ids) {
+                    P.works[id].partial_slot = next_slot;
+                    P.works[id].reduce_row = rr;
+                    P.reduce_slots.push_back(next_slot++);
+                }
+                P.reduce_indptr.push_back(int(P.reduce_slots.size()));
+                P.reduce_dst.push_back(ReduceDst{q, hb});
+            }
+            open_piece_ids.clear();
+            pieces_of_unit = 0;
+            cur_tile = 0;
+            ++u;
+        } else {
+            cur_tile = tile_end;
+        }
+    };
+
+    for (int list = 0; list < L; ++list) {
+        int64_t remain = payload;
+        const bool last_list = (list == L - 1);
+        while (u < n_units) {
+            const int tiles = unit_tiles(u);
+            const int rem_tiles = tiles - cur_tile;
+            if (last_list || remain >= rem_tiles + kPieceOverheadTiles) {
+                emit(cur_tile, tiles, true);
+                remain -= rem_tiles + kPieceOverheadTiles;
+            } else {
+                // cut the unit here, keeping both sides at least kMinPieceTiles long
+                int take = std::min(int(remain) - kPieceOverheadTiles, rem_tiles - kMinPieceTiles);
+                if (take >= kMinPieceTiles) {
+                    emit(cur_tile, cur_tile + take, false);
+                    break;
+                }
+                // too short to cut: take it whole if at least half of it fits, else leave it
+                if (2 * remain >= rem_tiles + kPieceOverheadTiles) {
+                    emit(cur_tile, tiles, true);
+                    remain -= rem_tiles + kPieceOverheadTiles;
+                    continue;
+                }
+                break;
+            }
+        }
+        P.list_indptr[list + 1] = int(P.works.size());
+    }
+
+    WorkspaceHeader& h = P.hdr;
+    std::memset(&h, 0, sizeof(h));
+    h.magic = kWorkspaceMagic;
+    h.total_q = sh.total_q;
+    h.H = sh.H;
+    h.topk = sh.topk;
+    h.s_q = sh.s_q;
+    h.num_lists = L;
+    h.num_works = int(P.works.size());
+    h.num_partials = next_slot;
+    h.num_reduce_rows = int(P.reduce_dst.size());
+    h.num_head_blocks = n_hb;
+    int64_t off = 256;
+    h.off_list_indptr = off;
+    off = align256(off + int64_t(L + 1) * 4);
+    h.off_works = off;
+    off = align256(off + int64_t(P.works.size()) * sizeof(dsa_v32_work_info));
+    h.off_reduce_indptr = off;
+    off = align256(off + int64_t(P.reduce_indptr.size()) * 4);
+    h.off_reduce_slots = off;
+    off = align256(off + int64_t(std::max<size_t>(P.reduce_slots.size(), 1)) * 4);
+    h.off_reduce_dst = off;
+    off = align256(off + int64_t(std::max<size_t>(P.reduce_dst.size(), 1)) * sizeof(ReduceDst));
+    h.off_o_accum = off;
+    off = align256(off + int64_t(next_slot) * kHeadsPerBlock * kDV * 4);
+    h.off_lse_accum = off;
+    off = align256(off + int64_t(next_slot) * kHeadsPerBlock * 4);
+    h.total_bytes = off;
+    return DSA_V32_OK;
+}
+
+// Serialises header + tables (everything before the partial buffers) into `blob`.
+inline int64_t plan_meta_bytes(const HostPlan& P) { return P.hdr.off_o_accum; }
+
+inline void serialize_plan(const HostPlan& P, uint8_t* blob) {
+    std::memset(blob, 0, size_t(plan_meta_bytes(P)));
+    std::memcpy(blob, &P.hdr, sizeof(P.hdr));
+    std::memcpy(blob + P.hdr.off_list_indptr, P.list_indptr.data(), P.list_indptr.size() * 4);
+    std::memcpy(blob + P.hdr.off_works, P.works.data(), P.works.size() * sizeof(dsa_v32_work_info));
+    std::memcpy(blob + P.hdr.off_reduce_indptr, P.reduce_indptr.data(), P.reduce_indptr.size() * 4);
+    if (!P.reduce_slots.empty())
+        std::memcpy(blob + P.hdr.off_reduce_slots, P.reduce_slots.data(), P.reduce_slots.size() * 4);
+    if (!P.reduce_dst.empty())
+        std::memcpy(blob + P.hdr.off_reduce_dst, P.reduce_dst.data(), P.reduce_dst.size() * sizeof(ReduceDst));
+}
+
+}  // namespace dsa

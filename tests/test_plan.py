@@ -1,0 +1,96 @@
+"""Planner (metadata stage) invariants, checked on the host through dsa_v32_plan_host: every slot of
+every (query row, head block) is covered exactly once, split units own distinct partial slots that
+the reduce tables list, and the work is balanced across the CTA pairs."""
+import ctypes as C
+import struct
+
+import numpy as np
+import pytest
+
+from opfoundry_b200 import api
+
+HDR = struct.Struct("<I" + "i" * 11 + "q" * 8)
+TILE = 32
+
+
+def parse(blob):
+    f = HDR.unpack_from(blob, 0)
+    h = dict(zip(["magic", "total_q", "H", "topk", "s_q", "num_lists", "num_works", "num_partials", "num_reduce_rows",
+                  "num_head_blocks", "status", "_pad", "off_list_indptr", "off_works", "off_reduce_indptr",
+                  "off_reduce_slots", "off_reduce_dst", "off_o_accum", "off_lse_accum", "total_bytes"], f))
+    indptr = np.frombuffer(blob, np.int32, h["num_lists"] + 1, h["off_list_indptr"])
+    works = np.frombuffer(blob, np.int32, h["num_works"] * 8, h["off_works"]).reshape(-1, 8)
+    r_indptr = np.frombuffer(blob, np.int32, h["num_reduce_rows"] + 1, h["off_reduce_indptr"])
+    r_slots = np.frombuffer(blob, np.int32, int(r_indptr[-1]), h["off_reduce_slots"])
+    r_dst = np.frombuffer(blob, np.int32, h["num_reduce_rows"] * 2, h["off_reduce_dst"]).reshape(-1, 2)
+    return h, indptr, works, r_indptr, r_slots, r_dst
+
+
+def check_plan(total_q, H, topk, s_q=1, num_sms=148, hint=None):
+    built = pytest.importorskip("opfoundry_b200.build")
+    built.build()
+    blob = api.plan_host(total_q, H, topk, s_q, num_sms=num_sms, valid_len_hint=hint)
+    h, indptr, works, r_indptr, r_slots, r_dst = parse(blob)
+    assert h["magic"] == 0x44534133 and h["num_lists"] == num_sms // 2
+    assert indptr[0] == 0 and indptr[-1] == h["num_works"] and np.all(np.diff(indptr) >= 0)
+    n_hb = (H + 127) // 128
+    cover = {}
+    for w in works:
+        q, slot, kb, ke, hb, rr = (int(x) for x in w[:6])
+        assert 0 <= q < total_q and 0 <= hb < n_hb and 0 <= kb < ke <= topk
+        assert kb % TILE == 0
+        cover.setdefault((q, hb), []).append((kb, ke, slot, rr))
+    assert len(cover) == total_q * n_hb
+    seen_slots = set()
+    for (q, hb), pieces in cover.items():
+        pieces.sort()
+        want_len = topk if hint is None else max(1, min(topk, int(hint[q])))
+        assert pieces[0][0] == 0 and pieces[-1][1] == want_len
+        for a, b in zip(pieces, pieces[1:]):
+            assert a[1] == b[0]
+        if len(pieces) == 1:
+            assert pieces[0][2] == -1 and pieces[0][3] == -1
+        else:
+            rr = pieces[0][3]
+            assert all(p[3] == rr for p in pieces) and tuple(r_dst[rr]) == (q, hb)
+            slots = [p[2] for p in pieces]
+            assert all(s >= 0 for s in slots) and not (set(slots) & seen_slots)
+            seen_slots |= set(slots)
+            assert sorted(r_slots[r_indptr[rr]:r_indptr[rr + 1]].tolist()) == sorted(slots)
+    assert len(seen_slots) == h["num_partials"]
+    assert h["total_bytes"] >= h["off_lse_accum"] + h["num_partials"] * 128 * 4
+    # balance: cost of a list in tile steps
+    cost = [sum((int(w[3]) - int(w[2]) + TILE - 1) // TILE for w in works[indptr[i]:indptr[i + 1]])
+            for i in range(h["num_lists"])]
+    return h, cost
+
+
+def test_decode_config2_shape():
+    h, cost = check_plan(64, 128, 2048)
+    assert max(cost) <= 1.25 * (sum(cost) / len(cost)) + 8
+    assert min(cost) > 0
+
+
+def test_decode_small_batches_and_heads():
+    for (tq, H, topk, sq) in [(1, 16, 2048, 1), (2, 16, 2048, 1), (4, 128, 100, 1), (256, 128, 2048, 2), (3, 200, 65, 1),
+                              (7, 128, 1, 1), (148, 128, 33, 1), (1, 128, 31, 1)]:
+        check_plan(tq, H, topk, sq)
+
+
+def test_prefill_with_valid_len_hint():
+    T, topk = 600, 256
+    hint = np.minimum(np.arange(T) + 1, topk).astype(np.int32)
+    h, cost = check_plan(T, 128, topk, s_q=T, hint=hint)
+    assert max(cost) <= 1.3 * (sum(cost) / len(cost)) + 8
+
+
+def test_other_sm_counts():
+    for sms in (2, 8, 132, 160):
+        check_plan(16, 128, 512, num_sms=sms)
+
+
+def test_bad_shapes_rejected():
+    for args in [(0, 128, 64, 1), (4, 0, 64, 1), (4, 128, 0, 1), (5, 128, 64, 2)]:
+        with pytest.raises(api.DsaError) as e:
+            api.plan_host(*args)
+        assert e.value.status == -2

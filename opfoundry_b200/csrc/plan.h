@@ -51,7 +51,9 @@ inline int build_plan(const dsa_v32_shape& sh, int num_sms, HostPlan& P) {
 
     int64_t total_cost = 0;
     for (int64_t u = 0; u < n_units; ++u) total_cost += unit_tiles(u) + kPieceOverheadTiles;
-    const int64_t payload = (total_cost + L - 1) / L + kPieceOverheadTiles;
+    // a list always has room for at least one minimum-length piece, so small batches still spread
+    const int64_t payload =
+        std::max<int64_t>((total_cost + L - 1) / L, kMinPieceTiles) + kPieceOverheadTiles;
 
     P.list_indptr.assign(L + 1, 0);
     P.works.clear();

@@ -20,10 +20,13 @@
 //   * warps 0-3 (softmax): one thread per head row; tcgen05.ld of S, log2-domain online softmax
 //     with lazy rescaling (the reference's threshold of 8: ..16mx4_64nx1_template.hpp:700-725),
 //     P -> bf16 -> tcgen05.st, epilogue O / l -> bf16 (or fp32 partial + lse for split items);
-//   * fp8 cache rows add warps 6-9 (dequantise): raw 656-byte rows are gathered unswizzled,
-//     converted e4m3 -> fp32, multiplied by the row's per-128 fp32 scale, rounded once to bf16
-//     and written into the swizzled MMA tile (the reference's LDS round trip:
-//     ..mxfp8_16mx8_32nx1_template.hpp:852-864).
+//   * fp8 cache rows add warps 6-9 (convert): raw 656-byte rows are gathered unswizzled and the
+//     e4m3 bytes are converted to bf16 exactly (no rounding: e4m3 has 4 significant bits) into the
+//     swizzled MMA tile (the reference's LDS round trip: ..mxfp8_16mx8_32nx1_template.hpp:852-864).
+//     The per-128 fp32 scales never touch the operands: Q K^T accumulates one fp32 score per scale
+//     group (plus one for the rope part) and the softmax warps form s = sum_g scale_g S_g + S_rope
+//     in fp32; for P V the softmax warps store one copy of P per scale group, pre-multiplied by
+//     that group's scale, and each copy multiplies its own 128 output columns.
 //
 // Every mbarrier wait is bounded; on expiry the CTA records DSA_V32_ERR_DEVICE_WAIT in the
 // workspace status word and drains to its normal exit, where TMEM is released.
@@ -52,11 +55,12 @@ struct Cfg {
     static constexpr int kOffKv = kQBytes;
     static constexpr int kOffRaw = kOffKv + kKvStages * kKvTileBytes;
     static constexpr int kOffCtl = kOffRaw + kRawStages * kRawTileBytes;
-    static constexpr int kSmemBytes = kOffCtl + 512 + 1024;  // control block + slack for 1024-byte alignment
+    static constexpr int kSmemBytes = kOffCtl + 1536 + 1024;  // control block + slack for 1024-byte alignment
 };
 
 // control block (after the tiles)
 struct Ctl {
+    float row_scale[2][kTileRows][4];  // fp8 cache: the four fp32 scales of every row of a tile
     uint64_t q_full, q_empty, o_free;
     uint64_t kv_full[2], kv_empty[2];
     uint64_t s_full[2], s_empty[2], p_full[2], pv_done[2];
@@ -65,13 +69,17 @@ struct Ctl {
     uint32_t tmem_base;
     int abort_flag;
 };
-static_assert(sizeof(Ctl) <= 512, "control block");
+static_assert(sizeof(Ctl) <= 1536, "control block");
 
-// TMEM columns
+// TMEM columns.
+//   bf16 cache: O [0,256) | S double-buffered 2 x 32 | P double-buffered 2 x 16 (packed bf16 pairs)
+//   fp8 cache:  O [0,256) | five S accumulators of 32 columns (one per 128-value scale group of
+//               the latent part, one for the rope part) | two P variants of 16 columns (P times
+//               the scale of each of the two scale groups this CTA's output half covers)
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColO = 0;     // 256 fp32 columns
-constexpr uint32_t kColS = 256;   // 2 x 32 fp32 columns
-constexpr uint32_t kColP = 320;   // 2 x 16 columns of packed bf16 pairs
+constexpr uint32_t kColO = 0;
+constexpr uint32_t kColS = 256;
+template <bool kFp8> __host__ __device__ constexpr uint32_t col_p() { return kFp8 ? 256 + 5 * 32 : 256 + 2 * 32; }
 
 // ------------------------------------------------------------------ index translation
 // Top-k slot value -> physical cache row, or -1 when the slot is padding / unusable.
@@ -217,14 +225,17 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (lane == 0) {
             constexpr uint32_t idesc_qk = make_idesc_bf16(kHeadsPerBlock, kTileRows, false);
             constexpr uint32_t idesc_pv = make_idesc_bf16(kHeadsPerBlock, kDvHalf, true);
+            constexpr uint32_t idesc_pv128 = make_idesc_bf16(kHeadsPerBlock, 128, true);
             constexpr int S = C::kKvStages;
+            constexpr int SB = kFp8 ? 1 : 2;  // S / P buffers
+            constexpr uint32_t kColP = col_p<kFp8>();
             uint32_t it_base = 0;
             int item_n = 0;
             bool ok = true;
             auto issue_qk = [&](uint32_t it, bool last_of_item) {
-                const int s = it % S, sb = it & 1;
+                const int s = it % S, sb = it % SB;
                 if (!mbar_wait(smem_u32(&ctl->kv_full[s]), (it / S) & 1, abort_flag)) { ok = false; return; }
-                if (!mbar_wait(smem_u32(&ctl->s_empty[sb]), ((it >> 1) & 1) ^ 1, abort_flag)) { ok = false; return; }
+                if (!mbar_wait(smem_u32(&ctl->s_empty[sb]), ((it / SB) & 1) ^ 1, abort_flag)) { ok = false; return; }
                 tc_fence_after();
                 const uint32_t kv = smem_u32(sKV + s * kKvTileBytes);
                 const uint32_t q = smem_u32(sQ);
@@ -233,26 +244,40 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     const int kb = ks >> 2, kin = ks & 3;
                     const uint64_t a = make_smem_desc_sw128(q + kb * kQBlockBytes + kin * 32, 16, 1024);
                     const uint64_t b = make_smem_desc_sw128(kv + kb * kKvBlockBytes + kin * 32, 16, 1024);
-                    umma_ss(tmem + kColS + sb * 32, a, b, idesc_qk, ks > 0 ? 1u : 0u);
+                    if (kFp8) {
+                        // one accumulator per 128-value scale group (two 64-column blocks), one for rope
+                        umma_ss(tmem + kColS + (kb >> 1) * 32, a, b, idesc_qk, (ks & 7) ? 1u : 0u);
+                    } else {
+                        umma_ss(tmem + kColS + sb * 32, a, b, idesc_qk, ks > 0 ? 1u : 0u);
+                    }
                 }
                 tc_commit(smem_u32(&ctl->s_full[sb]));
                 if (last_of_item) tc_commit(smem_u32(&ctl->q_empty));
             };
             auto issue_pv = [&](uint32_t it, bool first_of_item) {
-                const int s = it % S, sb = it & 1;
-                if (!mbar_wait(smem_u32(&ctl->p_full[sb]), (it >> 1) & 1, abort_flag)) { ok = false; return; }
+                const int s = it % S, sb = it % SB;
+                if (!mbar_wait(smem_u32(&ctl->p_full[sb]), (it / SB) & 1, abort_flag)) { ok = false; return; }
                 if (first_of_item && item_n > 0)
                     if (!mbar_wait(smem_u32(&ctl->o_free), (item_n - 1) & 1, abort_flag)) { ok = false; return; }
                 tc_fence_after();
                 const uint32_t v = smem_u32(sKV + s * kKvTileBytes + (4 * half) * kKvBlockBytes);
 #pragma unroll
                 for (int ks = 0; ks < kTileRows / 16; ++ks) {
-                    const uint64_t b = make_smem_desc_sw128(v + ks * 2048, kKvBlockBytes, 1024);
-                    umma_ts(tmem + kColO, tmem + kColP + sb * 16 + ks * 8, b, idesc_pv,
-                            (first_of_item && ks == 0) ? 0u : 1u);
+                    const uint32_t acc = (first_of_item && ks == 0) ? 0u : 1u;
+                    if (kFp8) {
+                        // two 128-column halves, each with P pre-multiplied by its scale group
+#pragma unroll
+                        for (int v2 = 0; v2 < 2; ++v2) {
+                            const uint64_t b = make_smem_desc_sw128(v + v2 * 2 * kKvBlockBytes + ks * 2048, kKvBlockBytes, 1024);
+                            umma_ts(tmem + kColO + v2 * 128, tmem + kColP + v2 * 16 + ks * 8, b, idesc_pv128, acc);
+                        }
+                    } else {
+                        const uint64_t b = make_smem_desc_sw128(v + ks * 2048, kKvBlockBytes, 1024);
+                        umma_ts(tmem + kColO, tmem + kColP + sb * 16 + ks * 8, b, idesc_pv, acc);
+                    }
                 }
                 tc_commit(smem_u32(&ctl->kv_empty[s]));
-                tc_commit(smem_u32(&ctl->pv_done[sb]));
+                tc_commit(smem_u32(&ctl->pv_done[it & 1]));
             };
             for (int w = w_begin; w < w_end && ok; ++w, ++item_n) {
                 const dsa_v32_work_info wi = p.works[w];
@@ -274,6 +299,8 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     } else if (warp < 4) {
         // ============================================================ softmax + epilogue
         constexpr int S = C::kKvStages;
+        constexpr int SB = kFp8 ? 1 : 2;
+        constexpr uint32_t kColP = col_p<kFp8>();
         const int row = tid;  // head row inside the block == TMEM lane
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
         uint32_t it = 0;
@@ -283,23 +310,42 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             float m_ref = -INFINITY;  // running reference maximum, log2 domain
             float l = 0.0f;
             for (int t = 0; t < n_tiles; ++t, ++it) {
-                const int sb = it & 1;
+                const int sb = it % SB;
                 if (!mbar_wait(smem_u32(&ctl->kv_full[it % S]), (it / S) & 1, abort_flag)) goto done;
                 const uint32_t mask = ctl->tile_mask[it & 3];
-                if (!mbar_wait(smem_u32(&ctl->s_full[sb]), (it >> 1) & 1, abort_flag)) goto done;
+                if (!mbar_wait(smem_u32(&ctl->s_full[sb]), (it / SB) & 1, abort_flag)) goto done;
                 tc_fence_after();
-                uint32_t sr[32];
-                tmem_ld32(lane_base + kColS + sb * 32, sr);
-                tmem_wait_ld();
+                float tv[32];
+                if (kFp8) {
+                    // s = sum_g scale[row][g] * S_g + S_rope : the cache values went through the MMA
+                    // unscaled (e4m3 is exact in bf16), so nothing is rounded before this point
+                    uint32_t sr[32];
+                    tmem_ld32(lane_base + kColS + 4 * 32, sr);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) tv[j] = __uint_as_float(sr[j]);
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        tmem_ld32(lane_base + kColS + g * 32, sr);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) tv[j] = fmaf(ctl->row_scale[it & 1][j][g], __uint_as_float(sr[j]), tv[j]);
+                    }
+                } else {
+                    uint32_t sr[32];
+                    tmem_ld32(lane_base + kColS + sb * 32, sr);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) tv[j] = __uint_as_float(sr[j]);
+                }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[sb]));
 
-                float tv[32];
                 float mt = -INFINITY;
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
-                    const float x = __uint_as_float(sr[j]) * p.scale_log2;
+                    const float x = tv[j] * p.scale_log2;
                     tv[j] = ((mask >> j) & 1u) ? x : -INFINITY;
                     mt = fmaxf(mt, tv[j]);
                 }
@@ -328,17 +374,34 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     m_ref = m_new;
                 }
                 const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
-                uint32_t pk[16];
                 float lsum = 0.0f;
+                if (kFp8) {
+                    uint32_t pk0[16], pk1[16];
+                    const int g0 = 2 * half;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const float p0 = ex2_approx(tv[2 * j] - m_use);
-                    const float p1 = ex2_approx(tv[2 * j + 1] - m_use);
-                    lsum += p0 + p1;
-                    pk[j] = pack_bf16x2(p0, p1);
+                    for (int j = 0; j < 16; ++j) {
+                        const float p0 = ex2_approx(tv[2 * j] - m_use);
+                        const float p1 = ex2_approx(tv[2 * j + 1] - m_use);
+                        lsum += p0 + p1;
+                        const float* sc0 = ctl->row_scale[it & 1][2 * j];
+                        const float* sc1 = ctl->row_scale[it & 1][2 * j + 1];
+                        pk0[j] = pack_bf16x2(p0 * sc0[g0], p1 * sc1[g0]);
+                        pk1[j] = pack_bf16x2(p0 * sc0[g0 + 1], p1 * sc1[g0 + 1]);
+                    }
+                    tmem_st16(lane_base + kColP, pk0);
+                    tmem_st16(lane_base + kColP + 16, pk1);
+                } else {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float p0 = ex2_approx(tv[2 * j] - m_use);
+                        const float p1 = ex2_approx(tv[2 * j + 1] - m_use);
+                        lsum += p0 + p1;
+                        pk[j] = pack_bf16x2(p0, p1);
+                    }
+                    tmem_st16(lane_base + kColP + sb * 16, pk);
                 }
                 l += lsum;
-                tmem_st16(lane_base + kColP + sb * 16, pk);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
@@ -414,7 +477,9 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const int ri = r & 3;
                 const uint8_t* src = grp + (qd >> 1) * 1024 + ri * 256 + (qd & 1) * 128;
                 const uint8_t* tail = grp + 2048 + ri * 144;
-                const float scale = reinterpret_cast<const float*>(tail)[qd];
+                // values go to the MMA unscaled (every e4m3 value is exact in bf16); the row's scales
+                // are applied to the fp32 scores and to P by the softmax warps
+                ctl->row_scale[it & 1][r][qd] = reinterpret_cast<const float*>(tail)[qd];
                 uint8_t* dst_row = sKV + r * 128;
 #pragma unroll
                 for (int cc = 0; cc < 8; ++cc) {
@@ -431,8 +496,8 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         const __half2 a = *reinterpret_cast<const __half2*>(&h01);
                         const __half2 b = *reinterpret_cast<const __half2*>(&h23);
                         const float2 fa = __half22float2(a), fb = __half22float2(b);
-                        o[2 * k + 0] = pack_bf16x2(fa.x * scale, fa.y * scale);
-                        o[2 * k + 1] = pack_bf16x2(fb.x * scale, fb.y * scale);
+                        o[2 * k + 0] = pack_bf16x2(fa.x, fa.y);
+                        o[2 * k + 1] = pack_bf16x2(fb.x, fb.y);
                     }
                     // 16 fp8 -> 16 bf16 = two 16-byte chunks of the 64-column block (2*qd + c/4)
                     const int kb = 2 * qd + (c >> 2);

@@ -171,6 +171,24 @@ int dsa_v32_combine(const dsa_v32_attn_args* args, void* stream);
 int dsa_v32_decode_pipeline(const dsa_v32_attn_args* args, int run_plan, void* stream);
 
 /*
+ * Host-buffer form of the pipeline, the call a serving loop makes once per step: copies this
+ * step's queries and top-k lists from (pinned) host memory into args->q / args->indices, runs
+ * attention + merge, and copies out / lse back to host memory, all asynchronously on `stream`.
+ * The cache, block table and workspace in `args` stay resident on the device.  Any of the host
+ * pointers may be NULL to skip that copy.  No counterpart in the reference, whose harness copies
+ * with hipMemcpy around the launch (common/host.cc:640-645, :599-600).
+ */
+typedef struct dsa_v32_host_io {
+    const void* q_host;          /* bf16, laid out like args->q */
+    const int32_t* indices_host; /* [total_q, topk] */
+    void* out_host;              /* bf16, laid out like args->out */
+    float* lse_host;             /* [total_q, H] */
+    int64_t q_bytes;
+    int64_t out_bytes;
+} dsa_v32_host_io;
+int dsa_v32_decode_pipeline_host(const dsa_v32_attn_args* args, const dsa_v32_host_io* io, void* stream);
+
+/*
  * Reads (and clears) the device status word of the workspace after synchronising `stream`:
  * 0, or DSA_V32_ERR_DEVICE_WAIT when a bounded wait inside a kernel ran out.
  */

@@ -44,10 +44,15 @@ class AttnArgs(C.Structure):
                 ("kv_dtype", C.c_int32), ("sm_scale", C.c_float)]
 
 
+class HostIO(C.Structure):
+    _fields_ = [("q_host", C.c_void_p), ("indices_host", C.c_void_p), ("out_host", C.c_void_p),
+                ("lse_host", C.c_void_p), ("q_bytes", C.c_int64), ("out_bytes", C.c_int64)]
+
+
 EXPORTS = ["dsa_v32_abi_version", "dsa_v32_error_string", "dsa_v32_plan_info_get", "dsa_v32_plan",
            "dsa_v32_plan_host", "dsa_v32_plan_read", "dsa_v32_decode_bf16", "dsa_v32_decode_fp8",
            "dsa_v32_prefill_bf16", "dsa_v32_combine", "dsa_v32_decode_pipeline", "dsa_v32_device_status",
-           "dsa_v32_debug_rows", "dsa_v32_pack_fp8_rows"]
+           "dsa_v32_debug_rows", "dsa_v32_pack_fp8_rows", "dsa_v32_decode_pipeline_host"]
 
 _lib = None
 
@@ -77,6 +82,7 @@ def lib():
                      "dsa_v32_device_status"):
             getattr(L, name).argtypes = [C.POINTER(AttnArgs), C.c_void_p]
         L.dsa_v32_decode_pipeline.argtypes = [C.POINTER(AttnArgs), C.c_int, C.c_void_p]
+        L.dsa_v32_decode_pipeline_host.argtypes = [C.POINTER(AttnArgs), C.POINTER(HostIO), C.c_void_p]
         L.dsa_v32_debug_rows.argtypes = [C.POINTER(AttnArgs), C.c_void_p, C.c_void_p]
         L.dsa_v32_pack_fp8_rows.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]
         _lib = L
@@ -236,3 +242,17 @@ def pack_fp8_rows(latent, rope, out=None, dst_rows=None):
     _check(lib().dsa_v32_pack_fp8_rows(latent.data_ptr(), rope.data_ptr(), dr, out.data_ptr(), n, _stream()),
            "dsa_v32_pack_fp8_rows")
     return out
+
+
+def mla_decode_step_host(args, q_host, indices_host, out_host, lse_host):
+    """One serving step with pinned HOST tensors: H2D of q / indices, attention + merge, D2H of
+    out / lse, all on the current stream (asynchronous; synchronise the stream to read results).
+    `args` comes from make_args and names the resident device buffers."""
+    io = HostIO()
+    io.q_host = q_host.data_ptr()
+    io.indices_host = indices_host.data_ptr()
+    io.out_host = out_host.data_ptr()
+    io.lse_host = lse_host.data_ptr()
+    io.q_bytes = q_host.numel() * q_host.element_size()
+    io.out_bytes = out_host.numel() * out_host.element_size()
+    _check(lib().dsa_v32_decode_pipeline_host(C.byref(args), C.byref(io), _stream()), "dsa_v32_decode_pipeline_host")

@@ -297,6 +297,34 @@ int dsa_v32_decode_pipeline(const dsa_v32_attn_args* a, int run_plan, void* stre
     return dsa_v32_combine(a, stream);
 }
 
+int dsa_v32_decode_pipeline_host(const dsa_v32_attn_args* a, const dsa_v32_host_io* io, void* stream) {
+    if (!a || !io) return DSA_V32_ERR_NULL;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+    if (io->q_host) {
+        if (io->q_bytes <= 0) return DSA_V32_ERR_SHAPE;
+        e = cudaMemcpyAsync(const_cast<void*>(a->q), io->q_host, (size_t)io->q_bytes, cudaMemcpyHostToDevice, st);
+        if (e != cudaSuccess) return (int)e;
+    }
+    if (io->indices_host) {
+        e = cudaMemcpyAsync(const_cast<int32_t*>(a->indices), io->indices_host, (size_t)a->total_q * a->topk * 4,
+                            cudaMemcpyHostToDevice, st);
+        if (e != cudaSuccess) return (int)e;
+    }
+    int rc = dsa_v32_decode_pipeline(a, 0, stream);
+    if (rc) return rc;
+    if (io->out_host) {
+        if (io->out_bytes <= 0) return DSA_V32_ERR_SHAPE;
+        e = cudaMemcpyAsync(io->out_host, a->out, (size_t)io->out_bytes, cudaMemcpyDeviceToHost, st);
+        if (e != cudaSuccess) return (int)e;
+    }
+    if (io->lse_host && a->lse) {
+        e = cudaMemcpyAsync(io->lse_host, a->lse, (size_t)a->total_q * a->H * 4, cudaMemcpyDeviceToHost, st);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return DSA_V32_OK;
+}
+
 int dsa_v32_device_status(const dsa_v32_attn_args* a, void* stream) {
     if (!a || !a->workspace) return DSA_V32_ERR_NULL;
     cudaStream_t st = (cudaStream_t)stream;

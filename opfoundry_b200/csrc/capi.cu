@@ -12,7 +12,7 @@
 #include "tmap.h"
 
 namespace dsa {
-int smem_bytes_attn(bool fp8);
+int max_resident_pairs(bool fp8, int* out);
 cudaError_t launch_attn(bool fp8, int num_lists, const CUtensorMap& tq, const CUtensorMap& tkv, const CUtensorMap& ttail,
                         const AttnParams& p, cudaStream_t stream);
 cudaError_t launch_combine(const float* o_accum, const float* lse_accum, const int32_t* reduce_indptr,
@@ -58,14 +58,17 @@ Registry& registry() {
     return r;
 }
 
+// Processors the planner may count on: twice the number of CTA pairs (clusters of two) the device
+// keeps resident at once, which can be below the SM count when a GPC holds an odd number of SMs.
 int device_sm_count(int* out) {
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return (int)e;
-    int n = 0;
-    e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (e != cudaSuccess) return (int)e;
-    *out = n;
+    int a = 0, b = 0;
+    int rc = max_resident_pairs(true, &a);
+    if (rc) return rc;
+    rc = max_resident_pairs(false, &b);
+    if (rc) return rc;
+    const int pairs = a < b ? a : b;
+    if (pairs < 1) return DSA_V32_ERR_DRIVER;
+    *out = 2 * pairs;
     return 0;
 }
 

@@ -1,36 +1,47 @@
 // Sparse MLA attention for sm_100a: decode (split over the top-k list) and prefill share one
-// warp-specialised kernel.
+// warp-specialised kernel run by clusters of two CTAs.
 //
 // What it computes is the reference lab's decode kernel family
 // (opus_attn/dsa_v32/gfx950/mla_decode_a16w16_16mx4_64nx1_template.hpp:815-926 and the mxfp8
 // variant mla_decode_mxfp8_16mx8_32nx1_template.hpp:1362-1490): for one work item = one query
 // row x one block of 128 heads x a slice of the query's top-k list, an online-softmax attention
 // over the gathered latent rows, K = all 576 columns of a row, V = its first 512 columns.
-// How it does it is specific to Blackwell:
+// How it does it is specific to Blackwell.
 //
-//   * one CTA pair per work list; the two CTAs of a pair walk the same list and each accumulates
-//     one 256-column half of the output (the full 128 x 512 fp32 output would fill all of TMEM);
-//   * warp 4 (producer): reads 32 top-k slots, translates them through the block table, and
-//     gathers the rows with TMA tile::gather4 into 128-byte-swizzled shared memory; the query
-//     block is loaded once per item with a tiled TMA load;
-//   * warp 5 (MMA issuer): S = Q K^T as 36 tcgen05.mma (M=128, N=32, K=16) with both operands in
-//     shared memory and the accumulator in TMEM, then O += P V as 2 tcgen05.mma (M=128, N=256,
-//     K=16) whose A operand is P in TMEM and whose B operand is the same gathered tile described
-//     MN-major;
-//   * warps 0-3 (softmax): one thread per head row; tcgen05.ld of S, log2-domain online softmax
-//     with lazy rescaling (the reference's threshold of 8: ..16mx4_64nx1_template.hpp:700-725),
-//     P -> bf16 -> tcgen05.st, epilogue O / l -> bf16 (or fp32 partial + lse for split items);
-//   * fp8 cache rows add warps 6-9 (convert): raw 656-byte rows are gathered unswizzled and the
-//     e4m3 bytes are converted to bf16 exactly (no rounding: e4m3 has 4 significant bits) into the
-//     swizzled MMA tile (the reference's LDS round trip: ..mxfp8_16mx8_32nx1_template.hpp:852-864).
-//     The per-128 fp32 scales never touch the operands: Q K^T accumulates one fp32 score per scale
-//     group (plus one for the rope part) and the softmax warps form s = sum_g scale_g S_g + S_rope
-//     in fp32; for P V the softmax warps store one copy of P per scale group, pre-multiplied by
-//     that group's scale, and each copy multiplies its own 128 output columns.
+// The 128 x 512 fp32 output would fill all 512 TMEM columns, so two CTAs (a cluster) share a work
+// item and split the 576 columns of the latent row between them:
+//       CTA 0: columns [0, 256)             CTA 1: columns [256, 512) + the 64 rope columns
+// Each CTA loads only its columns of Q, gathers only its columns of every selected row, computes
+// the partial scores Q_c K_c^T over its columns and owns the 256 output columns that are the
+// first 256 of its slice (V is a prefix of K), so no byte of the cache is fetched or converted
+// twice.  The partial scores are summed across the pair through distributed shared memory (each
+// softmax thread stores its row of partials into the peer's exchange buffer and arrives on the
+// peer's mbarrier); both CTAs then run the same softmax on the same numbers.
 //
-// Every mbarrier wait is bounded; on expiry the CTA records DSA_V32_ERR_DEVICE_WAIT in the
-// workspace status word and drains to its normal exit, where TMEM is released.
+// Warp roles inside a CTA:
+//   warps 0-3  softmax: one thread per head row (= TMEM lane); tcgen05.ld of the partial scores,
+//              exchange, log2-domain online softmax with lazy rescaling (the reference's threshold
+//              of 8: ..16mx4_64nx1_template.hpp:700-725), P -> bf16 -> tcgen05.st, epilogue
+//              O / l -> bf16, or fp32 partial + lse for split items
+//   warp 4     producer: reads 32 top-k slots, translates them through the block table and
+//              gathers the rows with TMA tile::gather4 (bf16 cache: straight into the 128-byte
+//              swizzled MMA tile; fp8 cache: raw bytes); loads the Q slice once per item
+//   warp 5     MMA issuer: S_c = Q_c K_c^T (tcgen05.mma M=128, N=32, K=16, operands in shared
+//              memory, accumulator in TMEM), then O_c += P V_c (A = P in TMEM, B = the same
+//              gathered tile described MN-major)
+//   warps 6-9  fp8 cache only: convert e4m3 -> bf16 exactly (e4m3 has 4 significant bits) into
+//              the swizzled MMA tile (the reference's LDS round trip:
+//              ..mxfp8_16mx8_32nx1_template.hpp:852-864).  The per-128 fp32 scales never touch the
+//              operands: Q K^T keeps one fp32 accumulator per scale group (plus one for rope) and
+//              the softmax warps form sum_g scale_g S_g in fp32 before the exchange; for P V they
+//              store one copy of P per scale group, pre-multiplied by that group's scale, and each
+//              copy multiplies its own 128 output columns.
+//
+// Every mbarrier wait is bounded; on expiry the CTA raises its own and its peer's abort flag,
+// records DSA_V32_ERR_DEVICE_WAIT in the workspace status word and both drain to the normal exit
+// (cluster barrier, TMEM release).
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cfloat>
 #include "defs.h"
 #include "ptx.cuh"
@@ -38,48 +49,52 @@
 namespace dsa {
 
 // ------------------------------------------------------------------ shared-memory map
-constexpr int kQKBlocks = kDQK / 64;                        // 9 blocks of 64 columns (128 bytes)
-constexpr int kQBlockBytes = kHeadsPerBlock * 128;          // 16384
-constexpr int kQBytes = kQKBlocks * kQBlockBytes;           // 147456
-constexpr int kKvBlockBytes = kTileRows * 128;              // 4096: one 64-column block of a tile
-constexpr int kKvTileBytes = kQKBlocks * kKvBlockBytes;     // 36864
-constexpr int kRawGroupBytes = 2688;                        // 4 rows: 4x256 | 4x256 | 4x144 (+pad to 128)
-constexpr int kRawTileBytes = (kTileRows / 4) * kRawGroupBytes;  // 21504
-constexpr int kRawTxBytes = kTileRows * kFp8RowBytes;       // bytes the three gathers deliver per tile
+constexpr int kMaxKBlocks = 5;                            // 64-column blocks per CTA: 4 (CTA 0) or 5 (CTA 1)
+constexpr int kQBlockBytes = kHeadsPerBlock * 128;        // 16384
+constexpr int kQBytesMax = kMaxKBlocks * kQBlockBytes;    // 81920
+constexpr int kKvBlockBytes = kTileRows * 128;            // 4096: one 64-column block of a 32-row tile
+constexpr int kKvTileBytes = kMaxKBlocks * kKvBlockBytes; // 20480
+constexpr int kRawGroupBytes = 1024 + 640;                // 4 rows: 4 x 256 latent bytes | 4 x 144 tail (+pad)
+constexpr int kRawTileBytes = (kTileRows / 4) * kRawGroupBytes;   // 13312
+constexpr int kRawTxBytes = kTileRows * (256 + 144);      // bytes the two gathers deliver per tile
+constexpr int kXbufBytes = kHeadsPerBlock * kTileRows * 4;        // 16384: one tile of fp32 partial scores
+constexpr int kMaskSlots = 16;
 
 template <bool kFp8>
 struct Cfg {
-    static constexpr int kKvStages = kFp8 ? 1 : 2;
-    static constexpr int kRawStages = kFp8 ? 2 : 0;
+    static constexpr int kKvStages = kFp8 ? 2 : 5;   // MMA-ready bf16 tiles
+    static constexpr int kRawStages = kFp8 ? 5 : 0;  // raw fp8 tiles in flight
     static constexpr int kThreads = kFp8 ? 320 : 192;
-    static constexpr int kOffKv = kQBytes;
+    static constexpr int kOffKv = kQBytesMax;
     static constexpr int kOffRaw = kOffKv + kKvStages * kKvTileBytes;
-    static constexpr int kOffCtl = kOffRaw + kRawStages * kRawTileBytes;
-    static constexpr int kSmemBytes = kOffCtl + 1536 + 1024;  // control block + slack for 1024-byte alignment
+    static constexpr int kOffX = kOffRaw + kRawStages * kRawTileBytes;
+    static constexpr int kOffCtl = kOffX + 2 * kXbufBytes;
+    static constexpr int kCtlBytes = 2048;
+    static constexpr int kSmemBytes = kOffCtl + kCtlBytes + 1024;  // + slack for 1024-byte alignment
 };
 
-// control block (after the tiles)
 struct Ctl {
-    float row_scale[2][kTileRows][4];  // fp8 cache: the four fp32 scales of every row of a tile
+    float row_scale[2][kTileRows][2];  // fp8 cache: the two scales (this CTA's groups) of every tile row
     uint64_t q_full, q_empty, o_free;
-    uint64_t kv_full[2], kv_empty[2];
+    uint64_t kv_full[8], kv_empty[8];
+    uint64_t raw_full[8], raw_empty[8];
     uint64_t s_full[2], s_empty[2], p_full[2], pv_done[2];
-    uint64_t raw_full[2], raw_empty[2];
-    uint32_t tile_mask[4];
+    uint64_t x_full[2];                // the peer's partial scores have landed in exchange buffer b
+    uint32_t tile_mask[kMaskSlots];
     uint32_t tmem_base;
     int abort_flag;
 };
-static_assert(sizeof(Ctl) <= 1536, "control block");
+static_assert(sizeof(Ctl) <= 2048, "control block");
 
-// TMEM columns.
-//   bf16 cache: O [0,256) | S double-buffered 2 x 32 | P double-buffered 2 x 16 (packed bf16 pairs)
-//   fp8 cache:  O [0,256) | five S accumulators of 32 columns (one per 128-value scale group of
-//               the latent part, one for the rope part) | two P variants of 16 columns (P times
-//               the scale of each of the two scale groups this CTA's output half covers)
+// TMEM columns (512 allocated).
+//   bf16 cache: O [0,256) | S 2 x 32 | P 2 x 16 (packed bf16 pairs)
+//   fp8 cache:  O [0,256) | S 2 buffers x 3 accumulators x 32 (scale group a, scale group b, rope)
+//               | P 2 buffers x 2 variants x 16
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColO = 0;
 constexpr uint32_t kColS = 256;
-template <bool kFp8> __host__ __device__ constexpr uint32_t col_p() { return kFp8 ? 256 + 5 * 32 : 256 + 2 * 32; }
+template <bool kFp8> __host__ __device__ constexpr uint32_t s_stride() { return kFp8 ? 96 : 32; }
+template <bool kFp8> __host__ __device__ constexpr uint32_t col_p() { return kColS + 2 * s_stride<kFp8>(); }
 
 // ------------------------------------------------------------------ index translation
 // Top-k slot value -> physical cache row, or -1 when the slot is padding / unusable.
@@ -113,11 +128,16 @@ __global__ void __launch_bounds__(Cfg<kFp8>::kThreads, 1)
 sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
                   const __grid_constant__ CUtensorMap tm_kv_tail, const AttnParams p) {
     using C = Cfg<kFp8>;
+    constexpr int S = C::kKvStages;
+    constexpr int R = kFp8 ? C::kRawStages : 1;
     extern __shared__ uint8_t smem_raw[];
+    // Both CTAs of a cluster compute the same offsets (the dynamic shared window starts at the same
+    // shared::cta address in every CTA of a launch), so a peer address is own address + mapa.
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sQ = smem;
     uint8_t* sKV = smem + C::kOffKv;
     uint8_t* sRaw = smem + C::kOffRaw;
+    uint8_t* sX = smem + C::kOffX;
     Ctl* ctl = reinterpret_cast<Ctl*>(smem + C::kOffCtl);
     volatile int* abort_flag = &ctl->abort_flag;
 
@@ -125,7 +145,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int warp = tid >> 5;
     const int lane = tid & 31;
     const int list = blockIdx.x >> 1;
-    const int half = blockIdx.x & 1;  // which 256 output columns this CTA accumulates
+    const int half = (int)cluster_ctarank();      // 0: columns [0,256); 1: columns [256,576)
+    const int peer = half ^ 1;
+    const int nkb = half ? 5 : 4;                 // 64-column blocks of this CTA's slice
+    const int col0 = half ? 256 : 0;              // first latent column of the slice
     const int w_begin = __ldg(p.list_indptr + list);
     const int w_end = __ldg(p.list_indptr + list + 1);
 
@@ -133,15 +156,18 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         mbar_init(smem_u32(&ctl->q_full), 1);
         mbar_init(smem_u32(&ctl->q_empty), 1);
         mbar_init(smem_u32(&ctl->o_free), 4);
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < 8; ++i) {
             mbar_init(smem_u32(&ctl->kv_full[i]), kFp8 ? 4 : 1);
             mbar_init(smem_u32(&ctl->kv_empty[i]), 1);
+            mbar_init(smem_u32(&ctl->raw_full[i]), 1);
+            mbar_init(smem_u32(&ctl->raw_empty[i]), 4);
+        }
+        for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&ctl->s_full[i]), 1);
             mbar_init(smem_u32(&ctl->s_empty[i]), 4);
             mbar_init(smem_u32(&ctl->p_full[i]), 4);
             mbar_init(smem_u32(&ctl->pv_done[i]), 1);
-            mbar_init(smem_u32(&ctl->raw_full[i]), 1);
-            mbar_init(smem_u32(&ctl->raw_empty[i]), 4);
+            mbar_init(smem_u32(&ctl->x_full[i]), kHeadsPerBlock);
         }
         ctl->abort_flag = 0;
         fence_mbar_init();
@@ -157,8 +183,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
     tc_fence_before();
     __syncthreads();
+    cluster_sync_all();   // the peer's barriers exist before anything is sent to it
     tc_fence_after();
     const uint32_t tmem = ctl->tmem_base;
+    const uint32_t peer_abort = map_to_cta(smem_u32(&ctl->abort_flag), peer);
 
     if (warp == 4) {
         // ============================================================ producer
@@ -168,13 +196,13 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         for (int w = w_begin; w < w_end; ++w, ++item_n) {
             const dsa_v32_work_info wi = p.works[w];
             const int seq = wi.q_row / p.s_q;
-            if (!mbar_wait(smem_u32(&ctl->q_empty), (item_n & 1) ^ 1, abort_flag)) goto done;
+            if (!warp_wait(smem_u32(&ctl->q_empty), (item_n & 1) ^ 1, abort_flag)) goto done;
             if (lane == 0) {
                 const uint32_t bar = smem_u32(&ctl->q_full);
-                mbar_arrive_expect_tx(bar, kQBytes);
-                for (int kb = 0; kb < kQKBlocks; ++kb)
-                    tma_load_3d(smem_u32(sQ + kb * kQBlockBytes), &tm_q, bar, kb * 64, wi.head_block * kHeadsPerBlock,
-                                wi.q_row);
+                mbar_arrive_expect_tx(bar, nkb * kQBlockBytes);
+                for (int kb = 0; kb < nkb; ++kb)
+                    tma_load_3d(smem_u32(sQ + kb * kQBlockBytes), &tm_q, bar, col0 + kb * 64,
+                                wi.head_block * kHeadsPerBlock, wi.q_row);
             }
             const int32_t* idx_row = p.indices + (size_t)wi.q_row * p.topk;
             for (int k0 = wi.k_begin; k0 < wi.k_end; k0 += kTileRows, ++it) {
@@ -189,33 +217,32 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const int r2 = __shfl_sync(0xffffffffu, coord, 4 * g + 2);
                 const int r3 = __shfl_sync(0xffffffffu, coord, 4 * g + 3);
                 if (!kFp8) {
-                    const int s = it & 1;
-                    if (!mbar_wait(smem_u32(&ctl->kv_empty[s]), ((it >> 1) & 1) ^ 1, abort_flag)) goto done;
+                    const int s = it % S;
+                    if (!warp_wait(smem_u32(&ctl->kv_empty[s]), ((it / S) & 1) ^ 1, abort_flag)) goto done;
                     const uint32_t bar = smem_u32(&ctl->kv_full[s]);
                     if (lane == 0) {
-                        ctl->tile_mask[it & 3] = mask;
-                        mbar_arrive_expect_tx(bar, kKvTileBytes);
+                        ctl->tile_mask[it % kMaskSlots] = mask;
+                        mbar_arrive_expect_tx(bar, nkb * kKvBlockBytes);
                     }
                     __syncwarp();
                     if (lane < 8) {
                         const uint32_t dst = smem_u32(sKV + s * kKvTileBytes + g * 512);
-                        for (int kb = 0; kb < kQKBlocks; ++kb)
-                            tma_gather4(dst + kb * kKvBlockBytes, &tm_kv, bar, kb * 64, r0, r1, r2, r3);
+                        for (int kb = 0; kb < nkb; ++kb)
+                            tma_gather4(dst + kb * kKvBlockBytes, &tm_kv, bar, col0 + kb * 64, r0, r1, r2, r3);
                     }
                 } else {
-                    const int s = it & 1;
-                    if (!mbar_wait(smem_u32(&ctl->raw_empty[s]), ((it >> 1) & 1) ^ 1, abort_flag)) goto done;
+                    const int s = it % R;
+                    if (!warp_wait(smem_u32(&ctl->raw_empty[s]), ((it / R) & 1) ^ 1, abort_flag)) goto done;
                     const uint32_t bar = smem_u32(&ctl->raw_full[s]);
                     if (lane == 0) {
-                        ctl->tile_mask[it & 3] = mask;
+                        ctl->tile_mask[it % kMaskSlots] = mask;
                         mbar_arrive_expect_tx(bar, kRawTxBytes);
                     }
                     __syncwarp();
                     if (lane < 8) {
                         const uint32_t dst = smem_u32(sRaw + s * kRawTileBytes + g * kRawGroupBytes);
-                        tma_gather4(dst, &tm_kv, bar, 0, r0, r1, r2, r3);
-                        tma_gather4(dst + 1024, &tm_kv, bar, 256, r0, r1, r2, r3);
-                        tma_gather4(dst + 2048, &tm_kv_tail, bar, 512, r0, r1, r2, r3);
+                        tma_gather4(dst, &tm_kv, bar, col0, r0, r1, r2, r3);              // 256 latent bytes
+                        tma_gather4(dst + 1024, &tm_kv_tail, bar, 512, r0, r1, r2, r3);  // scales + rope
                     }
                 }
             }
@@ -226,50 +253,49 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             constexpr uint32_t idesc_qk = make_idesc_bf16(kHeadsPerBlock, kTileRows, false);
             constexpr uint32_t idesc_pv = make_idesc_bf16(kHeadsPerBlock, kDvHalf, true);
             constexpr uint32_t idesc_pv128 = make_idesc_bf16(kHeadsPerBlock, 128, true);
-            constexpr int S = C::kKvStages;
-            constexpr int SB = kFp8 ? 1 : 2;  // S / P buffers
             constexpr uint32_t kColP = col_p<kFp8>();
             uint32_t it_base = 0;
             int item_n = 0;
             bool ok = true;
             auto issue_qk = [&](uint32_t it, bool last_of_item) {
-                const int s = it % S, sb = it % SB;
+                const int s = it % S, sb = it & 1;
                 if (!mbar_wait(smem_u32(&ctl->kv_full[s]), (it / S) & 1, abort_flag)) { ok = false; return; }
-                if (!mbar_wait(smem_u32(&ctl->s_empty[sb]), ((it / SB) & 1) ^ 1, abort_flag)) { ok = false; return; }
+                if (!mbar_wait(smem_u32(&ctl->s_empty[sb]), ((it >> 1) & 1) ^ 1, abort_flag)) { ok = false; return; }
                 tc_fence_after();
                 const uint32_t kv = smem_u32(sKV + s * kKvTileBytes);
                 const uint32_t q = smem_u32(sQ);
-#pragma unroll 4
-                for (int ks = 0; ks < kDQK / 16; ++ks) {
-                    const int kb = ks >> 2, kin = ks & 3;
-                    const uint64_t a = make_smem_desc_sw128(q + kb * kQBlockBytes + kin * 32, 16, 1024);
-                    const uint64_t b = make_smem_desc_sw128(kv + kb * kKvBlockBytes + kin * 32, 16, 1024);
-                    if (kFp8) {
-                        // one accumulator per 128-value scale group (two 64-column blocks), one for rope
-                        umma_ss(tmem + kColS + (kb >> 1) * 32, a, b, idesc_qk, (ks & 7) ? 1u : 0u);
-                    } else {
-                        umma_ss(tmem + kColS + sb * 32, a, b, idesc_qk, ks > 0 ? 1u : 0u);
+                const uint32_t d0 = tmem + kColS + sb * s_stride<kFp8>();
+                for (int kb = 0; kb < nkb; ++kb) {
+#pragma unroll
+                    for (int kin = 0; kin < 4; ++kin) {
+                        const uint64_t a = make_smem_desc_sw128(q + kb * kQBlockBytes + kin * 32, 16, 1024);
+                        const uint64_t b = make_smem_desc_sw128(kv + kb * kKvBlockBytes + kin * 32, 16, 1024);
+                        if (kFp8) {
+                            // one accumulator per scale group (two 64-column blocks each), one for rope
+                            umma_ss(d0 + (kb >> 1) * 32, a, b, idesc_qk, ((kb & 1) | kin) ? 1u : 0u);
+                        } else {
+                            umma_ss(d0, a, b, idesc_qk, (kb | kin) ? 1u : 0u);
+                        }
                     }
                 }
                 tc_commit(smem_u32(&ctl->s_full[sb]));
                 if (last_of_item) tc_commit(smem_u32(&ctl->q_empty));
             };
             auto issue_pv = [&](uint32_t it, bool first_of_item) {
-                const int s = it % S, sb = it % SB;
-                if (!mbar_wait(smem_u32(&ctl->p_full[sb]), (it / SB) & 1, abort_flag)) { ok = false; return; }
+                const int s = it % S, sb = it & 1;
+                if (!mbar_wait(smem_u32(&ctl->p_full[sb]), (it >> 1) & 1, abort_flag)) { ok = false; return; }
                 if (first_of_item && item_n > 0)
                     if (!mbar_wait(smem_u32(&ctl->o_free), (item_n - 1) & 1, abort_flag)) { ok = false; return; }
                 tc_fence_after();
-                const uint32_t v = smem_u32(sKV + s * kKvTileBytes + (4 * half) * kKvBlockBytes);
+                const uint32_t v = smem_u32(sKV + s * kKvTileBytes);   // V = first 256 columns of the slice
 #pragma unroll
                 for (int ks = 0; ks < kTileRows / 16; ++ks) {
                     const uint32_t acc = (first_of_item && ks == 0) ? 0u : 1u;
                     if (kFp8) {
-                        // two 128-column halves, each with P pre-multiplied by its scale group
 #pragma unroll
                         for (int v2 = 0; v2 < 2; ++v2) {
                             const uint64_t b = make_smem_desc_sw128(v + v2 * 2 * kKvBlockBytes + ks * 2048, kKvBlockBytes, 1024);
-                            umma_ts(tmem + kColO + v2 * 128, tmem + kColP + v2 * 16 + ks * 8, b, idesc_pv128, acc);
+                            umma_ts(tmem + kColO + v2 * 128, tmem + kColP + sb * 32 + v2 * 16 + ks * 8, b, idesc_pv128, acc);
                         }
                     } else {
                         const uint64_t b = make_smem_desc_sw128(v + ks * 2048, kKvBlockBytes, 1024);
@@ -277,19 +303,15 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     }
                 }
                 tc_commit(smem_u32(&ctl->kv_empty[s]));
-                tc_commit(smem_u32(&ctl->pv_done[it & 1]));
+                tc_commit(smem_u32(&ctl->pv_done[sb]));
             };
             for (int w = w_begin; w < w_end && ok; ++w, ++item_n) {
                 const dsa_v32_work_info wi = p.works[w];
                 const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
                 if (!mbar_wait(smem_u32(&ctl->q_full), item_n & 1, abort_flag)) { ok = false; break; }
-                if (S > 1) issue_qk(it_base, n_tiles == 1);
+                issue_qk(it_base, n_tiles == 1);
                 for (int t = 0; t < n_tiles && ok; ++t) {
-                    if (S > 1) {
-                        if (t + 1 < n_tiles) issue_qk(it_base + t + 1, t + 2 == n_tiles);
-                    } else {
-                        issue_qk(it_base + t, t + 1 == n_tiles);
-                    }
+                    if (t + 1 < n_tiles) issue_qk(it_base + t + 1, t + 2 == n_tiles);
                     if (ok) issue_pv(it_base + t, t == 0);
                 }
                 it_base += n_tiles;
@@ -298,49 +320,85 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         __syncwarp();
     } else if (warp < 4) {
         // ============================================================ softmax + epilogue
-        constexpr int S = C::kKvStages;
-        constexpr int SB = kFp8 ? 1 : 2;
         constexpr uint32_t kColP = col_p<kFp8>();
         const int row = tid;  // head row inside the block == TMEM lane
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+        const uint32_t peer_x = map_to_cta(smem_u32(sX), peer);
+        const uint32_t peer_xfull = map_to_cta(smem_u32(&ctl->x_full[0]), peer);
         uint32_t it = 0;
+        float part[32];  // this CTA's partial scores of the tile whose exchange is in flight
+
+        // partial scores of tile `jt`: TMEM -> registers -> the peer's exchange buffer
+        auto fetch_send = [&](uint32_t jt) -> bool {
+            const int sb = jt & 1;
+            if (kFp8)
+                if (!warp_wait(smem_u32(&ctl->kv_full[jt % S]), (jt / S) & 1, abort_flag)) return false;
+            if (!warp_wait(smem_u32(&ctl->s_full[sb]), (jt >> 1) & 1, abort_flag)) return false;
+            tc_fence_after();
+            const uint32_t s0 = lane_base + kColS + sb * s_stride<kFp8>();
+            uint32_t sr[32];
+            if (kFp8) {
+                const float(*sc)[2] = ctl->row_scale[jt & 1];
+                tmem_ld32(s0, sr);
+                tmem_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) part[j] = sc[j][0] * __uint_as_float(sr[j]);
+                tmem_ld32(s0 + 32, sr);
+                tmem_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) part[j] = fmaf(sc[j][1], __uint_as_float(sr[j]), part[j]);
+                if (half) {
+                    tmem_ld32(s0 + 64, sr);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) part[j] += __uint_as_float(sr[j]);
+                }
+            } else {
+                tmem_ld32(s0, sr);
+                tmem_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) part[j] = __uint_as_float(sr[j]);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[sb]));
+            // layout of an exchange buffer: [8 chunks of 4 columns][128 rows][16 bytes]
+            const uint32_t dst = peer_x + sb * kXbufBytes + row * 16;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                st_cluster_f32x4(dst + c * (kHeadsPerBlock * 16), part[4 * c], part[4 * c + 1], part[4 * c + 2], part[4 * c + 3]);
+            mbar_arrive_cluster(peer_xfull + sb * 8);
+            return true;
+        };
+
         for (int w = w_begin; w < w_end; ++w) {
             const dsa_v32_work_info wi = p.works[w];
             const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
             float m_ref = -INFINITY;  // running reference maximum, log2 domain
             float l = 0.0f;
+            if (!fetch_send(it)) goto done;
             for (int t = 0; t < n_tiles; ++t, ++it) {
-                const int sb = it % SB;
-                if (!mbar_wait(smem_u32(&ctl->kv_full[it % S]), (it / S) & 1, abort_flag)) goto done;
-                const uint32_t mask = ctl->tile_mask[it & 3];
-                if (!mbar_wait(smem_u32(&ctl->s_full[sb]), (it / SB) & 1, abort_flag)) goto done;
-                tc_fence_after();
+                const int sb = it & 1;
+                // ---- full scores of tile `it` = own partial + the peer's
+                if (!warp_wait_cluster(smem_u32(&ctl->x_full[sb]), (it >> 1) & 1, abort_flag)) goto done;
                 float tv[32];
-                if (kFp8) {
-                    // s = sum_g scale[row][g] * S_g + S_rope : the cache values went through the MMA
-                    // unscaled (e4m3 is exact in bf16), so nothing is rounded before this point
-                    uint32_t sr[32];
-                    tmem_ld32(lane_base + kColS + 4 * 32, sr);
-                    tmem_wait_ld();
+                {
+                    const float4* src = reinterpret_cast<const float4*>(sX + sb * kXbufBytes + row * 16);
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) tv[j] = __uint_as_float(sr[j]);
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        tmem_ld32(lane_base + kColS + g * 32, sr);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) tv[j] = fmaf(ctl->row_scale[it & 1][j][g], __uint_as_float(sr[j]), tv[j]);
+                    for (int c = 0; c < 8; ++c) {
+                        const float4 o = src[c * kHeadsPerBlock];
+                        tv[4 * c + 0] = part[4 * c + 0] + o.x;
+                        tv[4 * c + 1] = part[4 * c + 1] + o.y;
+                        tv[4 * c + 2] = part[4 * c + 2] + o.z;
+                        tv[4 * c + 3] = part[4 * c + 3] + o.w;
                     }
-                } else {
-                    uint32_t sr[32];
-                    tmem_ld32(lane_base + kColS + sb * 32, sr);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) tv[j] = __uint_as_float(sr[j]);
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[sb]));
+                // ---- start the exchange of the next tile before the arithmetic of this one
+                if (t + 1 < n_tiles)
+                    if (!fetch_send(it + 1)) goto done;
+                if (!kFp8)
+                    if (!warp_wait(smem_u32(&ctl->kv_full[it % S]), (it / S) & 1, abort_flag)) goto done;
+                const uint32_t mask = ctl->tile_mask[it % kMaskSlots];
 
                 float mt = -INFINITY;
 #pragma unroll
@@ -358,7 +416,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         l *= f;
                         // O of this item so far is complete once the previous PV has finished
                         const uint32_t pit = it - 1;
-                        if (!mbar_wait(smem_u32(&ctl->pv_done[pit & 1]), (pit >> 1) & 1, abort_flag)) goto done;
+                        if (!warp_wait(smem_u32(&ctl->pv_done[pit & 1]), (pit >> 1) & 1, abort_flag)) goto done;
                         tc_fence_after();
 #pragma unroll 1
                         for (int c0 = 0; c0 < kDvHalf; c0 += 32) {
@@ -376,20 +434,18 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
                 float lsum = 0.0f;
                 if (kFp8) {
+                    const float(*sc)[2] = ctl->row_scale[it & 1];
                     uint32_t pk0[16], pk1[16];
-                    const int g0 = 2 * half;
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const float p0 = ex2_approx(tv[2 * j] - m_use);
                         const float p1 = ex2_approx(tv[2 * j + 1] - m_use);
                         lsum += p0 + p1;
-                        const float* sc0 = ctl->row_scale[it & 1][2 * j];
-                        const float* sc1 = ctl->row_scale[it & 1][2 * j + 1];
-                        pk0[j] = pack_bf16x2(p0 * sc0[g0], p1 * sc1[g0]);
-                        pk1[j] = pack_bf16x2(p0 * sc0[g0 + 1], p1 * sc1[g0 + 1]);
+                        pk0[j] = pack_bf16x2(p0 * sc[2 * j][0], p1 * sc[2 * j + 1][0]);
+                        pk1[j] = pack_bf16x2(p0 * sc[2 * j][1], p1 * sc[2 * j + 1][1]);
                     }
-                    tmem_st16(lane_base + kColP, pk0);
-                    tmem_st16(lane_base + kColP + 16, pk1);
+                    tmem_st16(lane_base + kColP + sb * 32, pk0);
+                    tmem_st16(lane_base + kColP + sb * 32 + 16, pk1);
                 } else {
                     uint32_t pk[16];
 #pragma unroll
@@ -410,7 +466,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             // ---- epilogue of the item
             {
                 const uint32_t pit = it - 1;
-                if (!mbar_wait(smem_u32(&ctl->pv_done[pit & 1]), (pit >> 1) & 1, abort_flag)) goto done;
+                if (!warp_wait(smem_u32(&ctl->pv_done[pit & 1]), (pit >> 1) & 1, abort_flag)) goto done;
                 tc_fence_after();
                 const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
                 const int head = wi.head_block * kHeadsPerBlock + row;
@@ -460,30 +516,29 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
         }
     } else if (kFp8) {
-        // ============================================================ dequantise (warps 6-9)
+        // ============================================================ convert (warps 6-9)
         const int dt = tid - 192;        // 0..127
         const int r = dt >> 2;           // tile row 0..31
-        const int qd = dt & 3;           // which 128-value scale group of the row
-        const int dwarp_lane0 = (lane == 0);
+        const int qd = dt & 3;           // which 64 of this CTA's 256 latent columns
         uint32_t it = 0;
         for (int w = w_begin; w < w_end; ++w) {
             const dsa_v32_work_info wi = p.works[w];
             const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
             for (int t = 0; t < n_tiles; ++t, ++it) {
-                const int rs = it & 1;
-                if (!mbar_wait(smem_u32(&ctl->raw_full[rs]), (it >> 1) & 1, abort_flag)) goto done;
-                if (!mbar_wait(smem_u32(&ctl->kv_empty[0]), (it & 1) ^ 1, abort_flag)) goto done;
+                const int rs = it % R, s = it % S;
+                if (!warp_wait(smem_u32(&ctl->raw_full[rs]), (it / R) & 1, abort_flag)) goto done;
+                if (!warp_wait(smem_u32(&ctl->kv_empty[s]), ((it / S) & 1) ^ 1, abort_flag)) goto done;
                 const uint8_t* grp = sRaw + rs * kRawTileBytes + (r >> 2) * kRawGroupBytes;
                 const int ri = r & 3;
-                const uint8_t* src = grp + (qd >> 1) * 1024 + ri * 256 + (qd & 1) * 128;
-                const uint8_t* tail = grp + 2048 + ri * 144;
-                // values go to the MMA unscaled (every e4m3 value is exact in bf16); the row's scales
-                // are applied to the fp32 scores and to P by the softmax warps
-                ctl->row_scale[it & 1][r][qd] = reinterpret_cast<const float*>(tail)[qd];
-                uint8_t* dst_row = sKV + r * 128;
+                const uint8_t* src = grp + ri * 256 + qd * 64;
+                const uint8_t* tail = grp + 1024 + ri * 144;
+                // the row's scales are applied to the fp32 scores and to P by the softmax warps
+                if ((qd & 1) == 0)
+                    ctl->row_scale[it & 1][r][qd >> 1] = reinterpret_cast<const float*>(tail)[2 * half + (qd >> 1)];
+                uint8_t* dst_row = sKV + s * kKvTileBytes + qd * kKvBlockBytes + r * 128;
 #pragma unroll
-                for (int cc = 0; cc < 8; ++cc) {
-                    const int c = (cc + r) & 7;  // rotate so the 8 rows of a warp hit different banks
+                for (int cc = 0; cc < 4; ++cc) {
+                    const int c = (cc + r) & 3;  // rotate so the rows of a warp hit different banks
                     const uint4 raw = *reinterpret_cast<const uint4*>(src + c * 16);
                     const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
                     uint32_t o[8];
@@ -493,31 +548,27 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         const uint16_t lo16 = (uint16_t)(wv[k] & 0xFFFFu), hi16 = (uint16_t)(wv[k] >> 16);
                         asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h01) : "h"(lo16));
                         asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h23) : "h"(hi16));
-                        const __half2 a = *reinterpret_cast<const __half2*>(&h01);
-                        const __half2 b = *reinterpret_cast<const __half2*>(&h23);
-                        const float2 fa = __half22float2(a), fb = __half22float2(b);
+                        const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&h01));
+                        const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&h23));
                         o[2 * k + 0] = pack_bf16x2(fa.x, fa.y);
                         o[2 * k + 1] = pack_bf16x2(fb.x, fb.y);
                     }
-                    // 16 fp8 -> 16 bf16 = two 16-byte chunks of the 64-column block (2*qd + c/4)
-                    const int kb = 2 * qd + (c >> 2);
-                    const int ch = (c & 3) * 2;
-                    uint8_t* d = dst_row + kb * kKvBlockBytes;
-                    *reinterpret_cast<uint4*>(d + (((ch + 0) ^ (r & 7)) * 16)) = make_uint4(o[0], o[1], o[2], o[3]);
-                    *reinterpret_cast<uint4*>(d + (((ch + 1) ^ (r & 7)) * 16)) = make_uint4(o[4], o[5], o[6], o[7]);
+                    // 16 bytes -> 16 bf16 = chunks 2c, 2c+1 of this thread's 128-byte block row
+                    *reinterpret_cast<uint4*>(dst_row + (((2 * c + 0) ^ (r & 7)) * 16)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    *reinterpret_cast<uint4*>(dst_row + (((2 * c + 1) ^ (r & 7)) * 16)) = make_uint4(o[4], o[5], o[6], o[7]);
                 }
-                // rope: 64 bf16 = 8 chunks; this thread copies chunks 2*qd, 2*qd+1 into block 8
-                {
+                if (half) {
+                    // rope: 64 bf16 = 8 chunks into block 4; this thread copies chunks 2*qd, 2*qd+1
                     const uint4 a = *reinterpret_cast<const uint4*>(tail + 16 + (2 * qd + 0) * 16);
                     const uint4 b = *reinterpret_cast<const uint4*>(tail + 16 + (2 * qd + 1) * 16);
-                    uint8_t* d = dst_row + 8 * kKvBlockBytes;
+                    uint8_t* d = sKV + s * kKvTileBytes + 4 * kKvBlockBytes + r * 128;
                     *reinterpret_cast<uint4*>(d + (((2 * qd + 0) ^ (r & 7)) * 16)) = a;
                     *reinterpret_cast<uint4*>(d + (((2 * qd + 1) ^ (r & 7)) * 16)) = b;
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
-                if (dwarp_lane0) {
-                    mbar_arrive(smem_u32(&ctl->kv_full[0]));
+                if (lane == 0) {
+                    mbar_arrive(smem_u32(&ctl->kv_full[s]));
                     mbar_arrive(smem_u32(&ctl->raw_empty[rs]));
                 }
             }
@@ -525,9 +576,11 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
 
 done:
+    if (ctl->abort_flag) st_cluster_u32(peer_abort, 1u);   // let the peer stop waiting for us
     tc_fence_before();
     __syncthreads();
     if (tid == 0 && ctl->abort_flag) atomicExch(p.status, DSA_V32_ERR_DEVICE_WAIT);
+    cluster_sync_all();   // nobody leaves while the peer may still store into this CTA's shared memory
     if (warp == 5) {
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
@@ -617,28 +670,62 @@ __global__ void __launch_bounds__(256) pack_fp8_rows_kernel(const float* __restr
 }
 
 // ------------------------------------------------------------------ launch helpers (called from capi.cu)
-int smem_bytes_attn(bool fp8) { return fp8 ? Cfg<true>::kSmemBytes : Cfg<false>::kSmemBytes; }
+template <bool kFp8>
+static cudaError_t configure() {
+    static bool done = false;
+    if (done) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(sparse_mla_kernel<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg<kFp8>::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    done = true;
+    return cudaSuccess;
+}
+
+template <bool kFp8>
+static void fill_launch(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, int num_lists, cudaStream_t stream) {
+    cfg->gridDim = dim3(2 * num_lists, 1, 1);
+    cfg->blockDim = dim3(Cfg<kFp8>::kThreads, 1, 1);
+    cfg->dynamicSmemBytes = Cfg<kFp8>::kSmemBytes;
+    cfg->stream = stream;
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg->attrs = attr;
+    cfg->numAttrs = 1;
+}
+
+// How many CTA pairs the device can keep resident at once (one work list per pair).
+int max_resident_pairs(bool fp8, int* out) {
+    cudaError_t e = fp8 ? configure<true>() : configure<false>();
+    if (e != cudaSuccess) return (int)e;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    int n = 0;
+    if (fp8) {
+        fill_launch<true>(&cfg, attr, 1, nullptr);
+        e = cudaOccupancyMaxActiveClusters(&n, sparse_mla_kernel<true>, &cfg);
+    } else {
+        fill_launch<false>(&cfg, attr, 1, nullptr);
+        e = cudaOccupancyMaxActiveClusters(&n, sparse_mla_kernel<false>, &cfg);
+    }
+    if (e != cudaSuccess) return (int)e;
+    *out = n;
+    return 0;
+}
 
 cudaError_t launch_attn(bool fp8, int num_lists, const CUtensorMap& tq, const CUtensorMap& tkv, const CUtensorMap& ttail,
                         const AttnParams& p, cudaStream_t stream) {
-    static bool configured[2] = {false, false};
-    cudaError_t e;
+    cudaError_t e = fp8 ? configure<true>() : configure<false>();
+    if (e != cudaSuccess) return e;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
     if (fp8) {
-        if (!configured[1]) {
-            e = cudaFuncSetAttribute(sparse_mla_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<true>::kSmemBytes);
-            if (e != cudaSuccess) return e;
-            configured[1] = true;
-        }
-        sparse_mla_kernel<true><<<2 * num_lists, Cfg<true>::kThreads, Cfg<true>::kSmemBytes, stream>>>(tq, tkv, ttail, p);
-    } else {
-        if (!configured[0]) {
-            e = cudaFuncSetAttribute(sparse_mla_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<false>::kSmemBytes);
-            if (e != cudaSuccess) return e;
-            configured[0] = true;
-        }
-        sparse_mla_kernel<false><<<2 * num_lists, Cfg<false>::kThreads, Cfg<false>::kSmemBytes, stream>>>(tq, tkv, ttail, p);
+        fill_launch<true>(&cfg, attr, num_lists, stream);
+        return cudaLaunchKernelEx(&cfg, sparse_mla_kernel<true>, tq, tkv, ttail, p);
     }
-    return cudaGetLastError();
+    fill_launch<false>(&cfg, attr, num_lists, stream);
+    return cudaLaunchKernelEx(&cfg, sparse_mla_kernel<false>, tq, tkv, ttail, p);
 }
 
 cudaError_t launch_combine(const float* o_accum, const float* lse_accum, const int32_t* reduce_indptr,

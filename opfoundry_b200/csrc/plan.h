@@ -49,11 +49,11 @@ inline int build_plan(const dsa_v32_shape& sh, int num_sms, HostPlan& P) {
     };
     auto unit_tiles = [&](int64_t u) -> int { return std::max(1, (unit_len(u) + kTileRows - 1) / kTileRows); };
 
-    int64_t total_cost = 0;
-    for (int64_t u = 0; u < n_units; ++u) total_cost += unit_tiles(u) + kPieceOverheadTiles;
-    // a list always has room for at least one minimum-length piece, so small batches still spread
-    const int64_t payload =
-        std::max<int64_t>((total_cost + L - 1) / L, kMinPieceTiles) + kPieceOverheadTiles;
+    // Cost of a piece = its tile steps + a fixed overhead.  Every list is given an equal share of
+    // what is still to be handed out (recomputed list by list, so rounding and the overhead added by
+    // cuts never pile up in the last list).
+    int64_t tiles_left = 0;
+    for (int64_t u = 0; u < n_units; ++u) tiles_left += unit_tiles(u);
 
     P.list_indptr.assign(L + 1, 0);
     P.works.clear();
@@ -102,29 +102,34 @@ inline int build_plan(const dsa_v32_shape& sh, int num_sms, HostPlan& P) {
     };
 
     for (int list = 0; list < L; ++list) {
-        int64_t remain = payload;
         const bool last_list = (list == L - 1);
+        const double left = double(tiles_left) + double(n_units - u) * kPieceOverheadTiles;
+        const double budget = left / double(L - list);
+        double used = 0.0;
         while (u < n_units) {
             const int tiles = unit_tiles(u);
             const int rem_tiles = tiles - cur_tile;
-            if (last_list || remain >= rem_tiles + kPieceOverheadTiles) {
+            const int piece_cost = rem_tiles + kPieceOverheadTiles;
+            if (last_list || used + piece_cost <= budget + 0.5) {
                 emit(cur_tile, tiles, true);
-                remain -= rem_tiles + kPieceOverheadTiles;
-            } else {
-                // cut the unit here, keeping both sides at least kMinPieceTiles long
-                int take = std::min(int(remain) - kPieceOverheadTiles, rem_tiles - kMinPieceTiles);
-                if (take >= kMinPieceTiles) {
-                    emit(cur_tile, cur_tile + take, false);
-                    break;
-                }
-                // too short to cut: take it whole if at least half of it fits, else leave it
-                if (2 * remain >= rem_tiles + kPieceOverheadTiles) {
-                    emit(cur_tile, tiles, true);
-                    remain -= rem_tiles + kPieceOverheadTiles;
-                    continue;
-                }
+                used += piece_cost;
+                tiles_left -= rem_tiles;
+                continue;
+            }
+            // the share ends inside this unit: cut it, keeping both sides at least kMinPieceTiles long
+            const int room = int(budget - used + 0.5) - kPieceOverheadTiles;
+            const int take = std::min(room, rem_tiles - kMinPieceTiles);
+            if (take >= kMinPieceTiles) {
+                emit(cur_tile, cur_tile + take, false);
+                tiles_left -= take;
                 break;
             }
+            // too short to cut: take it whole when more than half of it belongs here, else leave it
+            if (2.0 * (budget - used) >= double(piece_cost)) {
+                emit(cur_tile, tiles, true);
+                tiles_left -= rem_tiles;
+            }
+            break;
         }
         P.list_indptr[list + 1] = int(P.works.size());
     }

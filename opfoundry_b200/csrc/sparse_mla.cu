@@ -48,6 +48,20 @@
 
 namespace dsa {
 
+#ifdef DSA_PROFILE
+// Working aid (never compiled into the shipped library): per-role time stamps of the first tiles of
+// cluster 0, to see which stage of the pipeline the others wait for.
+__device__ long long* g_prof = nullptr;
+#define PROF(role, tile, slot)                                                                      \
+    do {                                                                                            \
+        if (g_prof != nullptr && blockIdx.x < 2 && (tile) < 64 && lane == 0)                        \
+            g_prof[((blockIdx.x * 8 + (role)) * 64 + (tile)) * 4 + (slot)] = clock64();             \
+    } while (0)
+extern "C" int dsa_v32_set_prof(long long* buf) { return (int)cudaMemcpyToSymbol(g_prof, &buf, sizeof(buf)); }
+#else
+#define PROF(role, tile, slot) do { } while (0)
+#endif
+
 // ------------------------------------------------------------------ shared-memory map
 constexpr int kMaxKBlocks = 5;                            // 64-column blocks per CTA: 4 (CTA 0) or 5 (CTA 1)
 constexpr int kQBlockBytes = kHeadsPerBlock * 128;        // 16384
@@ -62,8 +76,8 @@ constexpr int kMaskSlots = 16;
 
 template <bool kFp8>
 struct Cfg {
-    static constexpr int kKvStages = kFp8 ? 2 : 5;   // MMA-ready bf16 tiles
-    static constexpr int kRawStages = kFp8 ? 5 : 0;  // raw fp8 tiles in flight
+    static constexpr int kKvStages = kFp8 ? 3 : 5;   // MMA-ready bf16 tiles
+    static constexpr int kRawStages = kFp8 ? 3 : 0;  // raw fp8 tiles in flight
     static constexpr int kThreads = kFp8 ? 320 : 192;
     static constexpr int kOffKv = kQBytesMax;
     static constexpr int kOffRaw = kOffKv + kKvStages * kKvTileBytes;
@@ -74,7 +88,7 @@ struct Cfg {
 };
 
 struct Ctl {
-    float row_scale[2][kTileRows][2];  // fp8 cache: the two scales (this CTA's groups) of every tile row
+    float row_scale[4][kTileRows][2];  // fp8 cache: the two scales (this CTA's groups) of every tile row
     uint64_t q_full, q_empty, o_free;
     uint64_t kv_full[8], kv_empty[8];
     uint64_t raw_full[8], raw_empty[8];
@@ -97,21 +111,30 @@ template <bool kFp8> __host__ __device__ constexpr uint32_t s_stride() { return 
 template <bool kFp8> __host__ __device__ constexpr uint32_t col_p() { return kColS + 2 * s_stride<kFp8>(); }
 
 // ------------------------------------------------------------------ index translation
-// Top-k slot value -> physical cache row, or -1 when the slot is padding / unusable.
-__device__ __forceinline__ int translate_row(int idx, int seq, const AttnParams& p) {
+// Top-k slot value -> physical cache row, or -1 when the slot is padding / unusable.  Split in two so
+// the producer can issue the block-table load of one tile and finish the arithmetic tiles later:
+//   block_of(idx)        issues the block-table load (0 when there is nothing to load)
+//   row_of(idx, phys)    the physical row from the loaded block number
+__device__ __forceinline__ int block_of(int idx, int seq, const AttnParams& p) {
+    if (idx < 0 || p.block_table == nullptr) return 0;
+    const int blk = idx / p.page_block_size;
+    if (blk >= p.block_table_stride) return -1;
+    return __ldg(p.block_table + (size_t)seq * p.block_table_stride + blk);
+}
+__device__ __forceinline__ int row_of(int idx, int phys, int seq, const AttnParams& p) {
     if (idx < 0) return -1;
     long long row;
     if (p.block_table != nullptr) {
-        const int blk = idx / p.page_block_size;
-        if (blk >= p.block_table_stride) return -1;
-        const int phys = __ldg(p.block_table + (size_t)seq * p.block_table_stride + blk);
         if (phys < 0) return -1;
-        row = (long long)phys * p.page_block_size + (idx - blk * p.page_block_size);
+        row = (long long)phys * p.page_block_size + (idx % p.page_block_size);
     } else {
         row = (long long)seq * p.kv_batch_stride_rows + idx;
     }
     if (row < 0 || row >= p.num_kv_rows) return -1;
     return (int)row;
+}
+__device__ __forceinline__ int translate_row(int idx, int seq, const AttnParams& p) {
+    return row_of(idx, block_of(idx, seq, p), seq, p);
 }
 
 __global__ void debug_rows_kernel(AttnParams p, int total_q, int32_t* rows_out) {
@@ -119,6 +142,57 @@ __global__ void debug_rows_kernel(AttnParams p, int total_q, int32_t* rows_out) 
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
         const int q = (int)(i / p.topk);
         rows_out[i] = translate_row(__ldg(p.indices + i), q / p.s_q, p);
+    }
+}
+
+// ------------------------------------------------------------------ e4m3 -> bf16, exact, two at a time
+// Input: the two e4m3 bytes in the high byte of each 16-bit half.  Moving the 7 magnitude bits down
+// by 4 puts the 4 exponent bits and 3 mantissa bits where bf16 keeps them; read as bf16 that number
+// is the e4m3 value times 2^-120 (normal and subnormal codes alike), so one exact multiply by 2^120
+// finishes the conversion without going through the conversion unit.  (0x7F, the e4m3 NaN, becomes
+// 480 instead of NaN; a cache row that is never selected is never converted.)
+__device__ __forceinline__ uint32_t e4m3x2_to_bf16x2(uint32_t hi_bytes) {
+    const uint32_t y = (hi_bytes & 0x80008000u) | ((hi_bytes >> 4) & 0x07F007F0u);
+    uint32_t z;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(z) : "r"(y), "r"(0x7B807B80u));
+    return z;
+}
+
+// ------------------------------------------------------------------ MMA issue (whole warp converged)
+// S_c (+)= Q_c K_c^T for one 32-row tile: NKB blocks of 64 columns, four K=16 steps each.  With an fp8
+// cache every scale group (two blocks) and the rope block get their own accumulator.
+template <bool kFp8, int NKB>
+__device__ __forceinline__ void issue_qk_mmas(uint32_t d0, uint64_t q_desc, uint64_t k_desc, uint32_t el) {
+    constexpr uint32_t idesc = make_idesc_bf16(kHeadsPerBlock, kTileRows, false);
+#pragma unroll
+    for (int kb = 0; kb < NKB; ++kb) {
+#pragma unroll
+        for (int kin = 0; kin < 4; ++kin) {
+            const uint64_t a = q_desc + static_cast<uint64_t>((kb * kQBlockBytes + kin * 32) >> 4);
+            const uint64_t b = k_desc + static_cast<uint64_t>((kb * kKvBlockBytes + kin * 32) >> 4);
+            if (kFp8) umma_ss_el(d0 + (kb >> 1) * 32, a, b, idesc, ((kb & 1) | kin) ? 1u : 0u, el);
+            else umma_ss_el(d0, a, b, idesc, (kb | kin) ? 1u : 0u, el);
+        }
+    }
+}
+
+// O_c (+)= P V_c for one 32-row tile: two K=16 steps; V_c is the first 256 columns of the tile seen
+// MN-major.  fp8 cache: two scaled copies of P, each for its own 128 output columns.
+template <bool kFp8>
+__device__ __forceinline__ void issue_pv_mmas(uint32_t o_tmem, uint32_t p_tmem, uint64_t v_desc, bool overwrite, uint32_t el) {
+    constexpr uint32_t idesc256 = make_idesc_bf16(kHeadsPerBlock, kDvHalf, true);
+    constexpr uint32_t idesc128 = make_idesc_bf16(kHeadsPerBlock, 128, true);
+#pragma unroll
+    for (int ks = 0; ks < kTileRows / 16; ++ks) {
+        const uint32_t acc = (overwrite && ks == 0) ? 0u : 1u;
+        if (kFp8) {
+#pragma unroll
+            for (int v2 = 0; v2 < 2; ++v2)
+                umma_ts_el(o_tmem + v2 * 128, p_tmem + v2 * 16 + ks * 8,
+                           v_desc + static_cast<uint64_t>((v2 * 2 * kKvBlockBytes + ks * 2048) >> 4), idesc128, acc, el);
+        } else {
+            umma_ts_el(o_tmem, p_tmem + ks * 8, v_desc + static_cast<uint64_t>((ks * 2048) >> 4), idesc256, acc, el);
+        }
     }
 }
 
@@ -167,10 +241,12 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             mbar_init(smem_u32(&ctl->s_empty[i]), 4);
             mbar_init(smem_u32(&ctl->p_full[i]), 4);
             mbar_init(smem_u32(&ctl->pv_done[i]), 1);
-            mbar_init(smem_u32(&ctl->x_full[i]), kHeadsPerBlock);
+            mbar_init(smem_u32(&ctl->x_full[i]), 1);
         }
         ctl->abort_flag = 0;
         fence_mbar_init();
+        // the exchange barriers count bytes: armed here for tiles 0 and 1, re-armed by the softmax warps
+        for (int i = 0; i < 2; ++i) mbar_arrive_expect_tx(smem_u32(&ctl->x_full[i]), kXbufBytes);
     }
     if (warp == 5) {
         tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
@@ -205,10 +281,24 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                                 wi.head_block * kHeadsPerBlock, wi.q_row);
             }
             const int32_t* idx_row = p.indices + (size_t)wi.q_row * p.topk;
-            for (int k0 = wi.k_begin; k0 < wi.k_end; k0 += kTileRows, ++it) {
+            // Two-deep software pipeline over tiles so no load is consumed in the iteration that issues
+            // it: slots of tiles t+2, t+3 are in flight, block numbers of tiles t, t+1 are in flight.
+            auto load_slot = [&](int k0) -> int {
                 const int k = k0 + lane;
-                const int idx = (k < wi.k_end) ? __ldg(idx_row + k) : -1;
-                const int row = translate_row(idx, seq, p);
+                return (k < wi.k_end) ? __ldg(idx_row + k) : -1;
+            };
+            int idx_a = load_slot(wi.k_begin), idx_b = load_slot(wi.k_begin + kTileRows);
+            int idx_c = load_slot(wi.k_begin + 2 * kTileRows), idx_d = load_slot(wi.k_begin + 3 * kTileRows);
+            int phys_a = block_of(idx_a, seq, p), phys_b = block_of(idx_b, seq, p);
+            for (int k0 = wi.k_begin; k0 < wi.k_end; k0 += kTileRows, ++it) {
+                const int row = row_of(idx_a, phys_a, seq, p);
+                {
+                    const int phys_n = block_of(idx_c, seq, p);
+                    const int idx_n = load_slot(k0 + 4 * kTileRows);
+                    idx_a = idx_b; phys_a = phys_b;
+                    idx_b = idx_c; phys_b = phys_n;
+                    idx_c = idx_d; idx_d = idx_n;
+                }
                 const uint32_t mask = __ballot_sync(0xffffffffu, row >= 0);
                 const int coord = row >= 0 ? row : oob_row;
                 const int g = lane & 7;
@@ -245,79 +335,63 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         tma_gather4(dst + 1024, &tm_kv_tail, bar, 512, r0, r1, r2, r3);  // scales + rope
                     }
                 }
+                PROF(0, it, 0);
             }
         }
     } else if (warp == 5) {
-        // ============================================================ MMA issuer (one lane)
-        if (lane == 0) {
-            constexpr uint32_t idesc_qk = make_idesc_bf16(kHeadsPerBlock, kTileRows, false);
-            constexpr uint32_t idesc_pv = make_idesc_bf16(kHeadsPerBlock, kDvHalf, true);
-            constexpr uint32_t idesc_pv128 = make_idesc_bf16(kHeadsPerBlock, 128, true);
+        // ============================================================ MMA issuer
+        // The whole warp runs the loop converged (descriptors stay warp-uniform); one elected lane issues.
+        {
             constexpr uint32_t kColP = col_p<kFp8>();
+            constexpr uint32_t kPStride = kFp8 ? 32 : 16;
+            const uint32_t el = elect_one() ? 1u : 0u;
+            const uint64_t q_desc = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);
+            const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(sKV), 16, 1024);            // K-major view
+            const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(sKV), kKvBlockBytes, 1024); // MN-major view
             uint32_t it_base = 0;
             int item_n = 0;
             bool ok = true;
             auto issue_qk = [&](uint32_t it, bool last_of_item) {
                 const int s = it % S, sb = it & 1;
-                if (!mbar_wait(smem_u32(&ctl->kv_full[s]), (it / S) & 1, abort_flag)) { ok = false; return; }
-                if (!mbar_wait(smem_u32(&ctl->s_empty[sb]), ((it >> 1) & 1) ^ 1, abort_flag)) { ok = false; return; }
+                if (!warp_wait(smem_u32(&ctl->kv_full[s]), (it / S) & 1, abort_flag)) { ok = false; return; }
+                if (!warp_wait(smem_u32(&ctl->s_empty[sb]), ((it >> 1) & 1) ^ 1, abort_flag)) { ok = false; return; }
                 tc_fence_after();
-                const uint32_t kv = smem_u32(sKV + s * kKvTileBytes);
-                const uint32_t q = smem_u32(sQ);
+                PROF(1, it, 0);
+                const uint64_t k_desc = k_desc0 + static_cast<uint64_t>((s * kKvTileBytes) >> 4);
                 const uint32_t d0 = tmem + kColS + sb * s_stride<kFp8>();
-                for (int kb = 0; kb < nkb; ++kb) {
-#pragma unroll
-                    for (int kin = 0; kin < 4; ++kin) {
-                        const uint64_t a = make_smem_desc_sw128(q + kb * kQBlockBytes + kin * 32, 16, 1024);
-                        const uint64_t b = make_smem_desc_sw128(kv + kb * kKvBlockBytes + kin * 32, 16, 1024);
-                        if (kFp8) {
-                            // one accumulator per scale group (two 64-column blocks each), one for rope
-                            umma_ss(d0 + (kb >> 1) * 32, a, b, idesc_qk, ((kb & 1) | kin) ? 1u : 0u);
-                        } else {
-                            umma_ss(d0, a, b, idesc_qk, (kb | kin) ? 1u : 0u);
-                        }
-                    }
-                }
-                tc_commit(smem_u32(&ctl->s_full[sb]));
-                if (last_of_item) tc_commit(smem_u32(&ctl->q_empty));
+                if (half) issue_qk_mmas<kFp8, 5>(d0, q_desc, k_desc, el);
+                else issue_qk_mmas<kFp8, 4>(d0, q_desc, k_desc, el);
+                tc_commit_el(smem_u32(&ctl->s_full[sb]), el);
+                if (last_of_item) tc_commit_el(smem_u32(&ctl->q_empty), el);
+                PROF(1, it, 1);
             };
             auto issue_pv = [&](uint32_t it, bool first_of_item) {
                 const int s = it % S, sb = it & 1;
-                if (!mbar_wait(smem_u32(&ctl->p_full[sb]), (it >> 1) & 1, abort_flag)) { ok = false; return; }
+                if (!warp_wait(smem_u32(&ctl->p_full[sb]), (it >> 1) & 1, abort_flag)) { ok = false; return; }
                 if (first_of_item && item_n > 0)
-                    if (!mbar_wait(smem_u32(&ctl->o_free), (item_n - 1) & 1, abort_flag)) { ok = false; return; }
+                    if (!warp_wait(smem_u32(&ctl->o_free), (item_n - 1) & 1, abort_flag)) { ok = false; return; }
                 tc_fence_after();
-                const uint32_t v = smem_u32(sKV + s * kKvTileBytes);   // V = first 256 columns of the slice
-#pragma unroll
-                for (int ks = 0; ks < kTileRows / 16; ++ks) {
-                    const uint32_t acc = (first_of_item && ks == 0) ? 0u : 1u;
-                    if (kFp8) {
-#pragma unroll
-                        for (int v2 = 0; v2 < 2; ++v2) {
-                            const uint64_t b = make_smem_desc_sw128(v + v2 * 2 * kKvBlockBytes + ks * 2048, kKvBlockBytes, 1024);
-                            umma_ts(tmem + kColO + v2 * 128, tmem + kColP + sb * 32 + v2 * 16 + ks * 8, b, idesc_pv128, acc);
-                        }
-                    } else {
-                        const uint64_t b = make_smem_desc_sw128(v + ks * 2048, kKvBlockBytes, 1024);
-                        umma_ts(tmem + kColO, tmem + kColP + sb * 16 + ks * 8, b, idesc_pv, acc);
-                    }
-                }
-                tc_commit(smem_u32(&ctl->kv_empty[s]));
-                tc_commit(smem_u32(&ctl->pv_done[sb]));
+                PROF(1, it, 2);
+                issue_pv_mmas<kFp8>(tmem + kColO, tmem + kColP + sb * kPStride,
+                                    v_desc0 + static_cast<uint64_t>((s * kKvTileBytes) >> 4), first_of_item, el);
+                tc_commit_el(smem_u32(&ctl->kv_empty[s]), el);
+                tc_commit_el(smem_u32(&ctl->pv_done[sb]), el);
+                PROF(1, it, 3);
             };
             for (int w = w_begin; w < w_end && ok; ++w, ++item_n) {
                 const dsa_v32_work_info wi = p.works[w];
                 const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
-                if (!mbar_wait(smem_u32(&ctl->q_full), item_n & 1, abort_flag)) { ok = false; break; }
+                if (!warp_wait(smem_u32(&ctl->q_full), item_n & 1, abort_flag)) { ok = false; break; }
+                // scores run two tiles ahead of the P V products
                 issue_qk(it_base, n_tiles == 1);
+                if (ok && n_tiles > 1) issue_qk(it_base + 1, n_tiles == 2);
                 for (int t = 0; t < n_tiles && ok; ++t) {
-                    if (t + 1 < n_tiles) issue_qk(it_base + t + 1, t + 2 == n_tiles);
-                    if (ok) issue_pv(it_base + t, t == 0);
+                    issue_pv(it_base + t, t == 0);
+                    if (ok && t + 2 < n_tiles) issue_qk(it_base + t + 2, t + 3 == n_tiles);
                 }
                 it_base += n_tiles;
             }
         }
-        __syncwarp();
     } else if (warp < 4) {
         // ============================================================ softmax + epilogue
         constexpr uint32_t kColP = col_p<kFp8>();
@@ -335,18 +409,20 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (!warp_wait(smem_u32(&ctl->kv_full[jt % S]), (jt / S) & 1, abort_flag)) return false;
             if (!warp_wait(smem_u32(&ctl->s_full[sb]), (jt >> 1) & 1, abort_flag)) return false;
             tc_fence_after();
+            if (warp == 0) PROF(2, jt, 0);
             const uint32_t s0 = lane_base + kColS + sb * s_stride<kFp8>();
             uint32_t sr[32];
             if (kFp8) {
-                const float(*sc)[2] = ctl->row_scale[jt & 1];
+                const float(*sc)[2] = ctl->row_scale[jt % S];
+                uint32_t sr2[32];
                 tmem_ld32(s0, sr);
+                tmem_ld32(s0 + 32, sr2);
                 tmem_wait_ld();
 #pragma unroll
-                for (int j = 0; j < 32; ++j) part[j] = sc[j][0] * __uint_as_float(sr[j]);
-                tmem_ld32(s0 + 32, sr);
-                tmem_wait_ld();
-#pragma unroll
-                for (int j = 0; j < 32; ++j) part[j] = fmaf(sc[j][1], __uint_as_float(sr[j]), part[j]);
+                for (int j = 0; j < 32; ++j) {
+                    const float2 w2 = *reinterpret_cast<const float2*>(sc[j]);
+                    part[j] = fmaf(w2.y, __uint_as_float(sr2[j]), w2.x * __uint_as_float(sr[j]));
+                }
                 if (half) {
                     tmem_ld32(s0 + 64, sr);
                     tmem_wait_ld();
@@ -362,12 +438,14 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[sb]));
+            if (warp == 0) PROF(4, jt, 0);
             // layout of an exchange buffer: [8 chunks of 4 columns][128 rows][16 bytes]
             const uint32_t dst = peer_x + sb * kXbufBytes + row * 16;
 #pragma unroll
             for (int c = 0; c < 8; ++c)
-                st_cluster_f32x4(dst + c * (kHeadsPerBlock * 16), part[4 * c], part[4 * c + 1], part[4 * c + 2], part[4 * c + 3]);
-            mbar_arrive_cluster(peer_xfull + sb * 8);
+                st_async_f32x4(dst + c * (kHeadsPerBlock * 16), part[4 * c], part[4 * c + 1], part[4 * c + 2], part[4 * c + 3],
+                               peer_xfull + sb * 8);
+            if (warp == 0) PROF(2, jt, 1);
             return true;
         };
 
@@ -381,6 +459,9 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const int sb = it & 1;
                 // ---- full scores of tile `it` = own partial + the peer's
                 if (!warp_wait_cluster(smem_u32(&ctl->x_full[sb]), (it >> 1) & 1, abort_flag)) goto done;
+                if (warp == 0) PROF(2, it, 2);
+                // re-arm this buffer's barrier for the tile that lands in it next (tile it + 2)
+                if (tid == 0) mbar_arrive_expect_tx(smem_u32(&ctl->x_full[sb]), kXbufBytes);
                 float tv[32];
                 {
                     const float4* src = reinterpret_cast<const float4*>(sX + sb * kXbufBytes + row * 16);
@@ -393,9 +474,15 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         tv[4 * c + 3] = part[4 * c + 3] + o.w;
                     }
                 }
-                // ---- start the exchange of the next tile before the arithmetic of this one
-                if (t + 1 < n_tiles)
-                    if (!fetch_send(it + 1)) goto done;
+                // ---- start the exchange of the next tile before the arithmetic of this one when its
+                //      scores are already there; otherwise right after
+                bool next_sent = true;
+                if (t + 1 < n_tiles) {
+                    const uint32_t jt = it + 1;
+                    next_sent = __all_sync(0xffffffffu, mbar_test_wait(smem_u32(&ctl->s_full[jt & 1]), (jt >> 1) & 1));
+                    if (next_sent)
+                        if (!fetch_send(jt)) goto done;
+                }
                 if (!kFp8)
                     if (!warp_wait(smem_u32(&ctl->kv_full[it % S]), (it / S) & 1, abort_flag)) goto done;
                 const uint32_t mask = ctl->tile_mask[it % kMaskSlots];
@@ -431,10 +518,11 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     }
                     m_ref = m_new;
                 }
+                if (warp == 0) PROF(4, it, 1);
                 const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
                 float lsum = 0.0f;
                 if (kFp8) {
-                    const float(*sc)[2] = ctl->row_scale[it & 1];
+                    const float(*sc)[2] = ctl->row_scale[it % S];
                     uint32_t pk0[16], pk1[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
@@ -458,10 +546,14 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     tmem_st16(lane_base + kColP + sb * 16, pk);
                 }
                 l += lsum;
+                if (warp == 0) PROF(4, it, 2);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&ctl->p_full[sb]));
+                if (warp == 0) PROF(2, it, 3);
+                if (!next_sent)
+                    if (!fetch_send(it + 1)) goto done;
             }
             // ---- epilogue of the item
             {
@@ -528,13 +620,14 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const int rs = it % R, s = it % S;
                 if (!warp_wait(smem_u32(&ctl->raw_full[rs]), (it / R) & 1, abort_flag)) goto done;
                 if (!warp_wait(smem_u32(&ctl->kv_empty[s]), ((it / S) & 1) ^ 1, abort_flag)) goto done;
+                if (warp == 6) PROF(3, it, 0);
                 const uint8_t* grp = sRaw + rs * kRawTileBytes + (r >> 2) * kRawGroupBytes;
                 const int ri = r & 3;
                 const uint8_t* src = grp + ri * 256 + qd * 64;
                 const uint8_t* tail = grp + 1024 + ri * 144;
                 // the row's scales are applied to the fp32 scores and to P by the softmax warps
                 if ((qd & 1) == 0)
-                    ctl->row_scale[it & 1][r][qd >> 1] = reinterpret_cast<const float*>(tail)[2 * half + (qd >> 1)];
+                    ctl->row_scale[s][r][qd >> 1] = reinterpret_cast<const float*>(tail)[2 * half + (qd >> 1)];
                 uint8_t* dst_row = sKV + s * kKvTileBytes + qd * kKvBlockBytes + r * 128;
 #pragma unroll
                 for (int cc = 0; cc < 4; ++cc) {
@@ -544,14 +637,8 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     uint32_t o[8];
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        uint32_t h01, h23;
-                        const uint16_t lo16 = (uint16_t)(wv[k] & 0xFFFFu), hi16 = (uint16_t)(wv[k] >> 16);
-                        asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h01) : "h"(lo16));
-                        asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h23) : "h"(hi16));
-                        const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&h01));
-                        const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&h23));
-                        o[2 * k + 0] = pack_bf16x2(fa.x, fa.y);
-                        o[2 * k + 1] = pack_bf16x2(fb.x, fb.y);
+                        o[2 * k + 0] = e4m3x2_to_bf16x2(__byte_perm(wv[k], 0u, 0x1404u));
+                        o[2 * k + 1] = e4m3x2_to_bf16x2(__byte_perm(wv[k], 0u, 0x3424u));
                     }
                     // 16 bytes -> 16 bf16 = chunks 2c, 2c+1 of this thread's 128-byte block row
                     *reinterpret_cast<uint4*>(dst_row + (((2 * c + 0) ^ (r & 7)) * 16)) = make_uint4(o[0], o[1], o[2], o[3]);
@@ -571,6 +658,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     mbar_arrive(smem_u32(&ctl->kv_full[s]));
                     mbar_arrive(smem_u32(&ctl->raw_empty[rs]));
                 }
+                if (warp == 6) PROF(3, it, 1);
             }
         }
     }

@@ -94,6 +94,28 @@ def test_decode_fp8_paged_padded_poison(oracle):
     _, _, plan = compare(case, oracle, TOL_FP8)
 
 
+def test_decode_fp8_every_code_and_subnormals(oracle):
+    """Cache bytes drawn from every finite e4m3 code, and a second cache made of subnormal codes only
+    (|x| < 2^-6) with large scales so the result hangs on them: the in-kernel conversion must be exact."""
+    rng = np.random.default_rng(77)
+    base = synth.make_decode_case(2, 128, 256, 96, fp8=True, seed=78)
+    for mode in ("all", "subnormal"):
+        case = dict(base)
+        kv = base["kv"].copy()
+        n = kv.shape[0]
+        if mode == "all":
+            codes = rng.integers(0, 256, size=(n, 512)).astype(np.uint8)
+            codes[(codes & 0x7F) == 0x7F] = 0x3A          # no NaN codes
+            scales = rng.uniform(0.002, 0.02, size=(n, 4)).astype(np.float32)
+        else:
+            codes = (rng.integers(0, 8, size=(n, 512)) | (rng.integers(0, 2, size=(n, 512)) << 7)).astype(np.uint8)
+            scales = np.full((n, 4), 256.0, np.float32)
+        kv[:, :512] = codes
+        kv[:, 512:528] = scales.view(np.uint8).reshape(n, 16)
+        case["kv"] = kv
+        compare(case, oracle, TOL_FP8)
+
+
 def test_decode_fp8_small_heads(oracle):
     case = synth.make_decode_case(2, 16, 512, 130, fp8=True, paged=True, seed=13)
     compare(case, oracle, TOL_FP8)

@@ -52,10 +52,15 @@ namespace dsa {
 // Working aid (never compiled into the shipped library): per-role time stamps of the first tiles of
 // cluster 0, to see which stage of the pipeline the others wait for.
 __device__ long long* g_prof = nullptr;
+__device__ __forceinline__ long long prof_now() {   // one clock for all SMs (nanoseconds)
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 #define PROF(role, tile, slot)                                                                      \
     do {                                                                                            \
         if (g_prof != nullptr && blockIdx.x < 2 && (tile) < 64 && lane == 0)                        \
-            g_prof[((blockIdx.x * 8 + (role)) * 64 + (tile)) * 4 + (slot)] = clock64();             \
+            g_prof[((blockIdx.x * 8 + (role)) * 64 + (tile)) * 4 + (slot)] = prof_now();            \
     } while (0)
 extern "C" int dsa_v32_set_prof(long long* buf) { return (int)cudaMemcpyToSymbol(g_prof, &buf, sizeof(buf)); }
 #else
@@ -73,32 +78,40 @@ constexpr int kRawTileBytes = (kTileRows / 4) * kRawGroupBytes;   // 13312
 constexpr int kRawTxBytes = kTileRows * (256 + 144);      // bytes the two gathers deliver per tile
 constexpr int kXbufBytes = kHeadsPerBlock * kTileRows * 4;        // 16384: one tile of fp32 partial scores
 constexpr int kMaskSlots = 16;
+constexpr int kGroups = 2;                                // softmax warpgroups sharing a tile's columns
+constexpr int kSoftmaxWarps = 4 * kGroups;
+constexpr int kProducerWarp = kSoftmaxWarps;
+constexpr int kMmaWarp = kSoftmaxWarps + 1;
+constexpr int kConvertWarp0 = kSoftmaxWarps + 2;          // fp8 cache: four convert warps
 
 template <bool kFp8>
 struct Cfg {
     static constexpr int kKvStages = kFp8 ? 3 : 5;   // MMA-ready bf16 tiles
     static constexpr int kRawStages = kFp8 ? 3 : 0;  // raw fp8 tiles in flight
-    static constexpr int kThreads = kFp8 ? 320 : 192;
+    static constexpr int kThreads = 32 * (kSoftmaxWarps + 2 + (kFp8 ? 4 : 0));
     static constexpr int kOffKv = kQBytesMax;
     static constexpr int kOffRaw = kOffKv + kKvStages * kKvTileBytes;
     static constexpr int kOffX = kOffRaw + kRawStages * kRawTileBytes;
     static constexpr int kOffCtl = kOffX + 2 * kXbufBytes;
-    static constexpr int kCtlBytes = 2048;
+    static constexpr int kCtlBytes = 6144;
     static constexpr int kSmemBytes = kOffCtl + kCtlBytes + 1024;  // + slack for 1024-byte alignment
 };
 
 struct Ctl {
+    float row_max[2][kGroups][kHeadsPerBlock];  // per-group row maxima of a tile, combined across groups
+    float l_part[kGroups][kHeadsPerBlock];      // per-group row sums at the end of an item
     float row_scale[4][kTileRows][2];  // fp8 cache: the two scales (this CTA's groups) of every tile row
     uint64_t q_full, q_empty, o_free;
     uint64_t kv_full[8], kv_empty[8];
     uint64_t raw_full[8], raw_empty[8];
     uint64_t s_full[2], s_empty[2], p_full[2], pv_done[2];
+    uint64_t mx_bar[2], l_bar;
     uint64_t x_full[2];                // the peer's partial scores have landed in exchange buffer b
     uint32_t tile_mask[kMaskSlots];
     uint32_t tmem_base;
     int abort_flag;
 };
-static_assert(sizeof(Ctl) <= 2048, "control block");
+static_assert(sizeof(Ctl) <= 6144, "control block");
 
 // TMEM columns (512 allocated).
 //   bf16 cache: O [0,256) | S 2 x 32 | P 2 x 16 (packed bf16 pairs)
@@ -229,7 +242,8 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     if (tid == 0) {
         mbar_init(smem_u32(&ctl->q_full), 1);
         mbar_init(smem_u32(&ctl->q_empty), 1);
-        mbar_init(smem_u32(&ctl->o_free), 4);
+        mbar_init(smem_u32(&ctl->o_free), kSoftmaxWarps);
+        mbar_init(smem_u32(&ctl->l_bar), kSoftmaxWarps);
         for (int i = 0; i < 8; ++i) {
             mbar_init(smem_u32(&ctl->kv_full[i]), kFp8 ? 4 : 1);
             mbar_init(smem_u32(&ctl->kv_empty[i]), 1);
@@ -238,8 +252,9 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&ctl->s_full[i]), 1);
-            mbar_init(smem_u32(&ctl->s_empty[i]), 4);
-            mbar_init(smem_u32(&ctl->p_full[i]), 4);
+            mbar_init(smem_u32(&ctl->s_empty[i]), kSoftmaxWarps);
+            mbar_init(smem_u32(&ctl->p_full[i]), kSoftmaxWarps);
+            mbar_init(smem_u32(&ctl->mx_bar[i]), kSoftmaxWarps);
             mbar_init(smem_u32(&ctl->pv_done[i]), 1);
             mbar_init(smem_u32(&ctl->x_full[i]), 1);
         }
@@ -248,11 +263,11 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         // the exchange barriers count bytes: armed here for tiles 0 and 1, re-armed by the softmax warps
         for (int i = 0; i < 2; ++i) mbar_arrive_expect_tx(smem_u32(&ctl->x_full[i]), kXbufBytes);
     }
-    if (warp == 5) {
+    if (warp == kMmaWarp) {
         tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
         tmem_relinquish();
     }
-    if (warp == 4 && lane == 0) {
+    if (warp == kProducerWarp && lane == 0) {
         prefetch_tensormap(&tm_q);
         prefetch_tensormap(&tm_kv);
         if (kFp8) prefetch_tensormap(&tm_kv_tail);
@@ -264,7 +279,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const uint32_t tmem = ctl->tmem_base;
     const uint32_t peer_abort = map_to_cta(smem_u32(&ctl->abort_flag), peer);
 
-    if (warp == 4) {
+    if (warp == kProducerWarp) {
         // ============================================================ producer
         uint32_t it = 0;
         int item_n = 0;
@@ -338,7 +353,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 PROF(0, it, 0);
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == kMmaWarp) {
         // ============================================================ MMA issuer
         // The whole warp runs the loop converged (descriptors stay warp-uniform); one elected lane issues.
         {
@@ -382,25 +397,59 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const dsa_v32_work_info wi = p.works[w];
                 const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
                 if (!warp_wait(smem_u32(&ctl->q_full), item_n & 1, abort_flag)) { ok = false; break; }
-                // scores run two tiles ahead of the P V products
-                issue_qk(it_base, n_tiles == 1);
-                if (ok && n_tiles > 1) issue_qk(it_base + 1, n_tiles == 2);
-                for (int t = 0; t < n_tiles && ok; ++t) {
-                    issue_pv(it_base + t, t == 0);
-                    if (ok && t + 2 < n_tiles) issue_qk(it_base + t + 2, t + 3 == n_tiles);
+                // Scores may run up to two tiles ahead of the P V products.  Whichever of the two next
+                // steps has its inputs ready is issued first, so neither stream holds the other up.
+                const uint32_t it_end = it_base + n_tiles;
+                uint32_t qk_next = it_base, pv_next = it_base;
+                uint32_t idle = 0;
+                while (pv_next < it_end && ok) {
+                    bool did = false;
+                    if (qk_next < it_end && qk_next < pv_next + 3) {
+                        const bool ready = __all_sync(0xffffffffu,
+                            mbar_test_wait(smem_u32(&ctl->kv_full[qk_next % S]), (qk_next / S) & 1) &&
+                            mbar_test_wait(smem_u32(&ctl->s_empty[qk_next & 1]), ((qk_next >> 1) & 1) ^ 1));
+                        if (ready) {
+                            issue_qk(qk_next, qk_next + 1 == it_end);
+                            ++qk_next;
+                            did = true;
+                        }
+                    }
+                    if (ok && pv_next < qk_next) {
+                        const bool ready = __all_sync(0xffffffffu,
+                            mbar_test_wait(smem_u32(&ctl->p_full[pv_next & 1]), (pv_next >> 1) & 1));
+                        if (ready) {
+                            issue_pv(pv_next, pv_next == it_base);
+                            ++pv_next;
+                            did = true;
+                        }
+                    }
+                    if (did) {
+                        idle = 0;
+                    } else if (++idle > DSA_WAIT_LIMIT || ((idle & 0x3FFu) == 0 && *abort_flag)) {
+                        *abort_flag = 1;
+                        ok = false;
+                    }
                 }
                 it_base += n_tiles;
             }
         }
-    } else if (warp < 4) {
+    } else if (warp < kSoftmaxWarps) {
         // ============================================================ softmax + epilogue
+        // kGroups warpgroups share the 32 columns of a tile: thread = (head row, column group).
         constexpr uint32_t kColP = col_p<kFp8>();
-        const int row = tid;  // head row inside the block == TMEM lane
-        const uint32_t lane_base = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+        constexpr uint32_t kPStride = kFp8 ? 32 : 16;
+        constexpr int G = kGroups, CPT = kTileRows / G, NCH = CPT / 4, OCOLS = kDvHalf / G;
+        const int cg = warp >> 2;            // column group of this warp
+        const int quad = warp & 3;           // TMEM lane quadrant this warp may touch
+        const int row = quad * 32 + lane;    // head row inside the block == TMEM lane
+        const int c0 = cg * CPT;             // first tile column of this thread
+        const uint32_t lane_base = tmem + (static_cast<uint32_t>(quad * 32) << 16);
         const uint32_t peer_x = map_to_cta(smem_u32(sX), peer);
         const uint32_t peer_xfull = map_to_cta(smem_u32(&ctl->x_full[0]), peer);
+        const uint32_t x_off = static_cast<uint32_t>((cg * NCH) * kHeadsPerBlock + row) * 16u;  // chunk 0 of this thread
         uint32_t it = 0;
-        float part[32];  // this CTA's partial scores of the tile whose exchange is in flight
+        int item_n = 0;
+        float part[CPT];  // this CTA's partial scores of the tile whose exchange is in flight
 
         // partial scores of tile `jt`: TMEM -> registers -> the peer's exchange buffer
         auto fetch_send = [&](uint32_t jt) -> bool {
@@ -410,50 +459,50 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             if (!warp_wait(smem_u32(&ctl->s_full[sb]), (jt >> 1) & 1, abort_flag)) return false;
             tc_fence_after();
             if (warp == 0) PROF(2, jt, 0);
-            const uint32_t s0 = lane_base + kColS + sb * s_stride<kFp8>();
-            uint32_t sr[32];
+            const uint32_t s0 = lane_base + kColS + sb * s_stride<kFp8>() + c0;
+            uint32_t sr[CPT];
             if (kFp8) {
-                const float(*sc)[2] = ctl->row_scale[jt % S];
-                uint32_t sr2[32];
-                tmem_ld32(s0, sr);
-                tmem_ld32(s0 + 32, sr2);
+                const float(*sc)[2] = ctl->row_scale[jt % S] + c0;
+                uint32_t sr2[CPT];
+                tmem_ld_n<CPT>(s0, sr);
+                tmem_ld_n<CPT>(s0 + 32, sr2);
                 tmem_wait_ld();
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
+                for (int j = 0; j < CPT; ++j) {
                     const float2 w2 = *reinterpret_cast<const float2*>(sc[j]);
                     part[j] = fmaf(w2.y, __uint_as_float(sr2[j]), w2.x * __uint_as_float(sr[j]));
                 }
                 if (half) {
-                    tmem_ld32(s0 + 64, sr);
+                    tmem_ld_n<CPT>(s0 + 64, sr);
                     tmem_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) part[j] += __uint_as_float(sr[j]);
+                    for (int j = 0; j < CPT; ++j) part[j] += __uint_as_float(sr[j]);
                 }
             } else {
-                tmem_ld32(s0, sr);
+                tmem_ld_n<CPT>(s0, sr);
                 tmem_wait_ld();
 #pragma unroll
-                for (int j = 0; j < 32; ++j) part[j] = __uint_as_float(sr[j]);
+                for (int j = 0; j < CPT; ++j) part[j] = __uint_as_float(sr[j]);
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[sb]));
             if (warp == 0) PROF(4, jt, 0);
             // layout of an exchange buffer: [8 chunks of 4 columns][128 rows][16 bytes]
-            const uint32_t dst = peer_x + sb * kXbufBytes + row * 16;
+            const uint32_t dst = peer_x + sb * kXbufBytes + x_off;
 #pragma unroll
-            for (int c = 0; c < 8; ++c)
+            for (int c = 0; c < NCH; ++c)
                 st_async_f32x4(dst + c * (kHeadsPerBlock * 16), part[4 * c], part[4 * c + 1], part[4 * c + 2], part[4 * c + 3],
                                peer_xfull + sb * 8);
             if (warp == 0) PROF(2, jt, 1);
             return true;
         };
 
-        for (int w = w_begin; w < w_end; ++w) {
+        for (int w = w_begin; w < w_end; ++w, ++item_n) {
             const dsa_v32_work_info wi = p.works[w];
             const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
-            float m_ref = -INFINITY;  // running reference maximum, log2 domain
-            float l = 0.0f;
+            float m_ref = -INFINITY;  // running reference maximum of the row, log2 domain
+            float l = 0.0f;           // this thread's share of the row sum
             if (!fetch_send(it)) goto done;
             for (int t = 0; t < n_tiles; ++t, ++it) {
                 const int sb = it & 1;
@@ -462,11 +511,11 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (warp == 0) PROF(2, it, 2);
                 // re-arm this buffer's barrier for the tile that lands in it next (tile it + 2)
                 if (tid == 0) mbar_arrive_expect_tx(smem_u32(&ctl->x_full[sb]), kXbufBytes);
-                float tv[32];
+                float tv[CPT];
                 {
-                    const float4* src = reinterpret_cast<const float4*>(sX + sb * kXbufBytes + row * 16);
+                    const float4* src = reinterpret_cast<const float4*>(sX + sb * kXbufBytes + x_off);
 #pragma unroll
-                    for (int c = 0; c < 8; ++c) {
+                    for (int c = 0; c < NCH; ++c) {
                         const float4 o = src[c * kHeadsPerBlock];
                         tv[4 * c + 0] = part[4 * c + 0] + o.x;
                         tv[4 * c + 1] = part[4 * c + 1] + o.y;
@@ -485,14 +534,23 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 }
                 if (!kFp8)
                     if (!warp_wait(smem_u32(&ctl->kv_full[it % S]), (it / S) & 1, abort_flag)) goto done;
-                const uint32_t mask = ctl->tile_mask[it % kMaskSlots];
+                const uint32_t mask = ctl->tile_mask[it % kMaskSlots] >> c0;
 
                 float mt = -INFINITY;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
+                for (int j = 0; j < CPT; ++j) {
                     const float x = tv[j] * p.scale_log2;
                     tv[j] = ((mask >> j) & 1u) ? x : -INFINITY;
                     mt = fmaxf(mt, tv[j]);
+                }
+                // ---- row maximum over the columns of all groups
+                if (G > 1) {
+                    ctl->row_max[sb][cg][row] = mt;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&ctl->mx_bar[sb]));
+                    if (!warp_wait(smem_u32(&ctl->mx_bar[sb]), (it >> 1) & 1, abort_flag)) goto done;
+#pragma unroll
+                    for (int g = 0; g < G; ++g) mt = fmaxf(mt, ctl->row_max[sb][g][row]);
                 }
                 // lazy rescale: move the reference maximum only when a row outgrows it by more than 8
                 const bool need = mt > m_ref + 8.0f;
@@ -506,44 +564,51 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         if (!warp_wait(smem_u32(&ctl->pv_done[pit & 1]), (pit >> 1) & 1, abort_flag)) goto done;
                         tc_fence_after();
 #pragma unroll 1
-                        for (int c0 = 0; c0 < kDvHalf; c0 += 32) {
+                        for (int oc = cg * OCOLS; oc < (cg + 1) * OCOLS; oc += 32) {
                             uint32_t o[32];
-                            tmem_ld32(lane_base + kColO + c0, o);
+                            tmem_ld32(lane_base + kColO + oc, o);
                             tmem_wait_ld();
 #pragma unroll
                             for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * f);
-                            tmem_st32(lane_base + kColO + c0, o);
+                            tmem_st32(lane_base + kColO + oc, o);
                         }
                         tmem_wait_st();
                     }
                     m_ref = m_new;
                 }
                 if (warp == 0) PROF(4, it, 1);
+                // the P buffer of this tile was last read by the P V product of tile it - 2
+                if (t >= 2) {
+                    const uint32_t pit = it - 2;
+                    if (!warp_wait(smem_u32(&ctl->pv_done[pit & 1]), (pit >> 1) & 1, abort_flag)) goto done;
+                }
                 const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
                 float lsum = 0.0f;
                 if (kFp8) {
-                    const float(*sc)[2] = ctl->row_scale[it % S];
-                    uint32_t pk0[16], pk1[16];
+                    const float(*sc)[2] = ctl->row_scale[it % S] + c0;
+                    uint32_t pk0[CPT / 2], pk1[CPT / 2];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
+                    for (int j = 0; j < CPT / 2; ++j) {
                         const float p0 = ex2_approx(tv[2 * j] - m_use);
                         const float p1 = ex2_approx(tv[2 * j + 1] - m_use);
                         lsum += p0 + p1;
-                        pk0[j] = pack_bf16x2(p0 * sc[2 * j][0], p1 * sc[2 * j + 1][0]);
-                        pk1[j] = pack_bf16x2(p0 * sc[2 * j][1], p1 * sc[2 * j + 1][1]);
+                        const float2 wa = *reinterpret_cast<const float2*>(sc[2 * j]);
+                        const float2 wb = *reinterpret_cast<const float2*>(sc[2 * j + 1]);
+                        pk0[j] = pack_bf16x2(p0 * wa.x, p1 * wb.x);
+                        pk1[j] = pack_bf16x2(p0 * wa.y, p1 * wb.y);
                     }
-                    tmem_st16(lane_base + kColP + sb * 32, pk0);
-                    tmem_st16(lane_base + kColP + sb * 32 + 16, pk1);
+                    tmem_st_n<CPT / 2>(lane_base + kColP + sb * kPStride + cg * (CPT / 2), pk0);
+                    tmem_st_n<CPT / 2>(lane_base + kColP + sb * kPStride + 16 + cg * (CPT / 2), pk1);
                 } else {
-                    uint32_t pk[16];
+                    uint32_t pk[CPT / 2];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
+                    for (int j = 0; j < CPT / 2; ++j) {
                         const float p0 = ex2_approx(tv[2 * j] - m_use);
                         const float p1 = ex2_approx(tv[2 * j + 1] - m_use);
                         lsum += p0 + p1;
                         pk[j] = pack_bf16x2(p0, p1);
                     }
-                    tmem_st16(lane_base + kColP + sb * 16, pk);
+                    tmem_st_n<CPT / 2>(lane_base + kColP + sb * kPStride + cg * (CPT / 2), pk);
                 }
                 l += lsum;
                 if (warp == 0) PROF(4, it, 2);
@@ -557,6 +622,15 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
             // ---- epilogue of the item
             {
+                if (G > 1) {   // row sum over the groups
+                    ctl->l_part[cg][row] = l;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&ctl->l_bar));
+                    if (!warp_wait(smem_u32(&ctl->l_bar), item_n & 1, abort_flag)) goto done;
+                    l = 0.0f;
+#pragma unroll
+                    for (int g = 0; g < G; ++g) l += ctl->l_part[g][row];
+                }
                 const uint32_t pit = it - 1;
                 if (!warp_wait(smem_u32(&ctl->pv_done[pit & 1]), (pit >> 1) & 1, abort_flag)) goto done;
                 tc_fence_after();
@@ -568,12 +642,12 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     __nv_bfloat16* o_dst = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)wi.q_row * p.stride_o_row +
                                            (size_t)head * p.stride_o_head + half * kDvHalf;
 #pragma unroll 1
-                    for (int c0 = 0; c0 < kDvHalf; c0 += 32) {
+                    for (int oc = cg * OCOLS; oc < (cg + 1) * OCOLS; oc += 32) {
                         uint32_t o[32];
-                        tmem_ld32(lane_base + kColO + c0, o);
+                        tmem_ld32(lane_base + kColO + oc, o);
                         tmem_wait_ld();
                         if (live) {
-                            uint4* d4 = reinterpret_cast<uint4*>(o_dst + c0);
+                            uint4* d4 = reinterpret_cast<uint4*>(o_dst + oc);
 #pragma unroll
                             for (int v = 0; v < 4; ++v) {
                                 uint4 u;
@@ -585,21 +659,21 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                             }
                         }
                     }
-                    if (live && half == 0 && p.lse != nullptr) p.lse[(size_t)wi.q_row * p.H + head] = lse_nat;
+                    if (live && half == 0 && cg == 0 && p.lse != nullptr) p.lse[(size_t)wi.q_row * p.H + head] = lse_nat;
                 } else {
                     float* o_dst = p.o_accum + ((size_t)wi.partial_slot * kHeadsPerBlock + row) * kDV + half * kDvHalf;
 #pragma unroll 1
-                    for (int c0 = 0; c0 < kDvHalf; c0 += 32) {
+                    for (int oc = cg * OCOLS; oc < (cg + 1) * OCOLS; oc += 32) {
                         uint32_t o[32];
-                        tmem_ld32(lane_base + kColO + c0, o);
+                        tmem_ld32(lane_base + kColO + oc, o);
                         tmem_wait_ld();
-                        float4* d4 = reinterpret_cast<float4*>(o_dst + c0);
+                        float4* d4 = reinterpret_cast<float4*>(o_dst + oc);
 #pragma unroll
                         for (int v = 0; v < 8; ++v)
                             d4[v] = make_float4(__uint_as_float(o[4 * v + 0]) * inv, __uint_as_float(o[4 * v + 1]) * inv,
                                                 __uint_as_float(o[4 * v + 2]) * inv, __uint_as_float(o[4 * v + 3]) * inv);
                     }
-                    if (half == 0)
+                    if (half == 0 && cg == 0)
                         p.lse_accum[(size_t)wi.partial_slot * kHeadsPerBlock + row] = (l > 0.0f) ? lse_nat : -FLT_MAX;
                 }
                 tc_fence_before();
@@ -609,7 +683,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
     } else if (kFp8) {
         // ============================================================ convert (warps 6-9)
-        const int dt = tid - 192;        // 0..127
+        const int dt = tid - 32 * kConvertWarp0;   // 0..127
         const int r = dt >> 2;           // tile row 0..31
         const int qd = dt & 3;           // which 64 of this CTA's 256 latent columns
         uint32_t it = 0;
@@ -620,7 +694,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const int rs = it % R, s = it % S;
                 if (!warp_wait(smem_u32(&ctl->raw_full[rs]), (it / R) & 1, abort_flag)) goto done;
                 if (!warp_wait(smem_u32(&ctl->kv_empty[s]), ((it / S) & 1) ^ 1, abort_flag)) goto done;
-                if (warp == 6) PROF(3, it, 0);
+                if (warp == kConvertWarp0) PROF(3, it, 0);
                 const uint8_t* grp = sRaw + rs * kRawTileBytes + (r >> 2) * kRawGroupBytes;
                 const int ri = r & 3;
                 const uint8_t* src = grp + ri * 256 + qd * 64;
@@ -658,7 +732,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     mbar_arrive(smem_u32(&ctl->kv_full[s]));
                     mbar_arrive(smem_u32(&ctl->raw_empty[rs]));
                 }
-                if (warp == 6) PROF(3, it, 1);
+                if (warp == kConvertWarp0) PROF(3, it, 1);
             }
         }
     }
@@ -669,7 +743,7 @@ done:
     __syncthreads();
     if (tid == 0 && ctl->abort_flag) atomicExch(p.status, DSA_V32_ERR_DEVICE_WAIT);
     cluster_sync_all();   // nobody leaves while the peer may still store into this CTA's shared memory
-    if (warp == 5) {
+    if (warp == kMmaWarp) {
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
     }

@@ -189,6 +189,30 @@ typedef struct dsa_v32_host_io {
 int dsa_v32_decode_pipeline_host(const dsa_v32_attn_args* args, const dsa_v32_host_io* io, void* stream);
 
 /*
+ * The same pipeline for callers that cannot allocate device memory at all: code running where
+ * cudaMalloc is off limits (a plugin loaded into a host that owns the memory pool, a real-time
+ * serving loop that must not touch the allocator, a process whose memory was handed out at start-up).
+ * It has no counterpart in the reference, whose harness always allocates its plan with hipMalloc.
+ * args->workspace / workspace_bytes are ignored: the work list, reduce tables and split partials live
+ * in a fixed array inside the library's device image, DSA_V32_STATIC_SCRATCH_BYTES long, which every
+ * GPU that loads the library holds until the process exits.  Shapes whose plan does not fit are
+ * rejected with DSA_V32_ERR_SCRATCH_TOO_SMALL before anything is launched.  The call allocates nothing
+ * on the device (no cudaMalloc / cudaFree, no allocating library call).
+ *   - The first call on a device looks up the array's device address (with that device current) and
+ *     uploads the plan for the shape; a call with a new shape re-plans.  Make the first call for a
+ *     shape before starting any stream capture.
+ *   - All calls on a device share the one array and it keeps the previous call's contents; the status
+ *     word is cleared at the start of every call, everything else is rewritten before it is read.
+ *     Two calls that overlap on the GPU (different streams, no dependency) race on it: serialise them.
+ *   - Inputs and outputs are still the caller's buffers, exactly as in dsa_v32_decode_pipeline.
+ */
+#define DSA_V32_STATIC_SCRATCH_BYTES (32u << 20)
+#define DSA_V32_ERR_SCRATCH_TOO_SMALL (-7)
+int dsa_v32_decode_pipeline_static(const dsa_v32_attn_args* args, void* stream);
+/* Device address of that array on the current device, NULL before the first static call there. */
+void* dsa_v32_static_scratch_address(void);
+
+/*
  * Reads (and clears) the device status word of the workspace after synchronising `stream`:
  * 0, or DSA_V32_ERR_DEVICE_WAIT when a bounded wait inside a kernel ran out.
  */

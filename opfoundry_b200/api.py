@@ -17,6 +17,8 @@ D_QK, D_V, D_ROPE = 576, 512, 64
 BF16_ROW_BYTES, FP8_ROW_BYTES = 1152, 656
 KV_BF16, KV_FP8 = 0, 1
 ERR_DEVICE_WAIT = 1001
+ERR_SCRATCH_TOO_SMALL = -7
+STATIC_SCRATCH_BYTES = 32 << 20
 
 
 class WorkInfo(C.Structure):
@@ -52,7 +54,8 @@ class HostIO(C.Structure):
 EXPORTS = ["dsa_v32_abi_version", "dsa_v32_error_string", "dsa_v32_plan_info_get", "dsa_v32_plan",
            "dsa_v32_plan_host", "dsa_v32_plan_read", "dsa_v32_decode_bf16", "dsa_v32_decode_fp8",
            "dsa_v32_prefill_bf16", "dsa_v32_combine", "dsa_v32_decode_pipeline", "dsa_v32_device_status",
-           "dsa_v32_debug_rows", "dsa_v32_pack_fp8_rows", "dsa_v32_decode_pipeline_host"]
+           "dsa_v32_debug_rows", "dsa_v32_pack_fp8_rows", "dsa_v32_decode_pipeline_host",
+           "dsa_v32_decode_pipeline_static", "dsa_v32_static_scratch_address"]
 
 _lib = None
 
@@ -83,6 +86,9 @@ def lib():
             getattr(L, name).argtypes = [C.POINTER(AttnArgs), C.c_void_p]
         L.dsa_v32_decode_pipeline.argtypes = [C.POINTER(AttnArgs), C.c_int, C.c_void_p]
         L.dsa_v32_decode_pipeline_host.argtypes = [C.POINTER(AttnArgs), C.POINTER(HostIO), C.c_void_p]
+        L.dsa_v32_decode_pipeline_static.argtypes = [C.POINTER(AttnArgs), C.c_void_p]
+        L.dsa_v32_static_scratch_address.restype = C.c_void_p
+        L.dsa_v32_static_scratch_address.argtypes = []
         L.dsa_v32_debug_rows.argtypes = [C.POINTER(AttnArgs), C.c_void_p, C.c_void_p]
         L.dsa_v32_pack_fp8_rows.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]
         _lib = L
@@ -256,3 +262,32 @@ def mla_decode_step_host(args, q_host, indices_host, out_host, lse_host):
     io.q_bytes = q_host.numel() * q_host.element_size()
     io.out_bytes = out_host.numel() * out_host.element_size()
     _check(lib().dsa_v32_decode_pipeline_host(C.byref(args), C.byref(io), _stream()), "dsa_v32_decode_pipeline_host")
+
+
+def mla_decode_launch_pipeline_static(q, kv, indices, sm_scale, *, s_q=1, block_table=None, page_block_size=64,
+                                      kv_batch_stride_rows=0, out=None, lse=None, check=True):
+    """The pipeline for callers that may not allocate device memory: the split workspace is a fixed
+    array inside the library (32 MiB per GPU, shared by all calls, so calls must not overlap on the
+    GPU).  The first call for a shape plans it - make that call before any stream capture.  Shapes
+    whose plan does not fit raise DsaError with status ERR_SCRATCH_TOO_SMALL.  `out` / `lse` should be
+    passed in by such a caller; they are only created here for convenience when omitted."""
+    total_q, H = q.shape[0], q.shape[1]
+    if out is None:
+        out = torch.empty(total_q, H, D_V, dtype=torch.bfloat16, device=q.device)
+    if lse is None:
+        lse = torch.empty(total_q, H, dtype=torch.float32, device=q.device)
+
+    class _NoPlan:   # make_args only needs the shape facts of a plan
+        pass
+    np_ = _NoPlan()
+    np_.s_q = s_q
+    np_.workspace = torch.empty(0, dtype=torch.uint8)   # ignored by the entry point
+    a = make_args(q, kv, indices, np_, sm_scale, out=out, lse=lse, block_table=block_table,
+                  page_block_size=page_block_size, kv_batch_stride_rows=kv_batch_stride_rows)
+    a.workspace = None
+    a.workspace_bytes = 0
+    _check(lib().dsa_v32_decode_pipeline_static(C.byref(a), _stream()), "dsa_v32_decode_pipeline_static")
+    if check:
+        a.workspace = lib().dsa_v32_static_scratch_address()
+        _check(lib().dsa_v32_device_status(C.byref(a), _stream()), "dsa_v32_device_status")
+    return out, lse

@@ -179,6 +179,7 @@ const char* dsa_v32_error_string(int status) {
         case DSA_V32_ERR_WORKSPACE: return "workspace missing, too small, or not planned for this shape";
         case DSA_V32_ERR_DTYPE: return "kv_dtype does not match the entry point";
         case DSA_V32_ERR_DRIVER: return "tensor-map creation failed";
+        case DSA_V32_ERR_SCRATCH_TOO_SMALL: return "the plan for this shape does not fit the library's static scratch array";
         case DSA_V32_ERR_DEVICE_WAIT: return "a bounded device-side wait ran out";
         default: return status > 0 ? cudaGetErrorString((cudaError_t)status) : "unknown status";
     }
@@ -326,6 +327,77 @@ int dsa_v32_decode_pipeline_host(const dsa_v32_attn_args* a, const dsa_v32_host_
         if (e != cudaSuccess) return (int)e;
     }
     return DSA_V32_OK;
+}
+
+// ------------------------------------------------------------------ no-allocation variant
+// Scratch for callers that may not allocate: lives in the library's device image.  In host code the
+// name below is only a handle for the runtime; the device address comes from cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_static_scratch[DSA_V32_STATIC_SCRATCH_BYTES];
+
+namespace {
+struct StaticScratchState {
+    void* dev_ptr = nullptr;   // device address of g_static_scratch on this device
+    dsa_v32_shape planned{};   // shape the array is currently planned for
+    bool has_plan = false;
+};
+std::mutex g_static_mu;
+StaticScratchState g_static_state[64];
+}  // namespace
+
+int dsa_v32_decode_pipeline_static(const dsa_v32_attn_args* a, void* stream) {
+    if (!a) return DSA_V32_ERR_NULL;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return DSA_V32_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    std::lock_guard<std::mutex> guard(g_static_mu);
+    StaticScratchState& S = g_static_state[dev];
+    if (S.dev_ptr == nullptr) {
+        // once per device, with that device current
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        if (ptr == nullptr) return DSA_V32_ERR_DRIVER;
+        S.dev_ptr = ptr;
+    }
+    const bool same = S.has_plan && S.planned.total_q == a->total_q && S.planned.H == a->H &&
+                      S.planned.topk == a->topk && S.planned.s_q == a->s_q;
+    if (!same) {
+        dsa_v32_shape sh;
+        std::memset(&sh, 0, sizeof(sh));
+        sh.total_q = a->total_q;
+        sh.H = a->H;
+        sh.topk = a->topk;
+        sh.s_q = a->s_q;
+        dsa_v32_plan_info info;
+        int rc = dsa_v32_plan_info_get(&sh, &info);
+        if (rc) return rc;
+        if (info.workspace_bytes > (int64_t)DSA_V32_STATIC_SCRATCH_BYTES) return DSA_V32_ERR_SCRATCH_TOO_SMALL;
+        S.has_plan = false;
+        rc = dsa_v32_plan(&sh, S.dev_ptr, DSA_V32_STATIC_SCRATCH_BYTES, stream);
+        if (rc) return rc;
+        S.planned = sh;
+        S.has_plan = true;
+    }
+    // the array keeps the last call's contents: the status word has to start at zero
+    e = cudaMemsetAsync(reinterpret_cast<uint8_t*>(S.dev_ptr) + offsetof(WorkspaceHeader, status), 0, 4, st);
+    if (e != cudaSuccess) return (int)e;
+    dsa_v32_attn_args b = *a;
+    b.workspace = S.dev_ptr;
+    b.workspace_bytes = DSA_V32_STATIC_SCRATCH_BYTES;
+    int rc = launch_attention(&b, b.kv_dtype, st);
+    if (rc) return rc;
+    return dsa_v32_combine(&b, stream);
+}
+
+// Device address of the static scratch on the current device (after the first static call); lets a
+// caller read the status word with dsa_v32_device_status by passing it as args->workspace.
+void* dsa_v32_static_scratch_address(void) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> guard(g_static_mu);
+    return g_static_state[dev].dev_ptr;
 }
 
 int dsa_v32_device_status(const dsa_v32_attn_args* a, void* stream) {

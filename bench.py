@@ -185,6 +185,66 @@ def workload_config():
                 valid_len_hint="given to the planner (the analogue of the reference's kv_indptr lengths)")
 
 
+def run_prefill(args, rank, world, local_rank, torch, dist, api, workloads):
+    """bf16 causal prefill: one sequence of T tokens, 128 heads, top-k 2048; a step = the whole prefill.
+    With N > 1 ranks the query tokens are cut into contiguous chunks of equal work, the latent cache is
+    replicated and nothing is exchanged (strong scaling of one sequence)."""
+    from opfoundry_b200 import shard
+    import numpy as np
+    T, H, topk = args.tokens, CFG["H"], CFG["topk"]
+    valid_all = np.minimum(np.arange(T) + 1, topk)
+    bounds = shard.shard_queries_equal_work(valid_all, world)
+    q0, q1 = bounds[rank], bounds[rank + 1]
+    W = workloads.prefill_bf16(T=T, H=H, topk=topk, seed=2026, q_begin=q0, q_end=q1)
+    nq = q1 - q0
+    plan = api.mla_decode_plan_create(nq, H, topk, nq, valid_len_hint=W["valid_len"])
+    out = torch.empty(nq, H, D_V, dtype=torch.bfloat16, device="cuda")
+    lse = torch.empty(nq, H, dtype=torch.float32, device="cuda")
+    a = api.make_args(W["q"], W["kv"], W["indices"], plan, 1.0 / math.sqrt(192.0), out=out, lse=lse)
+    L = api.lib()
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        api._check(L.dsa_v32_decode_pipeline(C.byref(a), 0, stream), "prefill")
+    torch.cuda.synchronize()
+    api._check(L.dsa_v32_device_status(C.byref(a), stream), "device status")
+    K = args.steps
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    e0.record()
+    for _ in range(K):
+        api._check(L.dsa_v32_decode_pipeline(C.byref(a), 0, stream), "prefill")
+    e1.record()
+    barrier()
+    sampler.stop()
+    ms = shard.max_over_ranks([e0.elapsed_time(e1)], "cuda")[0] / K
+    total_pairs = float(valid_all.sum())
+    if rank == 0:
+        pk = peaks()
+        flops = flops_of(total_pairs, H)
+        tf = flops / (ms * 1e-3) / 1e12
+        print(json.dumps(dict(
+            metric="sparse_mla_prefill_bf16_tflops", value=tf, unit="TFLOP/s", n_gpus=world, steps=K, warmup=args.warmup,
+            ms_per_step=ms, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="bf16 MMA, fp32 accumulate",
+            data="synthetic",
+            config=dict(workload="prefill_bf16_t%d_h128_topk2048_causal" % T, tokens=T, heads=H, topk=topk, pairs=total_pairs,
+                        sharding="contiguous query chunks of equal work, latent cache replicated, no exchange",
+                        l2="gathered rows per step %.1f GB from a %.1f MB cache (L2-resident by construction of the config)" % (
+                            total_pairs * 1152 / 1e9, T * 1152 / 1e6)),
+            roofline=dict(bound="tensor", achieved=tf, peak=pk["bf16_tflops"], unit="TFLOP/s", frac=tf / pk["bf16_tflops"],
+                          traffic=None, peak_source=pk["source"], kernel="sparse_mla_kernel<bf16>",
+                          flops_per_launch=flops, gathered_bytes_per_launch=total_pairs * 1152.0),
+            gpu_launches=K, clocks=sampler.summary())), flush=True)
+
+
 def e2e_leg(api, torch, W, plan, sm_scale, out, lse, K, barrier):
     """K steps through the host-buffer C-ABI call: pinned host q / index lists in, out / lse back,
     the caller synchronising on every step's result."""
@@ -222,6 +282,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--batch", type=int, default=CFG["B"], help="sequences per GPU (smaller only for profiler captures)")
+    ap.add_argument("--workload", default="decode_fp8", choices=["decode_fp8", "prefill_bf16"],
+                    help="decode_fp8: the headline; prefill_bf16: one 4096-token causal prefill (second half of the metric)")
+    ap.add_argument("--tokens", type=int, default=4096, help="prefill_bf16: sequence length")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -246,6 +309,11 @@ def main():
         if world > 1:
             dist.barrier()
     api.lib()
+    if args.workload == "prefill_bf16":
+        run_prefill(args, rank, world, local_rank, torch, dist, api, workloads)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     W = workloads.decode_fp8(B=CFG["B"], H=CFG["H"], kv_len=CFG["kv_len"], topk=CFG["topk"], page=CFG["page"],
                              pad_frac=CFG["pad_frac"], n_batches=CFG["n_batches"], seed=2026 + rank)

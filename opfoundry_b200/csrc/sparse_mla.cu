@@ -78,7 +78,7 @@ constexpr int kRawTileBytes = (kTileRows / 4) * kRawGroupBytes;   // 13312
 constexpr int kRawTxBytes = kTileRows * (256 + 144);      // bytes the two gathers deliver per tile
 constexpr int kXbufBytes = kHeadsPerBlock * kTileRows * 4;        // 16384: one tile of fp32 partial scores
 constexpr int kMaskSlots = 16;
-constexpr int kGroups = 2;                                // softmax warpgroups sharing a tile's columns
+constexpr int kGroups = 4;                                // softmax warpgroups sharing a tile's columns
 constexpr int kSoftmaxWarps = 4 * kGroups;
 constexpr int kProducerWarp = kSoftmaxWarps;
 constexpr int kMmaWarp = kSoftmaxWarps + 1;
@@ -93,7 +93,7 @@ struct Cfg {
     static constexpr int kOffRaw = kOffKv + kKvStages * kKvTileBytes;
     static constexpr int kOffX = kOffRaw + kRawStages * kRawTileBytes;
     static constexpr int kOffCtl = kOffX + 2 * kXbufBytes;
-    static constexpr int kCtlBytes = 6144;
+    static constexpr int kCtlBytes = 8192;
     static constexpr int kSmemBytes = kOffCtl + kCtlBytes + 1024;  // + slack for 1024-byte alignment
 };
 
@@ -106,12 +106,12 @@ struct Ctl {
     uint64_t raw_full[8], raw_empty[8];
     uint64_t s_full[2], s_empty[2], p_full[2], pv_done[2];
     uint64_t mx_bar[2], l_bar;
-    uint64_t x_full[2];                // the peer's partial scores have landed in exchange buffer b
+    uint64_t x_full[2][kSoftmaxWarps]; // the peer's partial scores for this warp's rows and columns have landed
     uint32_t tile_mask[kMaskSlots];
     uint32_t tmem_base;
     int abort_flag;
 };
-static_assert(sizeof(Ctl) <= 6144, "control block");
+static_assert(sizeof(Ctl) <= 8192, "control block");
 
 // TMEM columns (512 allocated).
 //   bf16 cache: O [0,256) | S 2 x 32 | P 2 x 16 (packed bf16 pairs)
@@ -256,12 +256,15 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             mbar_init(smem_u32(&ctl->p_full[i]), kSoftmaxWarps);
             mbar_init(smem_u32(&ctl->mx_bar[i]), kSoftmaxWarps);
             mbar_init(smem_u32(&ctl->pv_done[i]), 1);
-            mbar_init(smem_u32(&ctl->x_full[i]), 1);
+            for (int w = 0; w < kSoftmaxWarps; ++w) mbar_init(smem_u32(&ctl->x_full[i][w]), 1);
         }
         ctl->abort_flag = 0;
         fence_mbar_init();
-        // the exchange barriers count bytes: armed here for tiles 0 and 1, re-armed by the softmax warps
-        for (int i = 0; i < 2; ++i) mbar_arrive_expect_tx(smem_u32(&ctl->x_full[i]), kXbufBytes);
+        // the exchange barriers (one per softmax warp and buffer) count bytes: armed here for tiles 0
+        // and 1, re-armed by the softmax warps
+        for (int i = 0; i < 2; ++i)
+            for (int w = 0; w < kSoftmaxWarps; ++w)
+                mbar_arrive_expect_tx(smem_u32(&ctl->x_full[i][w]), kXbufBytes / kSoftmaxWarps);
     }
     if (warp == kMmaWarp) {
         tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
@@ -445,7 +448,9 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const int c0 = cg * CPT;             // first tile column of this thread
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(quad * 32) << 16);
         const uint32_t peer_x = map_to_cta(smem_u32(sX), peer);
-        const uint32_t peer_xfull = map_to_cta(smem_u32(&ctl->x_full[0]), peer);
+        // the peer thread with the same (warp, lane) reads what this thread sends, so each warp has its
+        // own byte-counting barrier in the peer (spreads the completion updates over 8 barriers)
+        const uint32_t peer_xfull = map_to_cta(smem_u32(&ctl->x_full[0][warp]), peer);
         const uint32_t x_off = static_cast<uint32_t>((cg * NCH) * kHeadsPerBlock + row) * 16u;  // chunk 0 of this thread
         uint32_t it = 0;
         int item_n = 0;
@@ -493,7 +498,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
             for (int c = 0; c < NCH; ++c)
                 st_async_f32x4(dst + c * (kHeadsPerBlock * 16), part[4 * c], part[4 * c + 1], part[4 * c + 2], part[4 * c + 3],
-                               peer_xfull + sb * 8);
+                               peer_xfull + sb * (8 * kSoftmaxWarps));
             if (warp == 0) PROF(2, jt, 1);
             return true;
         };
@@ -507,10 +512,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             for (int t = 0; t < n_tiles; ++t, ++it) {
                 const int sb = it & 1;
                 // ---- full scores of tile `it` = own partial + the peer's
-                if (!warp_wait_cluster(smem_u32(&ctl->x_full[sb]), (it >> 1) & 1, abort_flag)) goto done;
+                if (!warp_wait_cluster(smem_u32(&ctl->x_full[sb][warp]), (it >> 1) & 1, abort_flag)) goto done;
                 if (warp == 0) PROF(2, it, 2);
                 // re-arm this buffer's barrier for the tile that lands in it next (tile it + 2)
-                if (tid == 0) mbar_arrive_expect_tx(smem_u32(&ctl->x_full[sb]), kXbufBytes);
+                if (lane == 0) mbar_arrive_expect_tx(smem_u32(&ctl->x_full[sb][warp]), kXbufBytes / kSoftmaxWarps);
                 float tv[CPT];
                 {
                     const float4* src = reinterpret_cast<const float4*>(sX + sb * kXbufBytes + x_off);

@@ -33,7 +33,7 @@ CFG = dict(B=64, H=128, kv_len=32768, topk=2048, page=64, pad_frac=0.05, n_batch
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)
 # dram bytes (read + write) of one attention-kernel launch on the workload above, from the ncu
 # capture summarised in profiles/ (null until a capture exists for the current kernel)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 112.9e6  # 4 x 28.2 MB captured at batch 16 (profiles/sparse_mla_fp8_decode_pair_kernel.md)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 113.2e6  # 4 x 28.3 MB captured at batch 16 (profiles/sparse_mla_fp8_decode_cluster_kernel.md)
 
 
 def peaks():

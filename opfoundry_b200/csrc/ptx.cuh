@@ -99,6 +99,10 @@ __device__ __forceinline__ void st_async_f32x4(uint32_t caddr, float a, float b,
                  "f"(a), "f"(b), "f"(c), "f"(d), "r"(cbar)
                  : "memory");
 }
+__device__ __forceinline__ void st_async_u32(uint32_t caddr, uint32_t v, uint32_t cbar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.u32 [%0], %1, [%2];" ::"r"(caddr), "r"(v), "r"(cbar)
+                 : "memory");
+}
 // arrive on an mbarrier of another CTA of the cluster; releases this thread's earlier writes
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t caddr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(caddr) : "memory");

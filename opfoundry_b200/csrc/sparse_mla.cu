@@ -98,7 +98,7 @@ struct Cfg {
 };
 
 struct Ctl {
-    float row_max[2][kGroups][kHeadsPerBlock];  // per-group row maxima of a tile, combined across groups
+    float row_max[2][2][kHeadsPerBlock];        // per team: row maxima of the two column halves of a tile
     float l_part[kGroups][kHeadsPerBlock];      // per-group row sums at the end of an item
     float row_scale[4][kTileRows][2];  // fp8 cache: the two scales (this CTA's groups) of every tile row
     uint64_t q_full, q_empty, o_free;
@@ -106,7 +106,10 @@ struct Ctl {
     uint64_t raw_full[8], raw_empty[8];
     uint64_t s_full[2], s_empty[2], p_full[2], pv_done[2];
     uint64_t mx_bar[2], l_bar;
-    uint64_t x_full[2][kSoftmaxWarps]; // the peer's partial scores for this warp's rows and columns have landed
+    uint64_t x_full[kSoftmaxWarps];    // bytes of the peer's partial scores for this warp's rows / columns
+    uint64_t x_free[kSoftmaxWarps];    // credit (4 bytes): the peer's same warp has read what this warp sent last
+    uint32_t x_sink[kSoftmaxWarps];    // where the credit word lands
+    float m_shared[kHeadsPerBlock];    // reference maximum of every row, moved only at a tile's commit
     uint32_t tile_mask[kMaskSlots];
     uint32_t tmem_base;
     int abort_flag;
@@ -252,19 +255,18 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&ctl->s_full[i]), 1);
-            mbar_init(smem_u32(&ctl->s_empty[i]), kSoftmaxWarps);
-            mbar_init(smem_u32(&ctl->p_full[i]), kSoftmaxWarps);
-            mbar_init(smem_u32(&ctl->mx_bar[i]), kSoftmaxWarps);
+            mbar_init(smem_u32(&ctl->s_empty[i]), kSoftmaxWarps / 2);   // one team
+            mbar_init(smem_u32(&ctl->p_full[i]), kSoftmaxWarps / 2);
+            mbar_init(smem_u32(&ctl->mx_bar[i]), kSoftmaxWarps / 2);
             mbar_init(smem_u32(&ctl->pv_done[i]), 1);
-            for (int w = 0; w < kSoftmaxWarps; ++w) mbar_init(smem_u32(&ctl->x_full[i][w]), 1);
         }
         ctl->abort_flag = 0;
         fence_mbar_init();
-        // the exchange barriers (one per softmax warp and buffer) count bytes: armed here for tiles 0
-        // and 1, re-armed by the softmax warps
-        for (int i = 0; i < 2; ++i)
-            for (int w = 0; w < kSoftmaxWarps; ++w)
-                mbar_arrive_expect_tx(smem_u32(&ctl->x_full[i][w]), kXbufBytes / kSoftmaxWarps);
+        for (int w = 0; w < kSoftmaxWarps; ++w) {
+            mbar_init(smem_u32(&ctl->x_full[w]), 1);
+            mbar_init(smem_u32(&ctl->x_free[w]), 1);
+        }
+        fence_mbar_init();
     }
     if (warp == kMmaWarp) {
         tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
@@ -438,109 +440,120 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
     } else if (warp < kSoftmaxWarps) {
         // ============================================================ softmax + epilogue
-        // kGroups warpgroups share the 32 columns of a tile: thread = (head row, column group).
+        // Two teams of eight warps take alternate tiles (team = tile parity = score / P / exchange buffer
+        // index), so two tiles are in flight through the long part of a step (TMEM load, exchange, mask,
+        // max, exp).  Inside a team, warpgroup `chalf` owns 16 of the tile's 32 columns; thread = (head
+        // row, chalf).  Only the short commit of a tile is ordered after the commit of the tile before:
+        // there the shared reference maximum of the row is re-read, P (computed against a snapshot) is
+        // corrected to it, O is rescaled in the rare case the reference moves (lazy threshold 8), P is
+        // stored and the tile is released to the MMA warp.
         constexpr uint32_t kColP = col_p<kFp8>();
         constexpr uint32_t kPStride = kFp8 ? 32 : 16;
-        constexpr int G = kGroups, CPT = kTileRows / G, NCH = CPT / 4, OCOLS = kDvHalf / G;
-        const int cg = warp >> 2;            // column group of this warp
+        constexpr int G = kGroups, CPT = 16, NCH = CPT / 4, OCOLS = kDvHalf / G;
+        static_assert(kGroups == 4, "two teams x two column halves");
+        const int cg = warp >> 2;            // warpgroup
+        const int team = cg >> 1;            // tile parity this warp works on
+        const int chalf = cg & 1;            // which half of a tile's 32 columns
         const int quad = warp & 3;           // TMEM lane quadrant this warp may touch
         const int row = quad * 32 + lane;    // head row inside the block == TMEM lane
-        const int c0 = cg * CPT;             // first tile column of this thread
+        const int c0 = chalf * CPT;
+        const int sb = team;                 // buffer index of everything double-buffered per tile
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(quad * 32) << 16);
-        const uint32_t peer_x = map_to_cta(smem_u32(sX), peer);
-        // the peer thread with the same (warp, lane) reads what this thread sends, so each warp has its
-        // own byte-counting barrier in the peer (spreads the completion updates over 8 barriers)
-        const uint32_t peer_xfull = map_to_cta(smem_u32(&ctl->x_full[0][warp]), peer);
-        const uint32_t x_off = static_cast<uint32_t>((cg * NCH) * kHeadsPerBlock + row) * 16u;  // chunk 0 of this thread
-        uint32_t it = 0;
+        // exchange buffer of a tile: [8 chunks of 4 columns][128 rows][16 bytes]
+        const uint32_t x_off = static_cast<uint32_t>(sb * kXbufBytes) +
+                               static_cast<uint32_t>((chalf * NCH) * kHeadsPerBlock + row) * 16u;
+        const uint32_t peer_x = map_to_cta(smem_u32(sX), peer) + x_off;
+        // the peer thread with the same (warp, lane) reads what this thread sends: one byte-counting
+        // barrier per warp for arrival, one per warp for the credit "the peer has read the last one"
+        const uint32_t my_xfull = smem_u32(&ctl->x_full[warp]);
+        const uint32_t my_xfree = smem_u32(&ctl->x_free[warp]);
+        const uint32_t peer_xfull = map_to_cta(my_xfull, peer);
+        const uint32_t peer_xfree = map_to_cta(my_xfree, peer);
+        const uint32_t peer_xsink = map_to_cta(smem_u32(&ctl->x_sink[warp]), peer);
+        uint32_t it_base = 0;   // global tile counter at the start of the item
+        uint32_t n_x = 0;       // exchanges this warp has done (phases of its two exchange barriers)
         int item_n = 0;
-        float part[CPT];  // this CTA's partial scores of the tile whose exchange is in flight
-
-        // partial scores of tile `jt`: TMEM -> registers -> the peer's exchange buffer
-        auto fetch_send = [&](uint32_t jt) -> bool {
-            const int sb = jt & 1;
-            if (kFp8)
-                if (!warp_wait(smem_u32(&ctl->kv_full[jt % S]), (jt / S) & 1, abort_flag)) return false;
-            if (!warp_wait(smem_u32(&ctl->s_full[sb]), (jt >> 1) & 1, abort_flag)) return false;
-            tc_fence_after();
-            if (warp == 0) PROF(2, jt, 0);
-            const uint32_t s0 = lane_base + kColS + sb * s_stride<kFp8>() + c0;
-            uint32_t sr[CPT];
-            if (kFp8) {
-                const float(*sc)[2] = ctl->row_scale[jt % S] + c0;
-                uint32_t sr2[CPT];
-                tmem_ld_n<CPT>(s0, sr);
-                tmem_ld_n<CPT>(s0 + 32, sr2);
-                tmem_wait_ld();
-#pragma unroll
-                for (int j = 0; j < CPT; ++j) {
-                    const float2 w2 = *reinterpret_cast<const float2*>(sc[j]);
-                    part[j] = fmaf(w2.y, __uint_as_float(sr2[j]), w2.x * __uint_as_float(sr[j]));
-                }
-                if (half) {
-                    tmem_ld_n<CPT>(s0 + 64, sr);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int j = 0; j < CPT; ++j) part[j] += __uint_as_float(sr[j]);
-                }
-            } else {
-                tmem_ld_n<CPT>(s0, sr);
-                tmem_wait_ld();
-#pragma unroll
-                for (int j = 0; j < CPT; ++j) part[j] = __uint_as_float(sr[j]);
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[sb]));
-            if (warp == 0) PROF(4, jt, 0);
-            // layout of an exchange buffer: [8 chunks of 4 columns][128 rows][16 bytes]
-            const uint32_t dst = peer_x + sb * kXbufBytes + x_off;
-#pragma unroll
-            for (int c = 0; c < NCH; ++c)
-                st_async_f32x4(dst + c * (kHeadsPerBlock * 16), part[4 * c], part[4 * c + 1], part[4 * c + 2], part[4 * c + 3],
-                               peer_xfull + sb * (8 * kSoftmaxWarps));
-            if (warp == 0) PROF(2, jt, 1);
-            return true;
-        };
 
         for (int w = w_begin; w < w_end; ++w, ++item_n) {
             const dsa_v32_work_info wi = p.works[w];
             const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
-            float m_ref = -INFINITY;  // running reference maximum of the row, log2 domain
-            float l = 0.0f;           // this thread's share of the row sum
-            if (!fetch_send(it)) goto done;
-            for (int t = 0; t < n_tiles; ++t, ++it) {
-                const int sb = it & 1;
-                // ---- full scores of tile `it` = own partial + the peer's
-                if (!warp_wait_cluster(smem_u32(&ctl->x_full[sb][warp]), (it >> 1) & 1, abort_flag)) goto done;
-                if (warp == 0) PROF(2, it, 2);
-                // re-arm this buffer's barrier for the tile that lands in it next (tile it + 2)
-                if (lane == 0) mbar_arrive_expect_tx(smem_u32(&ctl->x_full[sb][warp]), kXbufBytes / kSoftmaxWarps);
+            const uint32_t it_end = it_base + n_tiles;
+            float l_part = 0.0f;        // this thread's share of the row sum, expressed against l_ref
+            float l_ref = 0.0f;
+            for (uint32_t it = it_base + ((team - it_base) & 1u); it < it_end; it += 2) {
+                const uint32_t ph = (it >> 1) & 1;
+                const bool first = (it == it_base);
                 float tv[CPT];
+                // ---- own partial scores out of TMEM
+                if (lane == 0) mbar_arrive_expect_tx(my_xfull, kXbufBytes / 8);
+                if (kFp8)
+                    if (!warp_wait(smem_u32(&ctl->kv_full[it % S]), (it / S) & 1, abort_flag)) goto done;
+                if (!warp_wait(smem_u32(&ctl->s_full[sb]), ph, abort_flag)) goto done;
+                tc_fence_after();
+                if (warp == 0 || warp == 8) PROF(2, it, 0);
                 {
-                    const float4* src = reinterpret_cast<const float4*>(sX + sb * kXbufBytes + x_off);
+                    const uint32_t s0 = lane_base + kColS + sb * s_stride<kFp8>() + c0;
+                    uint32_t sr[CPT];
+                    if (kFp8) {
+                        const float(*sc)[2] = ctl->row_scale[it % S] + c0;
+                        uint32_t sr2[CPT];
+                        tmem_ld_n<CPT>(s0, sr);
+                        tmem_ld_n<CPT>(s0 + 32, sr2);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < CPT; ++j) {
+                            const float2 w2 = *reinterpret_cast<const float2*>(sc[j]);
+                            tv[j] = fmaf(w2.y, __uint_as_float(sr2[j]), w2.x * __uint_as_float(sr[j]));
+                        }
+                        if (half) {
+                            tmem_ld_n<CPT>(s0 + 64, sr);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int j = 0; j < CPT; ++j) tv[j] += __uint_as_float(sr[j]);
+                        }
+                    } else {
+                        tmem_ld_n<CPT>(s0, sr);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < CPT; ++j) tv[j] = __uint_as_float(sr[j]);
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[sb]));   // the MMA warp may overwrite the scores
+                // ---- exchange: send when the peer has read what was sent last, add what it sent
+                if (n_x > 0)
+                    if (!warp_wait_cluster(my_xfree, (n_x - 1) & 1, abort_flag)) goto done;
+                if (lane == 0) mbar_arrive_expect_tx(my_xfree, 4);   // the credit for this send
+#pragma unroll
+                for (int c = 0; c < NCH; ++c)
+                    st_async_f32x4(peer_x + c * (kHeadsPerBlock * 16), tv[4 * c], tv[4 * c + 1], tv[4 * c + 2], tv[4 * c + 3],
+                                   peer_xfull);
+                if (warp == 0 || warp == 8) PROF(2, it, 1);
+                if (!warp_wait_cluster(my_xfull, n_x & 1, abort_flag)) goto done;
+                if (warp == 0 || warp == 8) PROF(2, it, 2);
+                {
+                    const float4* src = reinterpret_cast<const float4*>(sX + x_off);
 #pragma unroll
                     for (int c = 0; c < NCH; ++c) {
                         const float4 o = src[c * kHeadsPerBlock];
-                        tv[4 * c + 0] = part[4 * c + 0] + o.x;
-                        tv[4 * c + 1] = part[4 * c + 1] + o.y;
-                        tv[4 * c + 2] = part[4 * c + 2] + o.z;
-                        tv[4 * c + 3] = part[4 * c + 3] + o.w;
+                        tv[4 * c + 0] += o.x;
+                        tv[4 * c + 1] += o.y;
+                        tv[4 * c + 2] += o.z;
+                        tv[4 * c + 3] += o.w;
                     }
                 }
-                // ---- start the exchange of the next tile before the arithmetic of this one when its
-                //      scores are already there; otherwise right after
-                bool next_sent = true;
-                if (t + 1 < n_tiles) {
-                    const uint32_t jt = it + 1;
-                    next_sent = __all_sync(0xffffffffu, mbar_test_wait(smem_u32(&ctl->s_full[jt & 1]), (jt >> 1) & 1));
-                    if (next_sent)
-                        if (!fetch_send(jt)) goto done;
+                // credit: the peer may overwrite the buffer.  The credit word is computed from every lane's
+                // loaded values, so it cannot leave before all of the warp's reads have returned.
+                {
+                    const uint32_t dep = __reduce_or_sync(0xffffffffu, __float_as_uint(tv[0]) | __float_as_uint(tv[4]) |
+                                                                           __float_as_uint(tv[8]) | __float_as_uint(tv[12]));
+                    if (lane == 0) st_async_u32(peer_xsink, dep, peer_xfree);
                 }
+                ++n_x;
                 if (!kFp8)
                     if (!warp_wait(smem_u32(&ctl->kv_full[it % S]), (it / S) & 1, abort_flag)) goto done;
                 const uint32_t mask = ctl->tile_mask[it % kMaskSlots] >> c0;
-
                 float mt = -INFINITY;
 #pragma unroll
                 for (int j = 0; j < CPT; ++j) {
@@ -548,96 +561,99 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     tv[j] = ((mask >> j) & 1u) ? x : -INFINITY;
                     mt = fmaxf(mt, tv[j]);
                 }
-                // ---- row maximum over the columns of all groups
-                if (G > 1) {
-                    ctl->row_max[sb][cg][row] = mt;
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&ctl->mx_bar[sb]));
-                    if (!warp_wait(smem_u32(&ctl->mx_bar[sb]), (it >> 1) & 1, abort_flag)) goto done;
+                // ---- row maximum over the tile's 32 columns (the two warpgroups of the team)
+                ctl->row_max[sb][chalf][row] = mt;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&ctl->mx_bar[sb]));
+                if (!warp_wait(smem_u32(&ctl->mx_bar[sb]), ph, abort_flag)) goto done;
+                mt = fmaxf(ctl->row_max[sb][0][row], ctl->row_max[sb][1][row]);
+                // ---- P against a snapshot of the reference maximum (the other team may still move it)
+                const float m_snap = first ? -INFINITY : ctl->m_shared[row];
+                const float m_c = (mt > m_snap + 8.0f) ? mt : m_snap;
+                const float m_c_use = (m_c == -INFINITY) ? 0.0f : m_c;
+                float lsum = 0.0f;
 #pragma unroll
-                    for (int g = 0; g < G; ++g) mt = fmaxf(mt, ctl->row_max[sb][g][row]);
+                for (int j = 0; j < CPT; ++j) {
+                    tv[j] = ex2_approx(tv[j] - m_c_use);
+                    lsum += tv[j];
                 }
-                // lazy rescale: move the reference maximum only when a row outgrows it by more than 8
-                const bool need = mt > m_ref + 8.0f;
-                if (__any_sync(0xffffffffu, need)) {
-                    const float m_new = need ? mt : m_ref;
-                    if (t > 0) {
-                        const float f = (m_ref == -INFINITY) ? 0.0f : ex2_approx(m_ref - m_new);
-                        l *= f;
-                        // O of this item so far is complete once the previous PV has finished
-                        const uint32_t pit = it - 1;
-                        if (!warp_wait(smem_u32(&ctl->pv_done[pit & 1]), (pit >> 1) & 1, abort_flag)) goto done;
+                if (warp == 0 || warp == 8) PROF(4, it, 1);
+                // ---- commit, in tile order: after the previous tile's commit (its P is released) ...
+                if (!first)
+                    if (!warp_wait(smem_u32(&ctl->p_full[sb ^ 1]), ((it - 1) >> 1) & 1, abort_flag)) goto done;
+                // ... and after the P V product that last read this team's P buffer
+                if (it >= 2)
+                    if (!warp_wait(smem_u32(&ctl->pv_done[sb]), ((it - 2) >> 1) & 1, abort_flag)) goto done;
+                const float m_cur = first ? -INFINITY : ctl->m_shared[row];
+                const bool raise = mt > m_cur + 8.0f;   // lazy: move the reference only past a margin of 8
+                const float m_fin = raise ? mt : m_cur;
+                const float m_fin_use = (m_fin == -INFINITY) ? 0.0f : m_fin;
+                const float f1 = (m_c == m_fin) ? 1.0f : ex2_approx(m_c_use - m_fin_use);   // snapshot -> final reference
+                if (__any_sync(0xffffffffu, raise)) {
+                    if (!first) {
+                        // O so far is complete once the previous tile's P V product has finished
+                        if (!warp_wait(smem_u32(&ctl->pv_done[sb ^ 1]), ((it - 1) >> 1) & 1, abort_flag)) goto done;
                         tc_fence_after();
+                        const float f2 = (m_cur == -INFINITY) ? 0.0f : ex2_approx(m_cur - m_fin);
 #pragma unroll 1
-                        for (int oc = cg * OCOLS; oc < (cg + 1) * OCOLS; oc += 32) {
+                        for (int oc = chalf * (kDvHalf / 2); oc < (chalf + 1) * (kDvHalf / 2); oc += 32) {
                             uint32_t o[32];
                             tmem_ld32(lane_base + kColO + oc, o);
                             tmem_wait_ld();
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * f);
+                            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * f2);
                             tmem_st32(lane_base + kColO + oc, o);
                         }
                         tmem_wait_st();
                     }
-                    m_ref = m_new;
                 }
-                if (warp == 0) PROF(4, it, 1);
-                // the P buffer of this tile was last read by the P V product of tile it - 2
-                if (t >= 2) {
-                    const uint32_t pit = it - 2;
-                    if (!warp_wait(smem_u32(&ctl->pv_done[pit & 1]), (pit >> 1) & 1, abort_flag)) goto done;
-                }
-                const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
-                float lsum = 0.0f;
-                if (kFp8) {
-                    const float(*sc)[2] = ctl->row_scale[it % S] + c0;
-                    uint32_t pk0[CPT / 2], pk1[CPT / 2];
+                if (chalf == 0 && (raise || first)) ctl->m_shared[row] = m_fin;
+                if (l_part != 0.0f && l_ref != m_fin) l_part *= ex2_approx(l_ref - m_fin);
+                l_part = fmaf(lsum, f1, l_part);
+                l_ref = m_fin;
+                {
+                    const uint32_t p0col = lane_base + kColP + sb * kPStride + chalf * (CPT / 2);
+                    if (kFp8) {
+                        const float(*sc)[2] = ctl->row_scale[it % S] + c0;
+                        uint32_t pk0[CPT / 2], pk1[CPT / 2];
 #pragma unroll
-                    for (int j = 0; j < CPT / 2; ++j) {
-                        const float p0 = ex2_approx(tv[2 * j] - m_use);
-                        const float p1 = ex2_approx(tv[2 * j + 1] - m_use);
-                        lsum += p0 + p1;
-                        const float2 wa = *reinterpret_cast<const float2*>(sc[2 * j]);
-                        const float2 wb = *reinterpret_cast<const float2*>(sc[2 * j + 1]);
-                        pk0[j] = pack_bf16x2(p0 * wa.x, p1 * wb.x);
-                        pk1[j] = pack_bf16x2(p0 * wa.y, p1 * wb.y);
-                    }
-                    tmem_st_n<CPT / 2>(lane_base + kColP + sb * kPStride + cg * (CPT / 2), pk0);
-                    tmem_st_n<CPT / 2>(lane_base + kColP + sb * kPStride + 16 + cg * (CPT / 2), pk1);
-                } else {
-                    uint32_t pk[CPT / 2];
+                        for (int j = 0; j < CPT / 2; ++j) {
+                            const float p0 = tv[2 * j] * f1, p1 = tv[2 * j + 1] * f1;
+                            const float2 wa = *reinterpret_cast<const float2*>(sc[2 * j]);
+                            const float2 wb = *reinterpret_cast<const float2*>(sc[2 * j + 1]);
+                            pk0[j] = pack_bf16x2(p0 * wa.x, p1 * wb.x);
+                            pk1[j] = pack_bf16x2(p0 * wa.y, p1 * wb.y);
+                        }
+                        tmem_st_n<CPT / 2>(p0col, pk0);
+                        tmem_st_n<CPT / 2>(p0col + 16, pk1);
+                    } else {
+                        uint32_t pk[CPT / 2];
 #pragma unroll
-                    for (int j = 0; j < CPT / 2; ++j) {
-                        const float p0 = ex2_approx(tv[2 * j] - m_use);
-                        const float p1 = ex2_approx(tv[2 * j + 1] - m_use);
-                        lsum += p0 + p1;
-                        pk[j] = pack_bf16x2(p0, p1);
+                        for (int j = 0; j < CPT / 2; ++j) pk[j] = pack_bf16x2(tv[2 * j] * f1, tv[2 * j + 1] * f1);
+                        tmem_st_n<CPT / 2>(p0col, pk);
                     }
-                    tmem_st_n<CPT / 2>(lane_base + kColP + sb * kPStride + cg * (CPT / 2), pk);
                 }
-                l += lsum;
-                if (warp == 0) PROF(4, it, 2);
+                if (warp == 0 || warp == 8) PROF(4, it, 2);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&ctl->p_full[sb]));
-                if (warp == 0) PROF(2, it, 3);
-                if (!next_sent)
-                    if (!fetch_send(it + 1)) goto done;
+                if (warp == 0 || warp == 8) PROF(2, it, 3);
             }
-            // ---- epilogue of the item
+            // ---- epilogue of the item (all sixteen warps)
             {
-                if (G > 1) {   // row sum over the groups
-                    ctl->l_part[cg][row] = l;
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&ctl->l_bar));
-                    if (!warp_wait(smem_u32(&ctl->l_bar), item_n & 1, abort_flag)) goto done;
-                    l = 0.0f;
+                const uint32_t it_last = it_end - 1;
+                // every tile of the item has been committed: the row's reference maximum is final
+                if (!warp_wait(smem_u32(&ctl->p_full[it_last & 1]), (it_last >> 1) & 1, abort_flag)) goto done;
+                const float m_ref = ctl->m_shared[row];
+                ctl->l_part[cg][row] = (l_part != 0.0f && l_ref != m_ref) ? l_part * ex2_approx(l_ref - m_ref) : l_part;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&ctl->l_bar));
+                if (!warp_wait(smem_u32(&ctl->l_bar), item_n & 1, abort_flag)) goto done;
+                float l = 0.0f;
 #pragma unroll
-                    for (int g = 0; g < G; ++g) l += ctl->l_part[g][row];
-                }
-                const uint32_t pit = it - 1;
-                if (!warp_wait(smem_u32(&ctl->pv_done[pit & 1]), (pit >> 1) & 1, abort_flag)) goto done;
+                for (int g = 0; g < G; ++g) l += ctl->l_part[g][row];
+                if (!warp_wait(smem_u32(&ctl->pv_done[it_last & 1]), (it_last >> 1) & 1, abort_flag)) goto done;
                 tc_fence_after();
                 const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
                 const int head = wi.head_block * kHeadsPerBlock + row;
@@ -685,6 +701,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&ctl->o_free));
             }
+            it_base = it_end;
         }
     } else if (kFp8) {
         // ============================================================ convert (warps 6-9)

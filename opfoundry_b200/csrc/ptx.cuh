@@ -61,6 +61,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
     for (uint32_t it = 0; it < DSA_WAIT_LIMIT; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(64);   // leave the issue slots to the warps that have work
         if ((it & 0x3FFu) == 0x3FFu && *abort_flag) return false;
     }
     *abort_flag = 1;
@@ -123,6 +124,7 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
     if (mbar_try_wait_cluster(bar, parity)) return true;
     for (uint32_t it = 0; it < DSA_WAIT_LIMIT; ++it) {
         if (mbar_try_wait_cluster(bar, parity)) return true;
+        __nanosleep(64);
         if ((it & 0x3FFu) == 0x3FFu && *abort_flag) return false;
     }
     *abort_flag = 1;

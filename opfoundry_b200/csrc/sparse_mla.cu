@@ -52,6 +52,7 @@ namespace dsa {
 // Working aid (never compiled into the shipped library): per-role time stamps of the first tiles of
 // cluster 0, to see which stage of the pipeline the others wait for.
 __device__ long long* g_prof = nullptr;
+__device__ int g_prof_list = 0;
 __device__ __forceinline__ long long prof_now() {   // one clock for all SMs (nanoseconds)
     long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -59,10 +60,11 @@ __device__ __forceinline__ long long prof_now() {   // one clock for all SMs (na
 }
 #define PROF(role, tile, slot)                                                                      \
     do {                                                                                            \
-        if (g_prof != nullptr && blockIdx.x < 2 && (tile) < 64 && lane == 0)                        \
-            g_prof[((blockIdx.x * 8 + (role)) * 64 + (tile)) * 4 + (slot)] = prof_now();            \
+        if (g_prof != nullptr && (blockIdx.x >> 1) == g_prof_list && (tile) < 64 && lane == 0)      \
+            g_prof[(((blockIdx.x & 1) * 8 + (role)) * 64 + (tile)) * 4 + (slot)] = prof_now();      \
     } while (0)
 extern "C" int dsa_v32_set_prof(long long* buf) { return (int)cudaMemcpyToSymbol(g_prof, &buf, sizeof(buf)); }
+extern "C" int dsa_v32_set_prof_list(int list) { return (int)cudaMemcpyToSymbol(g_prof_list, &list, sizeof(list)); }
 #else
 #define PROF(role, tile, slot) do { } while (0)
 #endif
@@ -86,8 +88,8 @@ constexpr int kConvertWarp0 = kSoftmaxWarps + 2;          // fp8 cache: four con
 
 template <bool kFp8>
 struct Cfg {
-    static constexpr int kKvStages = kFp8 ? 3 : 5;   // MMA-ready bf16 tiles
-    static constexpr int kRawStages = kFp8 ? 3 : 0;  // raw fp8 tiles in flight
+    static constexpr int kKvStages = kFp8 ? 4 : 5;   // MMA-ready bf16 tiles
+    static constexpr int kRawStages = kFp8 ? 2 : 0;  // raw fp8 tiles in flight
     static constexpr int kThreads = 32 * (kSoftmaxWarps + 2 + (kFp8 ? 4 : 0));
     static constexpr int kOffKv = kQBytesMax;
     static constexpr int kOffRaw = kOffKv + kKvStages * kKvTileBytes;
@@ -242,6 +244,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int w_begin = __ldg(p.list_indptr + list);
     const int w_end = __ldg(p.list_indptr + list + 1);
 
+    if (tid == 0) PROF(5, 0, 0);
     if (tid == 0) {
         mbar_init(smem_u32(&ctl->q_full), 1);
         mbar_init(smem_u32(&ctl->q_empty), 1);
@@ -282,6 +285,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     cluster_sync_all();   // the peer's barriers exist before anything is sent to it
     tc_fence_after();
     const uint32_t tmem = ctl->tmem_base;
+    if (tid == 0) PROF(5, 0, 1);
     const uint32_t peer_abort = map_to_cta(smem_u32(&ctl->abort_flag), peer);
 
     if (warp == kProducerWarp) {
@@ -430,9 +434,12 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     }
                     if (did) {
                         idle = 0;
-                    } else if (++idle > DSA_WAIT_LIMIT || ((idle & 0x3FFu) == 0 && *abort_flag)) {
-                        *abort_flag = 1;
-                        ok = false;
+                    } else {
+                        __nanosleep(100);   // nothing ready: do not spin on the issue port the other warps share
+                        if (++idle > DSA_WAIT_LIMIT || ((idle & 0x3FFu) == 0 && *abort_flag)) {
+                            *abort_flag = 1;
+                            ok = false;
+                        }
                     }
                 }
                 it_base += n_tiles;
@@ -764,7 +771,9 @@ done:
     tc_fence_before();
     __syncthreads();
     if (tid == 0 && ctl->abort_flag) atomicExch(p.status, DSA_V32_ERR_DEVICE_WAIT);
-    cluster_sync_all();   // nobody leaves while the peer may still store into this CTA's shared memory
+    if (tid == 0) PROF(5, 0, 2);
+    cluster_sync_all();
+    if (tid == 0) PROF(5, 0, 3);   // nobody leaves while the peer may still store into this CTA's shared memory
     if (warp == kMmaWarp) {
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);

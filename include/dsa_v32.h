@@ -206,7 +206,7 @@ int dsa_v32_decode_pipeline_host(const dsa_v32_attn_args* args, const dsa_v32_ho
  *     Two calls that overlap on the GPU (different streams, no dependency) race on it: serialise them.
  *   - Inputs and outputs are still the caller's buffers, exactly as in dsa_v32_decode_pipeline.
  */
-#define DSA_V32_STATIC_SCRATCH_BYTES (32u << 20)
+#define DSA_V32_STATIC_SCRATCH_BYTES (48u << 20)
 #define DSA_V32_ERR_SCRATCH_TOO_SMALL (-7)
 int dsa_v32_decode_pipeline_static(const dsa_v32_attn_args* args, void* stream);
 /* Device address of that array on the current device, NULL before the first static call there. */

@@ -18,7 +18,7 @@ BF16_ROW_BYTES, FP8_ROW_BYTES = 1152, 656
 KV_BF16, KV_FP8 = 0, 1
 ERR_DEVICE_WAIT = 1001
 ERR_SCRATCH_TOO_SMALL = -7
-STATIC_SCRATCH_BYTES = 32 << 20
+STATIC_SCRATCH_BYTES = 48 << 20
 
 
 class WorkInfo(C.Structure):
@@ -267,7 +267,7 @@ def mla_decode_step_host(args, q_host, indices_host, out_host, lse_host):
 def mla_decode_launch_pipeline_static(q, kv, indices, sm_scale, *, s_q=1, block_table=None, page_block_size=64,
                                       kv_batch_stride_rows=0, out=None, lse=None, check=True):
     """The pipeline for callers that may not allocate device memory: the split workspace is a fixed
-    array inside the library (32 MiB per GPU, shared by all calls, so calls must not overlap on the
+    array inside the library (48 MiB per GPU, shared by all calls, so calls must not overlap on the
     GPU).  The first call for a shape plans it - make that call before any stream capture.  Shapes
     whose plan does not fit raise DsaError with status ERR_SCRATCH_TOO_SMALL.  `out` / `lse` should be
     passed in by such a caller; they are only created here for convenience when omitted."""

@@ -101,10 +101,20 @@ inline int build_plan(const dsa_v32_shape& sh, int num_sms, HostPlan& P) {
         }
     };
 
+    // With little work only as many lists are used as can each get a minimum-length piece; the rest
+    // stay empty (their CTA pairs exit at once).
+    const int L_used = int(std::max<int64_t>(1, std::min<int64_t>(L, tiles_left / kMinPieceTiles)));
     for (int list = 0; list < L; ++list) {
-        const bool last_list = (list == L - 1);
-        const double left = double(tiles_left) + double(n_units - u) * kPieceOverheadTiles;
-        const double budget = left / double(L - list);
+        if (list >= L_used) {
+            P.list_indptr[list + 1] = int(P.works.size());
+            continue;
+        }
+        const bool last_list = (list == L_used - 1);
+        // pieces still to come: one per unit plus one more for every list boundary that cuts a unit
+        const int lists_left = L_used - list;
+        const double left =
+            double(tiles_left) + double(n_units - u + std::min<int64_t>(lists_left - 1, tiles_left / kMinPieceTiles)) * kPieceOverheadTiles;
+        const double budget = left / double(lists_left);
         double used = 0.0;
         while (u < n_units) {
             const int tiles = unit_tiles(u);

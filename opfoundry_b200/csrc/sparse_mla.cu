@@ -18,18 +18,24 @@
 // softmax thread stores its row of partials into the peer's exchange buffer and arrives on the
 // peer's mbarrier); both CTAs then run the same softmax on the same numbers.
 //
-// Warp roles inside a CTA:
-//   warps 0-3  softmax: one thread per head row (= TMEM lane); tcgen05.ld of the partial scores,
-//              exchange, log2-domain online softmax with lazy rescaling (the reference's threshold
-//              of 8: ..16mx4_64nx1_template.hpp:700-725), P -> bf16 -> tcgen05.st, epilogue
-//              O / l -> bf16, or fp32 partial + lse for split items
-//   warp 4     producer: reads 32 top-k slots, translates them through the block table and
+// Warp roles inside a CTA (22 warps for an fp8 cache, 18 for bf16):
+//   warps 0-15  softmax, as two teams of eight warps that take alternate 32-slot tiles (team = tile
+//              parity).  A team is two warpgroups; each owns 16 of the tile's 32 score columns and
+//              one thread per head row (= TMEM lane): tcgen05.ld of its partial scores, exchange
+//              with the peer CTA, log2-domain online softmax with lazy rescaling (the reference's
+//              threshold of 8: ..16mx4_64nx1_template.hpp:700-725), P -> bf16 -> tcgen05.st.  The
+//              teams work ahead of each other on scores but commit in tile order: the running
+//              maximum lives in shared memory, and a team that finds it moved while it worked
+//              corrects its P by the difference before storing.  Epilogue: O / l -> bf16, or the
+//              fp32 partial + lse of a split item.
+//   warp 16    producer: reads 32 top-k slots, translates them through the block table and
 //              gathers the rows with TMA tile::gather4 (bf16 cache: straight into the 128-byte
-//              swizzled MMA tile; fp8 cache: raw bytes); loads the Q slice once per item
-//   warp 5     MMA issuer: S_c = Q_c K_c^T (tcgen05.mma M=128, N=32, K=16, operands in shared
+//              swizzled MMA tile; fp8 cache: raw bytes), two tiles of index reads ahead; loads the
+//              Q slice once per item
+//   warp 17    MMA issuer: S_c = Q_c K_c^T (tcgen05.mma M=128, N=32, K=16, operands in shared
 //              memory, accumulator in TMEM), then O_c += P V_c (A = P in TMEM, B = the same
-//              gathered tile described MN-major)
-//   warps 6-9  fp8 cache only: convert e4m3 -> bf16 exactly (e4m3 has 4 significant bits) into
+//              gathered tile described MN-major); issues whichever of the two is ready first
+//   warps 18-21 fp8 cache only: convert e4m3 -> bf16 exactly (e4m3 has 4 significant bits) into
 //              the swizzled MMA tile (the reference's LDS round trip:
 //              ..mxfp8_16mx8_32nx1_template.hpp:852-864).  The per-128 fp32 scales never touch the
 //              operands: Q K^T keeps one fp32 accumulator per scale group (plus one for rope) and

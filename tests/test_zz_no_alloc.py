@@ -48,20 +48,21 @@ def test_static_scratch_matches_regular_pipeline_twice(built_lib, fp8):
 
 def test_static_scratch_rejects_shapes_beyond_its_size(built_lib):
     assert torch.cuda.is_available()
-    topk = 2048
-    # pick a batch whose plan (mostly fp32 split partials) does not fit the 32 MiB array
-    B = None
-    for cand in (85, 88, 82, 91, 94, 79, 100, 121):
-        sh, _ = api._shape(cand, 128, topk, 1, 0, None)
+    # The split partials are bounded by the number of work lists (at most two per list boundary), so only
+    # the per-unit tables of a very long query list outgrow the array: probe with one head and top-k 1.
+    H, topk = 1, 1
+    total_q = None
+    for cand in (1_700_000, 2_400_000, 4_800_000):
+        sh, _ = api._shape(cand, H, topk, 1, 0, None)
         info = api.PlanInfo()
         api._check(api.lib().dsa_v32_plan_info_get(sh, info), "dsa_v32_plan_info_get")
         if info.workspace_bytes > api.STATIC_SCRATCH_BYTES:
-            B = cand
+            total_q = cand
             break
-    assert B is not None, "no probe shape exceeds the static scratch on this device"
-    q = torch.zeros(B, 128, 576, dtype=torch.bfloat16, device="cuda")
+    assert total_q is not None, "no probe shape exceeds the static scratch on this device"
+    q = torch.zeros(total_q, H, 576, dtype=torch.bfloat16, device="cuda")
     kv = torch.zeros(4096, 576, dtype=torch.bfloat16, device="cuda")
-    idx = torch.zeros(B, topk, dtype=torch.int32, device="cuda")
+    idx = torch.zeros(total_q, topk, dtype=torch.int32, device="cuda")
     with pytest.raises(api.DsaError) as e:
         api.mla_decode_launch_pipeline_static(q, kv, idx, SCALE, kv_batch_stride_rows=0)
     assert e.value.status == api.ERR_SCRATCH_TOO_SMALL

@@ -33,7 +33,7 @@ CFG = dict(B=64, H=128, kv_len=32768, topk=2048, page=64, pad_frac=0.05, n_batch
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)
 # dram bytes (read + write) of one attention-kernel launch on the workload above, from the ncu
 # capture summarised in profiles/ (null until a capture exists for the current kernel)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 113.2e6  # 4 x 28.3 MB captured at batch 16 (profiles/sparse_mla_fp8_decode_cluster_kernel.md)
+NCU_TRAFFIC_BYTES_AT_BATCH16 = 28.46e6  # dram read + write of one launch captured at batch 16 (profiles/sparse_mla_fp8_decode_cluster_kernel.md)
 
 
 def peaks():
@@ -395,7 +395,7 @@ def main():
                     scaling="weak", vs_baseline=None, dtype="bf16 MMA, fp32 accumulate (fp8 e4m3 cache)", data="synthetic",
                     config=workload_config(),
                     roofline=dict(bound="tensor", achieved=attn_tf, peak=pk["bf16_tflops"], unit="TFLOP/s",
-                                  frac=attn_tf / pk["bf16_tflops"], traffic=NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                                  frac=attn_tf / pk["bf16_tflops"], traffic=NCU_TRAFFIC_BYTES_AT_BATCH16 * B / 16.0,
                                   peak_source=pk["source"], kernel="sparse_mla_kernel<fp8>", kernel_us=attn_ms * 1e3,
                                   flops_per_launch=step_flops, gathered_bytes_per_launch=gathered,
                                   gathered_gbs=gathered / (attn_ms * 1e-3) / 1e9, hbm_peak_gbs=pk["hbm_gbs"],

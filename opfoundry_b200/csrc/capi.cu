@@ -104,6 +104,9 @@ int check_args(const dsa_v32_attn_args* a, int want_dtype, WorkspaceHeader* hdr)
 
 void fill_params(const dsa_v32_attn_args* a, const WorkspaceHeader& h, AttnParams* p) {
     uint8_t* ws = reinterpret_cast<uint8_t*>(a->workspace);
+    p->q = a->q;
+    p->stride_q_row = a->stride_q_row;
+    p->stride_q_head = a->stride_q_head;
     p->indices = a->indices;
     p->block_table = a->block_table;
     p->out = a->out;

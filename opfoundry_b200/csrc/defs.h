@@ -36,6 +36,8 @@ struct ReduceDst {
 
 // Kernel parameters (passed by value next to the tensor maps).
 struct AttnParams {
+    const void* q;     // bf16 [total_q][H][576] with the element strides below (read directly for a bf16 cache)
+    int64_t stride_q_row, stride_q_head;
     const int32_t* indices;
     const int32_t* block_table;
     void* out;     // bf16

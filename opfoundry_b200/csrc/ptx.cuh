@@ -51,18 +51,46 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Every wait in these kernels is bounded.  When the bound runs out, or another thread of the
-// CTA already gave up, the wait returns false; the caller records a status code and the CTA
-// drains to its normal exit (TMEM is freed there).  Nothing spins forever and nothing traps.
+// try_wait with an explicit suspend-time hint: the thread is parked by the hardware until the phase
+// completes or about `ns` nanoseconds have passed, so a waiting warp neither takes issue slots from the
+// warps that have work nor sleeps past the completion (as a nanosleep back-off does).
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Every wait in these kernels is bounded, by time: a wait that has not been satisfied after
+// DSA_WAIT_BUDGET_NS gives up.  When the bound runs out, or another thread of the CTA already gave
+// up, the wait returns false; the caller records a status code and the CTA drains to its normal
+// exit (TMEM is freed there).  Nothing spins forever and nothing traps.
 #ifndef DSA_WAIT_LIMIT
-#define DSA_WAIT_LIMIT (1u << 24)
+#define DSA_WAIT_LIMIT (1u << 24)      // iteration bound of the polling loops that are not mbarrier waits
+#endif
+#ifndef DSA_WAIT_HINT_NS
+#define DSA_WAIT_HINT_NS 20000u        // one parked try_wait
+#endif
+#ifndef DSA_WAIT_BUDGET_NS
+#define DSA_WAIT_BUDGET_NS 2000000000ull
 #endif
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_ns();
     for (uint32_t it = 0; it < DSA_WAIT_LIMIT; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
-        __nanosleep(64);   // leave the issue slots to the warps that have work
-        if ((it & 0x3FFu) == 0x3FFu && *abort_flag) return false;
+        if (mbar_try_wait_hint(bar, parity, DSA_WAIT_HINT_NS)) return true;
+        if (*abort_flag) return false;
+        if (global_ns() - t0 > DSA_WAIT_BUDGET_NS) break;
     }
     *abort_flag = 1;
     return false;
@@ -119,13 +147,25 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
         : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ bool mbar_try_wait_cluster_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
 // bounded like mbar_wait; acquires at cluster scope (the data was written by the peer CTA)
 __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait_cluster(bar, parity)) return true;
+    const uint64_t t0 = global_ns();
     for (uint32_t it = 0; it < DSA_WAIT_LIMIT; ++it) {
-        if (mbar_try_wait_cluster(bar, parity)) return true;
-        __nanosleep(64);
-        if ((it & 0x3FFu) == 0x3FFu && *abort_flag) return false;
+        if (mbar_try_wait_cluster_hint(bar, parity, DSA_WAIT_HINT_NS)) return true;
+        if (*abort_flag) return false;
+        if (global_ns() - t0 > DSA_WAIT_BUDGET_NS) break;
     }
     *abort_flag = 1;
     return false;

@@ -18,7 +18,7 @@
 // softmax thread stores its row of partials into the peer's exchange buffer and arrives on the
 // peer's mbarrier); both CTAs then run the same softmax on the same numbers.
 //
-// Warp roles inside a CTA (22 warps for an fp8 cache, 18 for bf16):
+// Warp roles inside a CTA (23 warps for an fp8 cache, 19 for bf16):
 //   warps 0-15  softmax, as two teams of eight warps that take alternate 32-slot tiles (team = tile
 //              parity).  A team is two warpgroups; each owns 16 of the tile's 32 score columns and
 //              one thread per head row (= TMEM lane): tcgen05.ld of its partial scores, exchange
@@ -32,10 +32,11 @@
 //              gathers the rows with TMA tile::gather4 (bf16 cache: straight into the 128-byte
 //              swizzled MMA tile; fp8 cache: raw bytes), two tiles of index reads ahead; loads the
 //              Q slice once per item
-//   warp 17    MMA issuer: S_c = Q_c K_c^T (tcgen05.mma M=128, N=32, K=16, operands in shared
-//              memory, accumulator in TMEM), then O_c += P V_c (A = P in TMEM, B = the same
-//              gathered tile described MN-major); issues whichever of the two is ready first
-//   warps 18-21 fp8 cache only: convert e4m3 -> bf16 exactly (e4m3 has 4 significant bits) into
+//   warp 17    score MMA issuer: S_c = Q_c K_c^T (tcgen05.mma M=128, N=32, K=16, accumulator in TMEM;
+//              bf16 cache: A = the Q slice held in TMEM, fp8 cache: A = Q in shared memory)
+//   warp 18    P V MMA issuer: O_c += P V_c (A = P in TMEM, B = the same gathered tile described
+//              MN-major).  Two issuers so that neither stream waits behind the other's barriers.
+//   warps 19-22 fp8 cache only: convert e4m3 -> bf16 exactly (e4m3 has 4 significant bits) into
 //              the swizzled MMA tile (the reference's LDS round trip:
 //              ..mxfp8_16mx8_32nx1_template.hpp:852-864).  The per-128 fp32 scales never touch the
 //              operands: Q K^T keeps one fp32 accumulator per scale group (plus one for rope) and
@@ -54,15 +55,14 @@
 
 namespace dsa {
 
+
 #ifdef DSA_PROFILE
 // Working aid (never compiled into the shipped library): per-role time stamps of the first tiles of
 // cluster 0, to see which stage of the pipeline the others wait for.
 __device__ long long* g_prof = nullptr;
 __device__ int g_prof_list = 0;
-__device__ __forceinline__ long long prof_now() {   // one clock for all SMs (nanoseconds)
-    long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
+__device__ __forceinline__ long long prof_now() {   // SM-local cycle counter (cheap to read)
+    return clock64();
 }
 #define PROF(role, tile, slot)                                                                      \
     do {                                                                                            \
@@ -89,15 +89,19 @@ constexpr int kMaskSlots = 16;
 constexpr int kGroups = 4;                                // softmax warpgroups sharing a tile's columns
 constexpr int kSoftmaxWarps = 4 * kGroups;
 constexpr int kProducerWarp = kSoftmaxWarps;
-constexpr int kMmaWarp = kSoftmaxWarps + 1;
-constexpr int kConvertWarp0 = kSoftmaxWarps + 2;          // fp8 cache: four convert warps
+constexpr int kMmaWarp = kSoftmaxWarps + 1;               // issues the score MMAs (and owns the TMEM allocation)
+constexpr int kPvWarp = kSoftmaxWarps + 2;                // issues the P V MMAs
+constexpr int kConvertWarp0 = kSoftmaxWarps + 3;          // fp8 cache: four convert warps
 
 template <bool kFp8>
 struct Cfg {
-    static constexpr int kKvStages = kFp8 ? 4 : 5;   // MMA-ready bf16 tiles
+    // bf16 cache: the Q slice lives in TMEM (A operand of the score MMAs), written there by the softmax
+    // warps straight from global memory, so shared memory holds no Q and more tiles instead.
+    static constexpr bool kQInTmem = !kFp8;
+    static constexpr int kKvStages = kFp8 ? 4 : 8;   // MMA-ready bf16 tiles
     static constexpr int kRawStages = kFp8 ? 2 : 0;  // raw fp8 tiles in flight
-    static constexpr int kThreads = 32 * (kSoftmaxWarps + 2 + (kFp8 ? 4 : 0));
-    static constexpr int kOffKv = kQBytesMax;
+    static constexpr int kThreads = 32 * (kSoftmaxWarps + 3 + (kFp8 ? 4 : 0));
+    static constexpr int kOffKv = kQInTmem ? 0 : kQBytesMax;
     static constexpr int kOffRaw = kOffKv + kKvStages * kKvTileBytes;
     static constexpr int kOffX = kOffRaw + kRawStages * kRawTileBytes;
     static constexpr int kOffCtl = kOffX + 2 * kXbufBytes;
@@ -125,14 +129,15 @@ struct Ctl {
 static_assert(sizeof(Ctl) <= 8192, "control block");
 
 // TMEM columns (512 allocated).
-//   bf16 cache: O [0,256) | S 2 x 32 | P 2 x 16 (packed bf16 pairs)
+//   bf16 cache: O [0,256) | Q slice [256,416) (packed bf16 pairs, 128 or 160 used) | S 2 x 32 | P 2 x 16
 //   fp8 cache:  O [0,256) | S 2 buffers x 3 accumulators x 32 (scale group a, scale group b, rope)
 //               | P 2 buffers x 2 variants x 16
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColO = 0;
-constexpr uint32_t kColS = 256;
+constexpr uint32_t kColQ = 256;   // bf16 cache only
+template <bool kFp8> __host__ __device__ constexpr uint32_t col_s() { return kFp8 ? 256 : 416; }
 template <bool kFp8> __host__ __device__ constexpr uint32_t s_stride() { return kFp8 ? 96 : 32; }
-template <bool kFp8> __host__ __device__ constexpr uint32_t col_p() { return kColS + 2 * s_stride<kFp8>(); }
+template <bool kFp8> __host__ __device__ constexpr uint32_t col_p() { return col_s<kFp8>() + 2 * s_stride<kFp8>(); }
 
 // ------------------------------------------------------------------ index translation
 // Top-k slot value -> physical cache row, or -1 when the slot is padding / unusable.  Split in two so
@@ -186,7 +191,7 @@ __device__ __forceinline__ uint32_t e4m3x2_to_bf16x2(uint32_t hi_bytes) {
 // S_c (+)= Q_c K_c^T for one 32-row tile: NKB blocks of 64 columns, four K=16 steps each.  With an fp8
 // cache every scale group (two blocks) and the rope block get their own accumulator.
 template <bool kFp8, int NKB>
-__device__ __forceinline__ void issue_qk_mmas(uint32_t d0, uint64_t q_desc, uint64_t k_desc, uint32_t el) {
+__device__ __forceinline__ void issue_qk_mmas(uint32_t d0, uint64_t q_desc, uint32_t q_tmem, uint64_t k_desc, uint32_t el) {
     constexpr uint32_t idesc = make_idesc_bf16(kHeadsPerBlock, kTileRows, false);
 #pragma unroll
     for (int kb = 0; kb < NKB; ++kb) {
@@ -195,7 +200,7 @@ __device__ __forceinline__ void issue_qk_mmas(uint32_t d0, uint64_t q_desc, uint
             const uint64_t a = q_desc + static_cast<uint64_t>((kb * kQBlockBytes + kin * 32) >> 4);
             const uint64_t b = k_desc + static_cast<uint64_t>((kb * kKvBlockBytes + kin * 32) >> 4);
             if (kFp8) umma_ss_el(d0 + (kb >> 1) * 32, a, b, idesc, ((kb & 1) | kin) ? 1u : 0u, el);
-            else umma_ss_el(d0, a, b, idesc, (kb | kin) ? 1u : 0u, el);
+            else umma_ts_el(d0, q_tmem + kb * 32 + kin * 8, b, idesc, (kb | kin) ? 1u : 0u, el);   // A = Q from TMEM
         }
     }
 }
@@ -231,7 +236,9 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     extern __shared__ uint8_t smem_raw[];
     // Both CTAs of a cluster compute the same offsets (the dynamic shared window starts at the same
     // shared::cta address in every CTA of a launch), so a peer address is own address + mapa.
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // (offset arithmetic on the array itself, not through an integer, so that the compiler keeps every
+    // access below in the shared address space instead of falling back to generic loads and stores)
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t* sQ = smem;
     uint8_t* sKV = smem + C::kOffKv;
     uint8_t* sRaw = smem + C::kOffRaw;
@@ -252,7 +259,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
     if (tid == 0) PROF(5, 0, 0);
     if (tid == 0) {
-        mbar_init(smem_u32(&ctl->q_full), 1);
+        mbar_init(smem_u32(&ctl->q_full), C::kQInTmem ? kSoftmaxWarps : 1);
         mbar_init(smem_u32(&ctl->q_empty), 1);
         mbar_init(smem_u32(&ctl->o_free), kSoftmaxWarps);
         mbar_init(smem_u32(&ctl->l_bar), kSoftmaxWarps);
@@ -302,8 +309,9 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         for (int w = w_begin; w < w_end; ++w, ++item_n) {
             const dsa_v32_work_info wi = p.works[w];
             const int seq = wi.q_row / p.s_q;
-            if (!warp_wait(smem_u32(&ctl->q_empty), (item_n & 1) ^ 1, abort_flag)) goto done;
-            if (lane == 0) {
+            if (!C::kQInTmem)
+                if (!warp_wait(smem_u32(&ctl->q_empty), (item_n & 1) ^ 1, abort_flag)) goto done;
+            if (!C::kQInTmem && lane == 0) {
                 const uint32_t bar = smem_u32(&ctl->q_full);
                 mbar_arrive_expect_tx(bar, nkb * kQBlockBytes);
                 for (int kb = 0; kb < nkb; ++kb)
@@ -369,86 +377,60 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
         }
     } else if (warp == kMmaWarp) {
-        // ============================================================ MMA issuer
+        // ============================================================ score MMA issuer
         // The whole warp runs the loop converged (descriptors stay warp-uniform); one elected lane issues.
-        {
-            constexpr uint32_t kColP = col_p<kFp8>();
-            constexpr uint32_t kPStride = kFp8 ? 32 : 16;
-            const uint32_t el = elect_one() ? 1u : 0u;
-            const uint64_t q_desc = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);
-            const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(sKV), 16, 1024);            // K-major view
-            const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(sKV), kKvBlockBytes, 1024); // MN-major view
-            uint32_t it_base = 0;
-            int item_n = 0;
-            bool ok = true;
-            auto issue_qk = [&](uint32_t it, bool last_of_item) {
+        // Scores and P V products are issued by two different warps, each blocking on its own inputs, so
+        // neither waits behind the other's barrier round trips; the tensor pipe runs them in issue order.
+        const uint32_t el = elect_one() ? 1u : 0u;
+        const uint64_t q_desc = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);
+        const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(sKV), 16, 1024);            // K-major view
+        uint32_t it = 0;
+        int item_n = 0;
+        for (int w = w_begin; w < w_end; ++w, ++item_n) {
+            const dsa_v32_work_info wi = p.works[w];
+            const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
+            if (!warp_wait(smem_u32(&ctl->q_full), item_n & 1, abort_flag)) goto done;
+            for (int t = 0; t < n_tiles; ++t, ++it) {
                 const int s = it % S, sb = it & 1;
-                if (!warp_wait(smem_u32(&ctl->kv_full[s]), (it / S) & 1, abort_flag)) { ok = false; return; }
-                if (!warp_wait(smem_u32(&ctl->s_empty[sb]), ((it >> 1) & 1) ^ 1, abort_flag)) { ok = false; return; }
+                if (!warp_wait(smem_u32(&ctl->kv_full[s]), (it / S) & 1, abort_flag)) goto done;
+                if (!warp_wait(smem_u32(&ctl->s_empty[sb]), ((it >> 1) & 1) ^ 1, abort_flag)) goto done;
                 tc_fence_after();
                 PROF(1, it, 0);
                 const uint64_t k_desc = k_desc0 + static_cast<uint64_t>((s * kKvTileBytes) >> 4);
-                const uint32_t d0 = tmem + kColS + sb * s_stride<kFp8>();
-                if (half) issue_qk_mmas<kFp8, 5>(d0, q_desc, k_desc, el);
-                else issue_qk_mmas<kFp8, 4>(d0, q_desc, k_desc, el);
+                const uint32_t d0 = tmem + col_s<kFp8>() + sb * s_stride<kFp8>();
+                if (half) issue_qk_mmas<kFp8, 5>(d0, q_desc, tmem + kColQ, k_desc, el);
+                else issue_qk_mmas<kFp8, 4>(d0, q_desc, tmem + kColQ, k_desc, el);
+                PROF(7, it, 0);
                 tc_commit_el(smem_u32(&ctl->s_full[sb]), el);
-                if (last_of_item) tc_commit_el(smem_u32(&ctl->q_empty), el);
+                if (t + 1 == n_tiles) tc_commit_el(smem_u32(&ctl->q_empty), el);
                 PROF(1, it, 1);
-            };
-            auto issue_pv = [&](uint32_t it, bool first_of_item) {
+            }
+        }
+    } else if (warp == kPvWarp) {
+        // ============================================================ P V MMA issuer
+        constexpr uint32_t kColP = col_p<kFp8>();
+        constexpr uint32_t kPStride = kFp8 ? 32 : 16;
+        const uint32_t el = elect_one() ? 1u : 0u;
+        const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(sKV), kKvBlockBytes, 1024); // MN-major view
+        uint32_t it = 0;
+        int item_n = 0;
+        for (int w = w_begin; w < w_end; ++w, ++item_n) {
+            const dsa_v32_work_info wi = p.works[w];
+            const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
+            for (int t = 0; t < n_tiles; ++t, ++it) {
                 const int s = it % S, sb = it & 1;
-                if (!warp_wait(smem_u32(&ctl->p_full[sb]), (it >> 1) & 1, abort_flag)) { ok = false; return; }
-                if (first_of_item && item_n > 0)
-                    if (!warp_wait(smem_u32(&ctl->o_free), (item_n - 1) & 1, abort_flag)) { ok = false; return; }
+                if (!warp_wait(smem_u32(&ctl->p_full[sb]), (it >> 1) & 1, abort_flag)) goto done;
+                if (t == 0 && item_n > 0)   // the previous item's O has been read out
+                    if (!warp_wait(smem_u32(&ctl->o_free), (item_n - 1) & 1, abort_flag)) goto done;
                 tc_fence_after();
                 PROF(1, it, 2);
                 issue_pv_mmas<kFp8>(tmem + kColO, tmem + kColP + sb * kPStride,
-                                    v_desc0 + static_cast<uint64_t>((s * kKvTileBytes) >> 4), first_of_item, el);
+                                    v_desc0 + static_cast<uint64_t>((s * kKvTileBytes) >> 4), t == 0, el);
+                PROF(6, it, 0);
                 tc_commit_el(smem_u32(&ctl->kv_empty[s]), el);
+                PROF(6, it, 1);
                 tc_commit_el(smem_u32(&ctl->pv_done[sb]), el);
                 PROF(1, it, 3);
-            };
-            for (int w = w_begin; w < w_end && ok; ++w, ++item_n) {
-                const dsa_v32_work_info wi = p.works[w];
-                const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
-                if (!warp_wait(smem_u32(&ctl->q_full), item_n & 1, abort_flag)) { ok = false; break; }
-                // Scores may run up to two tiles ahead of the P V products.  Whichever of the two next
-                // steps has its inputs ready is issued first, so neither stream holds the other up.
-                const uint32_t it_end = it_base + n_tiles;
-                uint32_t qk_next = it_base, pv_next = it_base;
-                uint32_t idle = 0;
-                while (pv_next < it_end && ok) {
-                    bool did = false;
-                    if (qk_next < it_end && qk_next < pv_next + 3) {
-                        const bool ready = __all_sync(0xffffffffu,
-                            mbar_test_wait(smem_u32(&ctl->kv_full[qk_next % S]), (qk_next / S) & 1) &&
-                            mbar_test_wait(smem_u32(&ctl->s_empty[qk_next & 1]), ((qk_next >> 1) & 1) ^ 1));
-                        if (ready) {
-                            issue_qk(qk_next, qk_next + 1 == it_end);
-                            ++qk_next;
-                            did = true;
-                        }
-                    }
-                    if (ok && pv_next < qk_next) {
-                        const bool ready = __all_sync(0xffffffffu,
-                            mbar_test_wait(smem_u32(&ctl->p_full[pv_next & 1]), (pv_next >> 1) & 1));
-                        if (ready) {
-                            issue_pv(pv_next, pv_next == it_base);
-                            ++pv_next;
-                            did = true;
-                        }
-                    }
-                    if (did) {
-                        idle = 0;
-                    } else {
-                        __nanosleep(100);   // nothing ready: do not spin on the issue port the other warps share
-                        if (++idle > DSA_WAIT_LIMIT || ((idle & 0x3FFu) == 0 && *abort_flag)) {
-                            *abort_flag = 1;
-                            ok = false;
-                        }
-                    }
-                }
-                it_base += n_tiles;
             }
         }
     } else if (warp < kSoftmaxWarps) {
@@ -487,10 +469,52 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         uint32_t n_x = 0;       // exchanges this warp has done (phases of its two exchange barriers)
         int item_n = 0;
 
+        // bf16 cache: this thread's share of an item's Q slice (its head row, a quarter of the slice's
+        // columns), read from global memory one item ahead and stored into TMEM when the item starts.
+        constexpr int kQRegs = C::kQInTmem ? 40 : 1;
+        uint32_t qreg[kQRegs];
+        const int q_ncol = half ? 40 : 32;          // TMEM columns (bf16 pairs) per warp
+        auto q_fetch = [&](const dsa_v32_work_info& wq) {
+            if (C::kQInTmem) {
+                const int head = wq.head_block * kHeadsPerBlock + row;
+                const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.q) + (size_t)wq.q_row * p.stride_q_row +
+                                           (size_t)head * p.stride_q_head + col0 + 2 * cg * q_ncol;
+                const bool live = head < p.H;
+#pragma unroll
+                for (int j = 0; j < kQRegs / 4; ++j) {
+                    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                    if (live && 4 * j < q_ncol) v = __ldg(reinterpret_cast<const uint4*>(src) + j);
+                    qreg[4 * j + 0] = v.x;
+                    qreg[4 * j + 1] = v.y;
+                    qreg[4 * j + 2] = v.z;
+                    qreg[4 * j + 3] = v.w;
+                }
+            }
+        };
+        if (C::kQInTmem && w_begin < w_end) q_fetch(p.works[w_begin]);
+
         for (int w = w_begin; w < w_end; ++w, ++item_n) {
             const dsa_v32_work_info wi = p.works[w];
             const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
             const uint32_t it_end = it_base + n_tiles;
+            if (C::kQInTmem) {
+                // the score MMAs of the previous item have all read its Q
+                if (!warp_wait(smem_u32(&ctl->q_empty), (item_n & 1) ^ 1, abort_flag)) goto done;
+                tc_fence_after();
+                const uint32_t qcol = lane_base + kColQ + cg * q_ncol;
+#pragma unroll
+                for (int j = 0; j < kQRegs / 8; ++j) {
+                    if (8 * j < q_ncol) {
+                        const uint32_t v[8] = {qreg[8 * j + 0], qreg[8 * j + 1], qreg[8 * j + 2], qreg[8 * j + 3],
+                                               qreg[8 * j + 4], qreg[8 * j + 5], qreg[8 * j + 6], qreg[8 * j + 7]};
+                        tmem_st_n<8>(qcol + 8 * j, v);
+                    }
+                }
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&ctl->q_full));
+            }
             float l_part = 0.0f;        // this thread's share of the row sum, expressed against l_ref
             float l_ref = 0.0f;
             for (uint32_t it = it_base + ((team - it_base) & 1u); it < it_end; it += 2) {
@@ -505,7 +529,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 tc_fence_after();
                 if (warp == 0 || warp == 8) PROF(2, it, 0);
                 {
-                    const uint32_t s0 = lane_base + kColS + sb * s_stride<kFp8>() + c0;
+                    const uint32_t s0 = lane_base + col_s<kFp8>() + sb * s_stride<kFp8>() + c0;
                     uint32_t sr[CPT];
                     if (kFp8) {
                         const float(*sc)[2] = ctl->row_scale[it % S] + c0;
@@ -513,6 +537,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         tmem_ld_n<CPT>(s0, sr);
                         tmem_ld_n<CPT>(s0 + 32, sr2);
                         tmem_wait_ld();
+                        if (warp == 0 || warp == 8) PROF(4, it, 0);
 #pragma unroll
                         for (int j = 0; j < CPT; ++j) {
                             const float2 w2 = *reinterpret_cast<const float2*>(sc[j]);
@@ -527,6 +552,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     } else {
                         tmem_ld_n<CPT>(s0, sr);
                         tmem_wait_ld();
+                        if (warp == 0 || warp == 8) PROF(4, it, 0);
 #pragma unroll
                         for (int j = 0; j < CPT; ++j) tv[j] = __uint_as_float(sr[j]);
                     }
@@ -538,6 +564,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (n_x > 0)
                     if (!warp_wait_cluster(my_xfree, (n_x - 1) & 1, abort_flag)) goto done;
                 if (lane == 0) mbar_arrive_expect_tx(my_xfree, 4);   // the credit for this send
+                if (warp == 0 || warp == 8) PROF(7, it, 1);
 #pragma unroll
                 for (int c = 0; c < NCH; ++c)
                     st_async_f32x4(peer_x + c * (kHeadsPerBlock * 16), tv[4 * c], tv[4 * c + 1], tv[4 * c + 2], tv[4 * c + 3],
@@ -580,6 +607,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (lane == 0) mbar_arrive(smem_u32(&ctl->mx_bar[sb]));
                 if (!warp_wait(smem_u32(&ctl->mx_bar[sb]), ph, abort_flag)) goto done;
                 mt = fmaxf(ctl->row_max[sb][0][row], ctl->row_max[sb][1][row]);
+                if (warp == 0 || warp == 8) PROF(7, it, 2);
                 // ---- P against a snapshot of the reference maximum (the other team may still move it)
                 const float m_snap = first ? -INFINITY : ctl->m_shared[row];
                 const float m_c = (mt > m_snap + 8.0f) ? mt : m_snap;
@@ -597,6 +625,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 // ... and after the P V product that last read this team's P buffer
                 if (it >= 2)
                     if (!warp_wait(smem_u32(&ctl->pv_done[sb]), ((it - 2) >> 1) & 1, abort_flag)) goto done;
+                if (warp == 0 || warp == 8) PROF(7, it, 3);
                 const float m_cur = first ? -INFINITY : ctl->m_shared[row];
                 const bool raise = mt > m_cur + 8.0f;   // lazy: move the reference only past a margin of 8
                 const float m_fin = raise ? mt : m_cur;
@@ -653,6 +682,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (lane == 0) mbar_arrive(smem_u32(&ctl->p_full[sb]));
                 if (warp == 0 || warp == 8) PROF(2, it, 3);
             }
+            if (C::kQInTmem && w + 1 < w_end) q_fetch(p.works[w + 1]);   // in flight during the epilogue
             // ---- epilogue of the item (all sixteen warps)
             {
                 const uint32_t it_last = it_end - 1;
@@ -717,7 +747,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             it_base = it_end;
         }
     } else if (kFp8) {
-        // ============================================================ convert (warps 6-9)
+        // ============================================================ convert
         const int dt = tid - 32 * kConvertWarp0;   // 0..127
         const int r = dt >> 2;           // tile row 0..31
         const int qd = dt & 3;           // which 64 of this CTA's 256 latent columns

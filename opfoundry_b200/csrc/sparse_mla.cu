@@ -64,10 +64,15 @@ __device__ int g_prof_list = 0;
 __device__ __forceinline__ long long prof_now() {   // SM-local cycle counter (cheap to read)
     return clock64();
 }
+// Stamps go to a shared-memory table (a clock read and one store, no global traffic on the path being
+// measured) that the CTA copies out when it exits: tiles [kProfTile0, kProfTile0 + 12) of the list,
+// 32-bit cycle counts, in the unused tail of the control block.
+constexpr int kProfTiles = 12, kProfTile0 = 6;
 #define PROF(role, tile, slot)                                                                      \
     do {                                                                                            \
-        if (g_prof != nullptr && (blockIdx.x >> 1) == g_prof_list && (tile) < 64 && lane == 0)      \
-            g_prof[(((blockIdx.x & 1) * 8 + (role)) * 64 + (tile)) * 4 + (slot)] = prof_now();      \
+        const uint32_t pt_ = static_cast<uint32_t>(tile) - kProfTile0;                              \
+        if (prof_on && pt_ < kProfTiles && lane == 0)                                               \
+            s_prof[((role) * kProfTiles + pt_) * 4 + (slot)] = static_cast<uint32_t>(prof_now());   \
     } while (0)
 extern "C" int dsa_v32_set_prof(long long* buf) { return (int)cudaMemcpyToSymbol(g_prof, &buf, sizeof(buf)); }
 extern "C" int dsa_v32_set_prof_list(int list) { return (int)cudaMemcpyToSymbol(g_prof_list, &list, sizeof(list)); }
@@ -83,15 +88,14 @@ constexpr int kKvBlockBytes = kTileRows * 128;            // 4096: one 64-column
 constexpr int kKvTileBytes = kMaxKBlocks * kKvBlockBytes; // 20480
 constexpr int kRawGroupBytes = 1024 + 640;                // 4 rows: 4 x 256 latent bytes | 4 x 144 tail (+pad)
 constexpr int kRawTileBytes = (kTileRows / 4) * kRawGroupBytes;   // 13312
-constexpr int kRawTxBytes = kTileRows * (256 + 144);      // bytes the two gathers deliver per tile
 constexpr int kXbufBytes = kHeadsPerBlock * kTileRows * 4;        // 16384: one tile of fp32 partial scores
 constexpr int kMaskSlots = 16;
 constexpr int kGroups = 4;                                // softmax warpgroups sharing a tile's columns
 constexpr int kSoftmaxWarps = 4 * kGroups;
-constexpr int kProducerWarp = kSoftmaxWarps;
-constexpr int kMmaWarp = kSoftmaxWarps + 1;               // issues the score MMAs (and owns the TMEM allocation)
-constexpr int kPvWarp = kSoftmaxWarps + 2;                // issues the P V MMAs
-constexpr int kConvertWarp0 = kSoftmaxWarps + 3;          // fp8 cache: four convert warps
+constexpr int kMmaWarp = kSoftmaxWarps;                   // issues the score MMAs (and owns the TMEM allocation)
+constexpr int kPvWarp = kSoftmaxWarps + 1;                // issues the P V MMAs
+constexpr int kLoaderWarp0 = kSoftmaxWarps + 2;           // four loader warps (fp8 cache: they also convert)
+constexpr int kLoaderWarps = 4;
 
 template <bool kFp8>
 struct Cfg {
@@ -100,7 +104,7 @@ struct Cfg {
     static constexpr bool kQInTmem = !kFp8;
     static constexpr int kKvStages = kFp8 ? 4 : 8;   // MMA-ready bf16 tiles
     static constexpr int kRawStages = kFp8 ? 2 : 0;  // raw fp8 tiles in flight
-    static constexpr int kThreads = 32 * (kSoftmaxWarps + 3 + (kFp8 ? 4 : 0));
+    static constexpr int kThreads = 32 * (kSoftmaxWarps + 2 + kLoaderWarps);
     static constexpr int kOffKv = kQInTmem ? 0 : kQBytesMax;
     static constexpr int kOffRaw = kOffKv + kKvStages * kKvTileBytes;
     static constexpr int kOffX = kOffRaw + kRawStages * kRawTileBytes;
@@ -112,10 +116,10 @@ struct Cfg {
 struct Ctl {
     float row_max[2][2][kHeadsPerBlock];        // per team: row maxima of the two column halves of a tile
     float l_part[kGroups][kHeadsPerBlock];      // per-group row sums at the end of an item
-    float row_scale[4][kTileRows][2];  // fp8 cache: the two scales (this CTA's groups) of every tile row
+    float row_scale[4][2][kTileRows];  // fp8 cache: per tile buffer, the scales of this CTA's two groups for every tile row
     uint64_t q_full, q_empty, o_free;
     uint64_t kv_full[8], kv_empty[8];
-    uint64_t raw_full[8], raw_empty[8];
+    uint64_t raw_full[16];   // fp8 cache: [raw buffer][loader warp], bytes of that warp's eight rows
     uint64_t s_full[2], s_empty[2], p_full[2], pv_done[2];
     uint64_t mx_bar[2], l_bar;
     uint64_t x_full[kSoftmaxWarps];    // bytes of the peer's partial scores for this warp's rows / columns
@@ -250,6 +254,13 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int warp = tid >> 5;
     const int lane = tid & 31;
     const int list = blockIdx.x >> 1;
+#ifdef DSA_PROFILE
+    static_assert(sizeof(Ctl) + 8 * kProfTiles * 4 * 4 <= C::kCtlBytes, "profile table");
+    uint32_t* s_prof = reinterpret_cast<uint32_t*>(smem + C::kOffCtl + C::kCtlBytes - 8 * kProfTiles * 4 * 4);
+    const bool prof_on = g_prof != nullptr && list == g_prof_list;
+    if (prof_on)
+        for (int i = tid; i < 8 * kProfTiles * 4; i += blockDim.x) s_prof[i] = 0;
+#endif
     const int half = (int)cluster_ctarank();      // 0: columns [0,256); 1: columns [256,576)
     const int peer = half ^ 1;
     const int nkb = half ? 5 : 4;                 // 64-column blocks of this CTA's slice
@@ -264,11 +275,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         mbar_init(smem_u32(&ctl->o_free), kSoftmaxWarps);
         mbar_init(smem_u32(&ctl->l_bar), kSoftmaxWarps);
         for (int i = 0; i < 8; ++i) {
-            mbar_init(smem_u32(&ctl->kv_full[i]), kFp8 ? 4 : 1);
+            mbar_init(smem_u32(&ctl->kv_full[i]), kLoaderWarps);
             mbar_init(smem_u32(&ctl->kv_empty[i]), 1);
-            mbar_init(smem_u32(&ctl->raw_full[i]), 1);
-            mbar_init(smem_u32(&ctl->raw_empty[i]), 4);
         }
+        for (int i = 0; i < 16; ++i) mbar_init(smem_u32(&ctl->raw_full[i]), 1);
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&ctl->s_full[i]), 1);
             mbar_init(smem_u32(&ctl->s_empty[i]), kSoftmaxWarps / 2);   // one team
@@ -284,11 +294,13 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         fence_mbar_init();
     }
+    // no row has a reference maximum yet (a tile may take its snapshot before the item's first tile commits)
+    if (tid < kHeadsPerBlock) ctl->m_shared[tid] = -INFINITY;
     if (warp == kMmaWarp) {
         tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
         tmem_relinquish();
     }
-    if (warp == kProducerWarp && lane == 0) {
+    if (warp == kLoaderWarp0 && lane == 0) {
         prefetch_tensormap(&tm_q);
         prefetch_tensormap(&tm_kv);
         if (kFp8) prefetch_tensormap(&tm_kv_tail);
@@ -301,82 +313,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     if (tid == 0) PROF(5, 0, 1);
     const uint32_t peer_abort = map_to_cta(smem_u32(&ctl->abort_flag), peer);
 
-    if (warp == kProducerWarp) {
-        // ============================================================ producer
-        uint32_t it = 0;
-        int item_n = 0;
-        const int oob_row = (int)p.num_kv_rows;  // first row outside the tensor: the gather zero-fills it
-        for (int w = w_begin; w < w_end; ++w, ++item_n) {
-            const dsa_v32_work_info wi = p.works[w];
-            const int seq = wi.q_row / p.s_q;
-            if (!C::kQInTmem)
-                if (!warp_wait(smem_u32(&ctl->q_empty), (item_n & 1) ^ 1, abort_flag)) goto done;
-            if (!C::kQInTmem && lane == 0) {
-                const uint32_t bar = smem_u32(&ctl->q_full);
-                mbar_arrive_expect_tx(bar, nkb * kQBlockBytes);
-                for (int kb = 0; kb < nkb; ++kb)
-                    tma_load_3d(smem_u32(sQ + kb * kQBlockBytes), &tm_q, bar, col0 + kb * 64,
-                                wi.head_block * kHeadsPerBlock, wi.q_row);
-            }
-            const int32_t* idx_row = p.indices + (size_t)wi.q_row * p.topk;
-            // Two-deep software pipeline over tiles so no load is consumed in the iteration that issues
-            // it: slots of tiles t+2, t+3 are in flight, block numbers of tiles t, t+1 are in flight.
-            auto load_slot = [&](int k0) -> int {
-                const int k = k0 + lane;
-                return (k < wi.k_end) ? __ldg(idx_row + k) : -1;
-            };
-            int idx_a = load_slot(wi.k_begin), idx_b = load_slot(wi.k_begin + kTileRows);
-            int idx_c = load_slot(wi.k_begin + 2 * kTileRows), idx_d = load_slot(wi.k_begin + 3 * kTileRows);
-            int phys_a = block_of(idx_a, seq, p), phys_b = block_of(idx_b, seq, p);
-            for (int k0 = wi.k_begin; k0 < wi.k_end; k0 += kTileRows, ++it) {
-                const int row = row_of(idx_a, phys_a, seq, p);
-                {
-                    const int phys_n = block_of(idx_c, seq, p);
-                    const int idx_n = load_slot(k0 + 4 * kTileRows);
-                    idx_a = idx_b; phys_a = phys_b;
-                    idx_b = idx_c; phys_b = phys_n;
-                    idx_c = idx_d; idx_d = idx_n;
-                }
-                const uint32_t mask = __ballot_sync(0xffffffffu, row >= 0);
-                const int coord = row >= 0 ? row : oob_row;
-                const int g = lane & 7;
-                const int r0 = __shfl_sync(0xffffffffu, coord, 4 * g + 0);
-                const int r1 = __shfl_sync(0xffffffffu, coord, 4 * g + 1);
-                const int r2 = __shfl_sync(0xffffffffu, coord, 4 * g + 2);
-                const int r3 = __shfl_sync(0xffffffffu, coord, 4 * g + 3);
-                if (!kFp8) {
-                    const int s = it % S;
-                    if (!warp_wait(smem_u32(&ctl->kv_empty[s]), ((it / S) & 1) ^ 1, abort_flag)) goto done;
-                    const uint32_t bar = smem_u32(&ctl->kv_full[s]);
-                    if (lane == 0) {
-                        ctl->tile_mask[it % kMaskSlots] = mask;
-                        mbar_arrive_expect_tx(bar, nkb * kKvBlockBytes);
-                    }
-                    __syncwarp();
-                    if (lane < 8) {
-                        const uint32_t dst = smem_u32(sKV + s * kKvTileBytes + g * 512);
-                        for (int kb = 0; kb < nkb; ++kb)
-                            tma_gather4(dst + kb * kKvBlockBytes, &tm_kv, bar, col0 + kb * 64, r0, r1, r2, r3);
-                    }
-                } else {
-                    const int s = it % R;
-                    if (!warp_wait(smem_u32(&ctl->raw_empty[s]), ((it / R) & 1) ^ 1, abort_flag)) goto done;
-                    const uint32_t bar = smem_u32(&ctl->raw_full[s]);
-                    if (lane == 0) {
-                        ctl->tile_mask[it % kMaskSlots] = mask;
-                        mbar_arrive_expect_tx(bar, kRawTxBytes);
-                    }
-                    __syncwarp();
-                    if (lane < 8) {
-                        const uint32_t dst = smem_u32(sRaw + s * kRawTileBytes + g * kRawGroupBytes);
-                        tma_gather4(dst, &tm_kv, bar, col0, r0, r1, r2, r3);              // 256 latent bytes
-                        tma_gather4(dst + 1024, &tm_kv_tail, bar, 512, r0, r1, r2, r3);  // scales + rope
-                    }
-                }
-                PROF(0, it, 0);
-            }
-        }
-    } else if (warp == kMmaWarp) {
+    if (warp == kMmaWarp) {
         // ============================================================ score MMA issuer
         // The whole warp runs the loop converged (descriptors stay warp-uniform); one elected lane issues.
         // Scores and P V products are issued by two different warps, each blocking on its own inputs, so
@@ -444,7 +381,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         // stored and the tile is released to the MMA warp.
         constexpr uint32_t kColP = col_p<kFp8>();
         constexpr uint32_t kPStride = kFp8 ? 32 : 16;
-        constexpr int G = kGroups, CPT = 16, NCH = CPT / 4, OCOLS = kDvHalf / G;
+        constexpr int G = kGroups, CPT = 16, NP = CPT / 2, NCH = CPT / 4, OCOLS = kDvHalf / G;
         static_assert(kGroups == 4, "two teams x two column halves");
         const int cg = warp >> 2;            // warpgroup
         const int team = cg >> 1;            // tile parity this warp works on
@@ -491,13 +428,22 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 }
             }
         };
-        if (C::kQInTmem && w_begin < w_end) q_fetch(p.works[w_begin]);
+        auto q_prefetch_l2 = [&](const dsa_v32_work_info& wq) {
+            const int head = wq.head_block * kHeadsPerBlock + row;
+            if (C::kQInTmem && head < p.H) {
+                const char* src = reinterpret_cast<const char*>(reinterpret_cast<const __nv_bfloat16*>(p.q) + (size_t)wq.q_row * p.stride_q_row +
+                                                               (size_t)head * p.stride_q_head + col0 + 2 * cg * q_ncol);
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(src + 2 * q_ncol * 2 - 16));
+            }
+        };
 
         for (int w = w_begin; w < w_end; ++w, ++item_n) {
             const dsa_v32_work_info wi = p.works[w];
             const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
             const uint32_t it_end = it_base + n_tiles;
             if (C::kQInTmem) {
+                q_fetch(wi);   // from L2 when this is not the list's first item (prefetched before the last epilogue)
                 // the score MMAs of the previous item have all read its Q
                 if (!warp_wait(smem_u32(&ctl->q_empty), (item_n & 1) ^ 1, abort_flag)) goto done;
                 tc_fence_after();
@@ -520,7 +466,9 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             for (uint32_t it = it_base + ((team - it_base) & 1u); it < it_end; it += 2) {
                 const uint32_t ph = (it >> 1) & 1;
                 const bool first = (it == it_base);
-                float tv[CPT];
+                // The tile's values live in pairs (64-bit registers) so that the fp32 arithmetic on them uses the
+                // two-wide forms (fma/mul/add .f32x2): half the instructions of the scalar forms.
+                uint64_t tv2[NP];
                 // ---- own partial scores out of TMEM
                 if (lane == 0) mbar_arrive_expect_tx(my_xfull, kXbufBytes / 8);
                 if (kFp8)
@@ -532,29 +480,32 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     const uint32_t s0 = lane_base + col_s<kFp8>() + sb * s_stride<kFp8>() + c0;
                     uint32_t sr[CPT];
                     if (kFp8) {
-                        const float(*sc)[2] = ctl->row_scale[it % S] + c0;
-                        uint32_t sr2[CPT];
+                        uint32_t sr2[CPT], sr3[CPT];
                         tmem_ld_n<CPT>(s0, sr);
                         tmem_ld_n<CPT>(s0 + 32, sr2);
+                        if (half) tmem_ld_n<CPT>(s0 + 64, sr3);
                         tmem_wait_ld();
                         if (warp == 0 || warp == 8) PROF(4, it, 0);
+                        const float4* sa = reinterpret_cast<const float4*>(ctl->row_scale[it % S][0] + c0);
+                        const float4* sb4 = reinterpret_cast<const float4*>(ctl->row_scale[it % S][1] + c0);
 #pragma unroll
-                        for (int j = 0; j < CPT; ++j) {
-                            const float2 w2 = *reinterpret_cast<const float2*>(sc[j]);
-                            tv[j] = fmaf(w2.y, __uint_as_float(sr2[j]), w2.x * __uint_as_float(sr[j]));
+                        for (int j = 0; j < CPT / 4; ++j) {
+                            const float4 wa = sa[j], wb = sb4[j];
+                            tv2[2 * j] = fma2(pack2(wb.x, wb.y), pack2u(sr2[4 * j], sr2[4 * j + 1]),
+                                              mul2(pack2(wa.x, wa.y), pack2u(sr[4 * j], sr[4 * j + 1])));
+                            tv2[2 * j + 1] = fma2(pack2(wb.z, wb.w), pack2u(sr2[4 * j + 2], sr2[4 * j + 3]),
+                                                  mul2(pack2(wa.z, wa.w), pack2u(sr[4 * j + 2], sr[4 * j + 3])));
                         }
                         if (half) {
-                            tmem_ld_n<CPT>(s0 + 64, sr);
-                            tmem_wait_ld();
 #pragma unroll
-                            for (int j = 0; j < CPT; ++j) tv[j] += __uint_as_float(sr[j]);
+                            for (int j = 0; j < NP; ++j) tv2[j] = add2(tv2[j], pack2u(sr3[2 * j], sr3[2 * j + 1]));
                         }
                     } else {
                         tmem_ld_n<CPT>(s0, sr);
                         tmem_wait_ld();
                         if (warp == 0 || warp == 8) PROF(4, it, 0);
 #pragma unroll
-                        for (int j = 0; j < CPT; ++j) tv[j] = __uint_as_float(sr[j]);
+                        for (int j = 0; j < NP; ++j) tv2[j] = pack2u(sr[2 * j], sr[2 * j + 1]);
                     }
                 }
                 tc_fence_before();
@@ -566,42 +517,56 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (lane == 0) mbar_arrive_expect_tx(my_xfree, 4);   // the credit for this send
                 if (warp == 0 || warp == 8) PROF(7, it, 1);
 #pragma unroll
-                for (int c = 0; c < NCH; ++c)
-                    st_async_f32x4(peer_x + c * (kHeadsPerBlock * 16), tv[4 * c], tv[4 * c + 1], tv[4 * c + 2], tv[4 * c + 3],
-                                   peer_xfull);
+                for (int c = 0; c < NCH; ++c) {
+                    float v0, v1, v2, v3;
+                    unpack2(tv2[2 * c], v0, v1);
+                    unpack2(tv2[2 * c + 1], v2, v3);
+                    st_async_f32x4(peer_x + c * (kHeadsPerBlock * 16), v0, v1, v2, v3, peer_xfull);
+                }
                 if (warp == 0 || warp == 8) PROF(2, it, 1);
                 if (!warp_wait_cluster(my_xfull, n_x & 1, abort_flag)) goto done;
                 if (warp == 0 || warp == 8) PROF(2, it, 2);
                 {
-                    const float4* src = reinterpret_cast<const float4*>(sX + x_off);
+                    // credit: the peer may overwrite the buffer.  The credit word is computed from every lane's
+                    // loaded values, so it cannot leave before all of the warp's reads have returned.
+                    const ulonglong2* src = reinterpret_cast<const ulonglong2*>(sX + x_off);
+                    uint32_t dep = 0;
 #pragma unroll
                     for (int c = 0; c < NCH; ++c) {
-                        const float4 o = src[c * kHeadsPerBlock];
-                        tv[4 * c + 0] += o.x;
-                        tv[4 * c + 1] += o.y;
-                        tv[4 * c + 2] += o.z;
-                        tv[4 * c + 3] += o.w;
+                        const ulonglong2 o = src[c * kHeadsPerBlock];
+                        tv2[2 * c] = add2(tv2[2 * c], o.x);
+                        tv2[2 * c + 1] = add2(tv2[2 * c + 1], o.y);
+                        dep |= static_cast<uint32_t>(o.x);
                     }
-                }
-                // credit: the peer may overwrite the buffer.  The credit word is computed from every lane's
-                // loaded values, so it cannot leave before all of the warp's reads have returned.
-                {
-                    const uint32_t dep = __reduce_or_sync(0xffffffffu, __float_as_uint(tv[0]) | __float_as_uint(tv[4]) |
-                                                                           __float_as_uint(tv[8]) | __float_as_uint(tv[12]));
+                    dep = __reduce_or_sync(0xffffffffu, dep);
                     if (lane == 0) st_async_u32(peer_xsink, dep, peer_xfree);
                 }
                 ++n_x;
                 if (!kFp8)
                     if (!warp_wait(smem_u32(&ctl->kv_full[it % S]), (it / S) & 1, abort_flag)) goto done;
-                const uint32_t mask = ctl->tile_mask[it % kMaskSlots] >> c0;
-                float mt = -INFINITY;
+                // ---- mask (padding slots; the mask is the same for every row, so a full tile skips this)
+                const uint32_t mask = (ctl->tile_mask[it % kMaskSlots] >> c0) & 0xFFFFu;
+                if (mask != 0xFFFFu) {
 #pragma unroll
-                for (int j = 0; j < CPT; ++j) {
-                    const float x = tv[j] * p.scale_log2;
-                    tv[j] = ((mask >> j) & 1u) ? x : -INFINITY;
-                    mt = fmaxf(mt, tv[j]);
+                    for (int j = 0; j < NP; ++j) {
+                        float v0, v1;
+                        unpack2(tv2[j], v0, v1);
+                        if (!((mask >> (2 * j)) & 1u)) v0 = -INFINITY;
+                        if (!((mask >> (2 * j + 1)) & 1u)) v1 = -INFINITY;
+                        tv2[j] = pack2(v0, v1);
+                    }
                 }
-                // ---- row maximum over the tile's 32 columns (the two warpgroups of the team)
+                // ---- row maximum over the tile's 32 columns (the two warpgroups of the team), in the log2
+                // domain; the scale is positive, so the maximum is taken on the raw scores and scaled once
+                float mt;
+                {
+                    float v[CPT];
+#pragma unroll
+                    for (int j = 0; j < NP; ++j) unpack2(tv2[j], v[2 * j], v[2 * j + 1]);
+                    const float t0 = max3(v[0], v[1], v[2]), t1 = max3(v[3], v[4], v[5]), t2 = max3(v[6], v[7], v[8]);
+                    const float t3 = max3(v[9], v[10], v[11]), t4 = max3(v[12], v[13], v[14]);
+                    mt = fmaxf(max3(t0, t1, v[15]), max3(t2, t3, t4)) * p.scale_log2;
+                }
                 ctl->row_max[sb][chalf][row] = mt;
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&ctl->mx_bar[sb]));
@@ -612,11 +577,20 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const float m_snap = first ? -INFINITY : ctl->m_shared[row];
                 const float m_c = (mt > m_snap + 8.0f) ? mt : m_snap;
                 const float m_c_use = (m_c == -INFINITY) ? 0.0f : m_c;
-                float lsum = 0.0f;
+                float lsum;
+                {
+                    const uint64_t c2 = pack2(p.scale_log2, p.scale_log2), nm2 = pack2(-m_c_use, -m_c_use);
+                    uint64_t ls2 = pack2(0.0f, 0.0f);
 #pragma unroll
-                for (int j = 0; j < CPT; ++j) {
-                    tv[j] = ex2_approx(tv[j] - m_c_use);
-                    lsum += tv[j];
+                    for (int j = 0; j < NP; ++j) {
+                        float v0, v1;
+                        unpack2(fma2(tv2[j], c2, nm2), v0, v1);
+                        tv2[j] = pack2(ex2_approx(v0), ex2_approx(v1));
+                        ls2 = add2(ls2, tv2[j]);
+                    }
+                    float l0, l1;
+                    unpack2(ls2, l0, l1);
+                    lsum = l0 + l1;
                 }
                 if (warp == 0 || warp == 8) PROF(4, it, 1);
                 // ---- commit, in tile order: after the previous tile's commit (its P is released) ...
@@ -630,7 +604,13 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const bool raise = mt > m_cur + 8.0f;   // lazy: move the reference only past a margin of 8
                 const float m_fin = raise ? mt : m_cur;
                 const float m_fin_use = (m_fin == -INFINITY) ? 0.0f : m_fin;
-                const float f1 = (m_c == m_fin) ? 1.0f : ex2_approx(m_c_use - m_fin_use);   // snapshot -> final reference
+                float f1 = 1.0f;   // snapshot -> final reference
+                if (!__all_sync(0xffffffffu, m_c == m_fin)) {
+                    f1 = (m_c == m_fin) ? 1.0f : ex2_approx(m_c_use - m_fin_use);
+                    const uint64_t f12 = pack2(f1, f1);
+#pragma unroll
+                    for (int j = 0; j < NP; ++j) tv2[j] = mul2(tv2[j], f12);
+                }
                 if (__any_sync(0xffffffffu, raise)) {
                     if (!first) {
                         // O so far is complete once the previous tile's P V product has finished
@@ -656,23 +636,24 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 {
                     const uint32_t p0col = lane_base + kColP + sb * kPStride + chalf * (CPT / 2);
                     if (kFp8) {
-                        const float(*sc)[2] = ctl->row_scale[it % S] + c0;
-                        uint32_t pk0[CPT / 2], pk1[CPT / 2];
+                        const float4* sa = reinterpret_cast<const float4*>(ctl->row_scale[it % S][0] + c0);
+                        const float4* sb4 = reinterpret_cast<const float4*>(ctl->row_scale[it % S][1] + c0);
+                        uint32_t pk0[NP], pk1[NP];
 #pragma unroll
-                        for (int j = 0; j < CPT / 2; ++j) {
-                            const float p0 = tv[2 * j] * f1, p1 = tv[2 * j + 1] * f1;
-                            const float2 wa = *reinterpret_cast<const float2*>(sc[2 * j]);
-                            const float2 wb = *reinterpret_cast<const float2*>(sc[2 * j + 1]);
-                            pk0[j] = pack_bf16x2(p0 * wa.x, p1 * wb.x);
-                            pk1[j] = pack_bf16x2(p0 * wa.y, p1 * wb.y);
+                        for (int j = 0; j < CPT / 4; ++j) {
+                            const float4 wa = sa[j], wb = sb4[j];
+                            pk0[2 * j] = pack_bf16x2_from2(mul2(tv2[2 * j], pack2(wa.x, wa.y)));
+                            pk0[2 * j + 1] = pack_bf16x2_from2(mul2(tv2[2 * j + 1], pack2(wa.z, wa.w)));
+                            pk1[2 * j] = pack_bf16x2_from2(mul2(tv2[2 * j], pack2(wb.x, wb.y)));
+                            pk1[2 * j + 1] = pack_bf16x2_from2(mul2(tv2[2 * j + 1], pack2(wb.z, wb.w)));
                         }
-                        tmem_st_n<CPT / 2>(p0col, pk0);
-                        tmem_st_n<CPT / 2>(p0col + 16, pk1);
+                        tmem_st_n<NP>(p0col, pk0);
+                        tmem_st_n<NP>(p0col + 16, pk1);
                     } else {
-                        uint32_t pk[CPT / 2];
+                        uint32_t pk[NP];
 #pragma unroll
-                        for (int j = 0; j < CPT / 2; ++j) pk[j] = pack_bf16x2(tv[2 * j] * f1, tv[2 * j + 1] * f1);
-                        tmem_st_n<CPT / 2>(p0col, pk);
+                        for (int j = 0; j < NP; ++j) pk[j] = pack_bf16x2_from2(tv2[j]);
+                        tmem_st_n<NP>(p0col, pk);
                     }
                 }
                 if (warp == 0 || warp == 8) PROF(4, it, 2);
@@ -682,7 +663,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (lane == 0) mbar_arrive(smem_u32(&ctl->p_full[sb]));
                 if (warp == 0 || warp == 8) PROF(2, it, 3);
             }
-            if (C::kQInTmem && w + 1 < w_end) q_fetch(p.works[w + 1]);   // in flight during the epilogue
+            if (C::kQInTmem && w + 1 < w_end) q_prefetch_l2(p.works[w + 1]);   // on its way to L2 during the epilogue
             // ---- epilogue of the item (all sixteen warps)
             {
                 const uint32_t it_last = it_end - 1;
@@ -693,6 +674,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&ctl->l_bar));
                 if (!warp_wait(smem_u32(&ctl->l_bar), item_n & 1, abort_flag)) goto done;
+                // every warp has read the item's final reference; the next item starts without one (its
+                // second tile may take its snapshot before its first tile commits).  The reset is ordered
+                // before any tile of the next item by this warp's arrival on q_full.
+                if (cg == 0) ctl->m_shared[row] = -INFINITY;
                 float l = 0.0f;
 #pragma unroll
                 for (int g = 0; g < G; ++g) l += ctl->l_part[g][row];
@@ -746,59 +731,154 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
             it_base = it_end;
         }
-    } else if (kFp8) {
-        // ============================================================ convert
-        const int dt = tid - 32 * kConvertWarp0;   // 0..127
-        const int r = dt >> 2;           // tile row 0..31
-        const int qd = dt & 3;           // which 64 of this CTA's 256 latent columns
-        uint32_t it = 0;
-        for (int w = w_begin; w < w_end; ++w) {
+    } else {
+        // ============================================================ loaders (and, for an fp8 cache, converters)
+        // Four warps; warp lw owns rows [8 lw, 8 lw + 8) of every tile: it reads their top-k slots,
+        // translates them through the block table and gathers them with TMA tile::gather4 (two lanes, one
+        // per group of four rows).  One warp can start a gather4 only every ~70 cycles, several warps
+        // overlap, so the issue is spread over four.  With an fp8 cache the same warp converts the rows
+        // it gathered (raw bytes -> bf16 MMA tile), one tile behind its own gathers.
+        const int lw = warp - kLoaderWarp0;
+        const int l8 = lane & 7;
+        const int gsel = lane & 1;
+        const int g = 2 * lw + gsel;             // group of four rows an issuing lane gathers
+        const int oob_row = (int)p.num_kv_rows;  // first row outside the tensor: the gather zero-fills it
+        uint8_t* mask_bytes = reinterpret_cast<uint8_t*>(ctl->tile_mask);
+        // convert mapping (fp8): thread = (row, 64-column quarter) of this warp's eight rows
+        const int r = 8 * lw + (lane >> 2);
+        const int qd = lane & 3;
+        uint32_t it_base = 0;
+        int item_n = 0;
+        for (int w = w_begin; w < w_end; ++w, ++item_n) {
             const dsa_v32_work_info wi = p.works[w];
+            const int seq = wi.q_row / p.s_q;
             const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
-            for (int t = 0; t < n_tiles; ++t, ++it) {
-                const int rs = it % R, s = it % S;
-                if (!warp_wait(smem_u32(&ctl->raw_full[rs]), (it / R) & 1, abort_flag)) goto done;
-                if (!warp_wait(smem_u32(&ctl->kv_empty[s]), ((it / S) & 1) ^ 1, abort_flag)) goto done;
-                if (warp == kConvertWarp0) PROF(3, it, 0);
-                const uint8_t* grp = sRaw + rs * kRawTileBytes + (r >> 2) * kRawGroupBytes;
-                const int ri = r & 3;
-                const uint8_t* src = grp + ri * 256 + qd * 64;
-                const uint8_t* tail = grp + 1024 + ri * 144;
-                // the row's scales are applied to the fp32 scores and to P by the softmax warps
-                if ((qd & 1) == 0)
-                    ctl->row_scale[s][r][qd >> 1] = reinterpret_cast<const float*>(tail)[2 * half + (qd >> 1)];
-                uint8_t* dst_row = sKV + s * kKvTileBytes + qd * kKvBlockBytes + r * 128;
-#pragma unroll
-                for (int cc = 0; cc < 4; ++cc) {
-                    const int c = (cc + r) & 3;  // rotate so the rows of a warp hit different banks
-                    const uint4 raw = *reinterpret_cast<const uint4*>(src + c * 16);
-                    const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
-                    uint32_t o[8];
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        o[2 * k + 0] = e4m3x2_to_bf16x2(__byte_perm(wv[k], 0u, 0x1404u));
-                        o[2 * k + 1] = e4m3x2_to_bf16x2(__byte_perm(wv[k], 0u, 0x3424u));
-                    }
-                    // 16 bytes -> 16 bf16 = chunks 2c, 2c+1 of this thread's 128-byte block row
-                    *reinterpret_cast<uint4*>(dst_row + (((2 * c + 0) ^ (r & 7)) * 16)) = make_uint4(o[0], o[1], o[2], o[3]);
-                    *reinterpret_cast<uint4*>(dst_row + (((2 * c + 1) ^ (r & 7)) * 16)) = make_uint4(o[4], o[5], o[6], o[7]);
-                }
-                if (half) {
-                    // rope: 64 bf16 = 8 chunks into block 4; this thread copies chunks 2*qd, 2*qd+1
-                    const uint4 a = *reinterpret_cast<const uint4*>(tail + 16 + (2 * qd + 0) * 16);
-                    const uint4 b = *reinterpret_cast<const uint4*>(tail + 16 + (2 * qd + 1) * 16);
-                    uint8_t* d = sKV + s * kKvTileBytes + 4 * kKvBlockBytes + r * 128;
-                    *reinterpret_cast<uint4*>(d + (((2 * qd + 0) ^ (r & 7)) * 16)) = a;
-                    *reinterpret_cast<uint4*>(d + (((2 * qd + 1) ^ (r & 7)) * 16)) = b;
-                }
-                fence_proxy_async_smem();
-                __syncwarp();
+            if (!C::kQInTmem && lw == 0) {
+                if (!warp_wait(smem_u32(&ctl->q_empty), (item_n & 1) ^ 1, abort_flag)) goto done;
                 if (lane == 0) {
-                    mbar_arrive(smem_u32(&ctl->kv_full[s]));
-                    mbar_arrive(smem_u32(&ctl->raw_empty[rs]));
+                    const uint32_t bar = smem_u32(&ctl->q_full);
+                    mbar_arrive_expect_tx(bar, nkb * kQBlockBytes);
+                    for (int kb = 0; kb < nkb; ++kb)
+                        tma_load_3d(smem_u32(sQ + kb * kQBlockBytes), &tm_q, bar, col0 + kb * 64,
+                                    wi.head_block * kHeadsPerBlock, wi.q_row);
                 }
-                if (warp == kConvertWarp0) PROF(3, it, 1);
             }
+            const int32_t* idx_row = p.indices + (size_t)wi.q_row * p.topk;
+            // Two-deep software pipeline over tiles so no load is consumed in the step that issues it:
+            // slots of tiles u+2, u+3 are in flight, block numbers of tiles u, u+1 are in flight.
+            auto load_slot = [&](int k0) -> int {
+                const int k = k0 + 8 * lw + l8;
+                return (k < wi.k_end) ? __ldg(idx_row + k) : -1;
+            };
+            int idx_a = load_slot(wi.k_begin), idx_b = load_slot(wi.k_begin + kTileRows);
+            int idx_c = load_slot(wi.k_begin + 2 * kTileRows), idx_d = load_slot(wi.k_begin + 3 * kTileRows);
+            int phys_a = block_of(idx_a, seq, p), phys_b = block_of(idx_b, seq, p);
+            // gathers of tile u of the item (global tile number itu); false when a wait gave up
+            auto issue = [&](int u, uint32_t itu) -> bool {
+                const int k0 = wi.k_begin + u * kTileRows;
+                const int row = row_of(idx_a, phys_a, seq, p);
+                {
+                    const int phys_n = block_of(idx_c, seq, p);
+                    const int idx_n = load_slot(k0 + 4 * kTileRows);
+                    idx_a = idx_b; phys_a = phys_b;
+                    idx_b = idx_c; phys_b = phys_n;
+                    idx_c = idx_d; idx_d = idx_n;
+                }
+                const uint32_t mask8 = __ballot_sync(0xffffffffu, row >= 0) & 0xFFu;
+                const int coord = row >= 0 ? row : oob_row;
+                const int r0 = __shfl_sync(0xffffffffu, coord, 4 * gsel + 0);
+                const int r1 = __shfl_sync(0xffffffffu, coord, 4 * gsel + 1);
+                const int r2 = __shfl_sync(0xffffffffu, coord, 4 * gsel + 2);
+                const int r3 = __shfl_sync(0xffffffffu, coord, 4 * gsel + 3);
+                if (!kFp8) {
+                    const int s = itu % S;
+                    PROF(0, itu, 1);
+                    if (!warp_wait(smem_u32(&ctl->kv_empty[s]), ((itu / S) & 1) ^ 1, abort_flag)) return false;
+                    PROF(0, itu, 2);
+                    const uint32_t bar = smem_u32(&ctl->kv_full[s]);
+                    if (lane == 0) {
+                        mask_bytes[(itu % kMaskSlots) * 4 + lw] = static_cast<uint8_t>(mask8);
+                        mbar_arrive_expect_tx(bar, nkb * 8 * 128);
+                    }
+                    __syncwarp();
+                    if (lane < 2) {
+                        const uint32_t dst = smem_u32(sKV + s * kKvTileBytes + g * 512);
+                        for (int kb = 0; kb < nkb; ++kb)
+                            tma_gather4(dst + kb * kKvBlockBytes, &tm_kv, bar, col0 + kb * 64, r0, r1, r2, r3);
+                    }
+                } else {
+                    const int rs = itu % R;
+                    const uint32_t bar = smem_u32(&ctl->raw_full[rs * 4 + lw]);
+                    PROF(0, itu, 2);
+                    if (lane == 0) {
+                        mask_bytes[(itu % kMaskSlots) * 4 + lw] = static_cast<uint8_t>(mask8);
+                        mbar_arrive_expect_tx(bar, 8 * (256 + 144));
+                    }
+                    __syncwarp();
+                    if (lane < 2) {
+                        const uint32_t dst = smem_u32(sRaw + rs * kRawTileBytes + g * kRawGroupBytes);
+                        tma_gather4(dst, &tm_kv, bar, col0, r0, r1, r2, r3);              // 256 latent bytes
+                        tma_gather4(dst + 1024, &tm_kv_tail, bar, 512, r0, r1, r2, r3);  // scales + rope
+                    }
+                }
+                if (lw == 0) PROF(0, itu, 0);
+                return true;
+            };
+            if (!kFp8) {
+                for (int u = 0; u < n_tiles; ++u)
+                    if (!issue(u, it_base + u)) goto done;
+            } else {
+                // gathers run R - 1 tiles ahead of the conversion; a raw buffer is reused by the warp that
+                // read it, in program order, so it needs no "empty" barrier
+                for (int u = 0; u < R - 1 && u < n_tiles; ++u)
+                    if (!issue(u, it_base + u)) goto done;
+                for (int t = 0; t < n_tiles; ++t) {
+                    const uint32_t it = it_base + t;
+                    const int rs = it % R, s = it % S;
+                    if (t + R - 1 < n_tiles)
+                        if (!issue(t + R - 1, it + R - 1)) goto done;
+                    if (!warp_wait(smem_u32(&ctl->raw_full[rs * 4 + lw]), (it / R) & 1, abort_flag)) goto done;
+                    if (lw == 0) PROF(3, it, 2);
+                    if (!warp_wait(smem_u32(&ctl->kv_empty[s]), ((it / S) & 1) ^ 1, abort_flag)) goto done;
+                    if (lw == 0) PROF(3, it, 0);
+                    const uint8_t* grp = sRaw + rs * kRawTileBytes + (r >> 2) * kRawGroupBytes;
+                    const int ri = r & 3;
+                    const uint8_t* src = grp + ri * 256 + qd * 64;
+                    const uint8_t* tail = grp + 1024 + ri * 144;
+                    // the row's scales are applied to the fp32 scores and to P by the softmax warps
+                    if ((qd & 1) == 0)
+                        ctl->row_scale[s][qd >> 1][r] = reinterpret_cast<const float*>(tail)[2 * half + (qd >> 1)];
+                    uint8_t* dst_row = sKV + s * kKvTileBytes + qd * kKvBlockBytes + r * 128;
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) {
+                        const int c = (cc + r) & 3;  // rotate so the rows of a warp hit different banks
+                        const uint4 raw = *reinterpret_cast<const uint4*>(src + c * 16);
+                        const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
+                        uint32_t o[8];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            o[2 * k + 0] = e4m3x2_to_bf16x2(__byte_perm(wv[k], 0u, 0x1404u));
+                            o[2 * k + 1] = e4m3x2_to_bf16x2(__byte_perm(wv[k], 0u, 0x3424u));
+                        }
+                        // 16 bytes -> 16 bf16 = chunks 2c, 2c+1 of this thread's 128-byte block row
+                        *reinterpret_cast<uint4*>(dst_row + (((2 * c + 0) ^ (r & 7)) * 16)) = make_uint4(o[0], o[1], o[2], o[3]);
+                        *reinterpret_cast<uint4*>(dst_row + (((2 * c + 1) ^ (r & 7)) * 16)) = make_uint4(o[4], o[5], o[6], o[7]);
+                    }
+                    if (half) {
+                        // rope: 64 bf16 = 8 chunks into block 4; this thread copies chunks 2*qd, 2*qd+1
+                        const uint4 a = *reinterpret_cast<const uint4*>(tail + 16 + (2 * qd + 0) * 16);
+                        const uint4 b = *reinterpret_cast<const uint4*>(tail + 16 + (2 * qd + 1) * 16);
+                        uint8_t* d = sKV + s * kKvTileBytes + 4 * kKvBlockBytes + r * 128;
+                        *reinterpret_cast<uint4*>(d + (((2 * qd + 0) ^ (r & 7)) * 16)) = a;
+                        *reinterpret_cast<uint4*>(d + (((2 * qd + 1) ^ (r & 7)) * 16)) = b;
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&ctl->kv_full[s]));
+                    if (lw == 0) PROF(3, it, 1);
+                }
+            }
+            it_base += n_tiles;
         }
     }
 
@@ -808,6 +888,10 @@ done:
     __syncthreads();
     if (tid == 0 && ctl->abort_flag) atomicExch(p.status, DSA_V32_ERR_DEVICE_WAIT);
     if (tid == 0) PROF(5, 0, 2);
+#ifdef DSA_PROFILE
+    if (prof_on)
+        for (int i = tid; i < 8 * kProfTiles * 4; i += blockDim.x) g_prof[(blockIdx.x & 1) * 8 * kProfTiles * 4 + i] = s_prof[i];
+#endif
     cluster_sync_all();
     if (tid == 0) PROF(5, 0, 3);   // nobody leaves while the peer may still store into this CTA's shared memory
     if (warp == kMmaWarp) {

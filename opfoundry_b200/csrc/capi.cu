@@ -102,9 +102,18 @@ int check_args(const dsa_v32_attn_args* a, int want_dtype, WorkspaceHeader* hdr)
     return DSA_V32_OK;
 }
 
+// page size and, when it is a power of two, its log2 (the kernels then shift and mask instead of dividing)
+void set_page(AttnParams* p, int page_block_size) {
+    p->page_block_size = page_block_size > 0 ? page_block_size : 1;
+    p->page_shift = -1;
+    for (int sh = 0; sh < 31; ++sh)
+        if (p->page_block_size == (1 << sh)) p->page_shift = sh;
+}
+
 void fill_params(const dsa_v32_attn_args* a, const WorkspaceHeader& h, AttnParams* p) {
     uint8_t* ws = reinterpret_cast<uint8_t*>(a->workspace);
     p->q = a->q;
+    p->kv = a->kv;
     p->stride_q_row = a->stride_q_row;
     p->stride_q_head = a->stride_q_head;
     p->indices = a->indices;
@@ -124,7 +133,7 @@ void fill_params(const dsa_v32_attn_args* a, const WorkspaceHeader& h, AttnParam
     p->topk = a->topk;
     p->s_q = a->s_q;
     p->block_table_stride = a->block_table_stride;
-    p->page_block_size = a->page_block_size > 0 ? a->page_block_size : 1;
+    set_page(p, a->page_block_size);
     p->scale_log2 = a->sm_scale * 1.4426950408889634f;
 }
 
@@ -151,13 +160,16 @@ int launch_attention(const dsa_v32_attn_args* a, int want_dtype, cudaStream_t st
             return DSA_V32_ERR_DRIVER;
         ttail = tkv;
     } else {
-        const uint64_t dims[2] = {uint64_t(kFp8RowBytes), uint64_t(a->num_kv_rows)};
+        // the 656-byte rows seen as 164 32-bit elements (a box may then be wider than 256 bytes):
+        // CTA 0 gathers elements [0, 64) = its 256 latent bytes, CTA 1 elements [64, 164) = its 256 latent
+        // bytes + the 16 scale bytes + the 128 rope bytes
+        const uint64_t dims[2] = {uint64_t(kFp8RowBytes / 4), uint64_t(a->num_kv_rows)};
         const uint64_t str[1] = {uint64_t(kFp8RowBytes)};
-        const uint32_t box_a[2] = {256, 1};
-        const uint32_t box_b[2] = {144, 1};
-        if (make_tmap(&tkv, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a->kv, dims, str, box_a, CU_TENSOR_MAP_SWIZZLE_NONE))
+        const uint32_t box_a[2] = {64, 1};
+        const uint32_t box_b[2] = {100, 1};
+        if (make_tmap(&tkv, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, a->kv, dims, str, box_a, CU_TENSOR_MAP_SWIZZLE_NONE))
             return DSA_V32_ERR_DRIVER;
-        if (make_tmap(&ttail, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a->kv, dims, str, box_b, CU_TENSOR_MAP_SWIZZLE_NONE))
+        if (make_tmap(&ttail, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, a->kv, dims, str, box_b, CU_TENSOR_MAP_SWIZZLE_NONE))
             return DSA_V32_ERR_DRIVER;
     }
     cudaError_t e = launch_attn(fp8, h.num_lists, tq, tkv, ttail, p, stream);
@@ -431,7 +443,7 @@ int dsa_v32_debug_rows(const dsa_v32_attn_args* a, int32_t* rows_out, void* stre
     p.topk = a->topk;
     p.s_q = a->s_q;
     p.block_table_stride = a->block_table_stride;
-    p.page_block_size = a->page_block_size > 0 ? a->page_block_size : 1;
+    set_page(&p, a->page_block_size);
     cudaError_t e = launch_debug_rows(p, a->total_q, rows_out, (cudaStream_t)stream);
     return e == cudaSuccess ? DSA_V32_OK : (int)e;
 }

@@ -36,6 +36,7 @@ struct ReduceDst {
 
 // Kernel parameters (passed by value next to the tensor maps).
 struct AttnParams {
+    const void* kv;    // the cache (read directly for the row scales of an fp8 cache)
     const void* q;     // bf16 [total_q][H][576] with the element strides below (read directly for a bf16 cache)
     int64_t stride_q_row, stride_q_head;
     const int32_t* indices;
@@ -51,6 +52,7 @@ struct AttnParams {
     int64_t kv_batch_stride_rows;
     int64_t num_kv_rows;
     int32_t H, topk, s_q, block_table_stride, page_block_size;
+    int32_t page_shift;  // log2(page_block_size) when that is a power of two, else -1
     float scale_log2;  // sm_scale * log2(e)
 };
 

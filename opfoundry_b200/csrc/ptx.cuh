@@ -212,6 +212,16 @@ __device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap* m, 
         : "memory");
 }
 
+// 4-byte asynchronous copy global -> shared (src_bytes = 0 writes zeros without reading), and an
+// mbarrier arrival that happens when all earlier cp.async of this thread have landed (it counts
+// against the barrier's expected arrivals).
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
 // ------------------------------------------------------------------ TMEM
 // Executed by one full warp.  Writes the allocated base address to *smem_dst.
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
@@ -438,6 +448,15 @@ __device__ __forceinline__ uint32_t pack_bf16x2_from2(uint64_t v) {
     uint32_t r;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
+}
+// four e4m3 bytes -> four f16 (exact: every e4m3 value is an f16 value; the NaN code stays NaN)
+__device__ __forceinline__ void e4m3x4_to_f16x4(uint32_t w, uint32_t& lo, uint32_t& hi) {
+    asm("{\n\t.reg .b16 l, h;\n\t"
+        "mov.b32 {l, h}, %2;\n\t"
+        "cvt.rn.f16x2.e4m3x2 %0, l;\n\t"
+        "cvt.rn.f16x2.e4m3x2 %1, h;\n\t}"
+        : "=r"(lo), "=r"(hi)
+        : "r"(w));
 }
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;

@@ -83,7 +83,6 @@ extern "C" int dsa_v32_set_prof_list(int list) { return (int)cudaMemcpyToSymbol(
 // ------------------------------------------------------------------ shared-memory map
 constexpr int kMaxKBlocks = 5;                            // 64-column blocks per CTA: 4 (CTA 0) or 5 (CTA 1)
 constexpr int kQBlockBytes = kHeadsPerBlock * 128;        // 16384
-constexpr int kQBytesMax = kMaxKBlocks * kQBlockBytes;    // 81920
 constexpr int kKvBlockBytes = kTileRows * 128;            // 4096: one 64-column block of a 32-row tile
 constexpr int kKvTileBytes = kMaxKBlocks * kKvBlockBytes; // 20480
 constexpr int kRawGroupBytes = 1024 + 640;                // 4 rows: 4 x 256 latent bytes | 4 x 144 tail (+pad)
@@ -94,32 +93,38 @@ constexpr int kGroups = 4;                                // softmax warpgroups 
 constexpr int kSoftmaxWarps = 4 * kGroups;
 constexpr int kMmaWarp = kSoftmaxWarps;                   // issues the score MMAs (and owns the TMEM allocation)
 constexpr int kPvWarp = kSoftmaxWarps + 1;                // issues the P V MMAs
-constexpr int kLoaderWarp0 = kSoftmaxWarps + 2;           // four loader warps (fp8 cache: they also convert)
+constexpr int kLoaderWarp0 = kSoftmaxWarps + 2;           // bf16 cache: four loader warps (two more stay idle)
 constexpr int kLoaderWarps = 4;
+constexpr int kGatherWarp0 = kSoftmaxWarps + 2;           // fp8 cache: two gather issuers ...
+constexpr int kGatherWarps = 2;
+constexpr int kConvertWarp0 = kGatherWarp0 + kGatherWarps; // ... and four converters
+constexpr int kScaleSlots = 16;                           // tiles whose row scales are kept (raw ring + tile ring <= 16)
 
 template <bool kFp8>
 struct Cfg {
-    // bf16 cache: the Q slice lives in TMEM (A operand of the score MMAs), written there by the softmax
-    // warps straight from global memory, so shared memory holds no Q and more tiles instead.
-    static constexpr bool kQInTmem = !kFp8;
-    static constexpr int kKvStages = kFp8 ? 4 : 8;   // MMA-ready bf16 tiles
-    static constexpr int kRawStages = kFp8 ? 2 : 0;  // raw fp8 tiles in flight
-    static constexpr int kThreads = 32 * (kSoftmaxWarps + 2 + kLoaderWarps);
-    static constexpr int kOffKv = kQInTmem ? 0 : kQBytesMax;
+    // The Q slice lives in TMEM (A operand of the score MMAs), written there by the softmax warps straight
+    // from global memory.  Only the rope block of an fp8 item stays in shared memory (TMEM is full).
+    static constexpr bool kQInTmem = true;
+    static constexpr int kQSmemBytes = kFp8 ? kQBlockBytes : 0;
+    static constexpr int kKvStages = kFp8 ? 5 : 8;   // MMA-ready bf16 tiles
+    static constexpr int kRawStages = kFp8 ? 5 : 0;  // raw fp8 tiles in flight (gathers run kRawStages - 1 tiles ahead)
+    static constexpr int kThreads = 32 * (kSoftmaxWarps + 2 + 6);
+    static constexpr int kOffKv = kQSmemBytes;
     static constexpr int kOffRaw = kOffKv + kKvStages * kKvTileBytes;
     static constexpr int kOffX = kOffRaw + kRawStages * kRawTileBytes;
     static constexpr int kOffCtl = kOffX + 2 * kXbufBytes;
-    static constexpr int kCtlBytes = 8192;
+    static constexpr int kCtlBytes = 12288;
     static constexpr int kSmemBytes = kOffCtl + kCtlBytes + 1024;  // + slack for 1024-byte alignment
 };
 
 struct Ctl {
     float row_max[2][2][kHeadsPerBlock];        // per team: row maxima of the two column halves of a tile
     float l_part[kGroups][kHeadsPerBlock];      // per-group row sums at the end of an item
-    float row_scale[4][2][kTileRows];  // fp8 cache: per tile buffer, the scales of this CTA's two groups for every tile row
+    float row_scale[kScaleSlots][2][kTileRows];  // fp8 cache: per tile buffer, the scales of this CTA's two groups for every tile row
     uint64_t q_full, q_empty, o_free;
     uint64_t kv_full[8], kv_empty[8];
-    uint64_t raw_full[16];   // fp8 cache: [raw buffer][loader warp], bytes of that warp's eight rows
+    uint64_t raw_full[16];   // fp8 cache: [raw buffer][gather warp]: that warp's sixteen rows and their scales have landed
+    uint64_t raw_empty[16];  // ... and both converter warps that read them are done
     uint64_t s_full[2], s_empty[2], p_full[2], pv_done[2];
     uint64_t mx_bar[2], l_bar;
     uint64_t x_full[kSoftmaxWarps];    // bytes of the peer's partial scores for this warp's rows / columns
@@ -130,18 +135,27 @@ struct Ctl {
     uint32_t tmem_base;
     int abort_flag;
 };
-static_assert(sizeof(Ctl) <= 8192, "control block");
+static_assert(sizeof(Ctl) <= 10752, "control block (the rest of its 12 KB holds the profile table of profile builds)");
 
 // TMEM columns (512 allocated).
 //   bf16 cache: O [0,256) | Q slice [256,416) (packed bf16 pairs, 128 or 160 used) | S 2 x 32 | P 2 x 16
-//   fp8 cache:  O [0,256) | S 2 buffers x 3 accumulators x 32 (scale group a, scale group b, rope)
-//               | P 2 buffers x 2 variants x 16
+//   fp8 cache:  O [0,256) | latent Q slice [256,384) | one score buffer of 3 accumulators x 32 (scale
+//               group a, scale group b, rope) | one P buffer of 2 variants x 16.  Single buffers: the
+//               scores are drained into registers right after they complete, and P is rewritten right
+//               after the product that read it.
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColO = 0;
-constexpr uint32_t kColQ = 256;   // bf16 cache only
-template <bool kFp8> __host__ __device__ constexpr uint32_t col_s() { return kFp8 ? 256 : 416; }
-template <bool kFp8> __host__ __device__ constexpr uint32_t s_stride() { return kFp8 ? 96 : 32; }
-template <bool kFp8> __host__ __device__ constexpr uint32_t col_p() { return col_s<kFp8>() + 2 * s_stride<kFp8>(); }
+constexpr uint32_t kColQ = 256;
+template <bool kFp8> __host__ __device__ constexpr uint32_t col_s() { return kFp8 ? 384 : 416; }
+template <bool kFp8> __host__ __device__ constexpr uint32_t col_p() { return 480; }
+// The per-tile barriers (s_full, s_empty, p_full, pv_done) always come in pairs indexed by the tile's
+// parity (= the softmax team that works on it), also where the TMEM buffer behind them is single: a team
+// that runs ahead must not take the other team's completion for its own.
+template <bool kFp8> __device__ __forceinline__ uint32_t buf_of(uint32_t it) { return it & 1u; }
+template <bool kFp8> __device__ __forceinline__ uint32_t phase_of(uint32_t it) { return (it >> 1) & 1u; }
+template <bool kFp8> constexpr uint32_t kBufReuse = kFp8 ? 1u : 2u;   // tiles between two uses of a score / P buffer
+template <bool kFp8> __device__ __forceinline__ uint32_t s_col_of(uint32_t it) { return col_s<kFp8>() + (kFp8 ? 0u : (it & 1u) * 32u); }
+template <bool kFp8> __device__ __forceinline__ uint32_t p_col_of(uint32_t it) { return col_p<kFp8>() + (kFp8 ? 0u : (it & 1u) * 16u); }
 
 // ------------------------------------------------------------------ index translation
 // Top-k slot value -> physical cache row, or -1 when the slot is padding / unusable.  Split in two so
@@ -150,7 +164,7 @@ template <bool kFp8> __host__ __device__ constexpr uint32_t col_p() { return col
 //   row_of(idx, phys)    the physical row from the loaded block number
 __device__ __forceinline__ int block_of(int idx, int seq, const AttnParams& p) {
     if (idx < 0 || p.block_table == nullptr) return 0;
-    const int blk = idx / p.page_block_size;
+    const int blk = p.page_shift >= 0 ? (idx >> p.page_shift) : idx / p.page_block_size;
     if (blk >= p.block_table_stride) return -1;
     return __ldg(p.block_table + (size_t)seq * p.block_table_stride + blk);
 }
@@ -159,7 +173,8 @@ __device__ __forceinline__ int row_of(int idx, int phys, int seq, const AttnPara
     long long row;
     if (p.block_table != nullptr) {
         if (phys < 0) return -1;
-        row = (long long)phys * p.page_block_size + (idx % p.page_block_size);
+        const int in_page = p.page_shift >= 0 ? (idx & (p.page_block_size - 1)) : idx % p.page_block_size;
+        row = (long long)phys * p.page_block_size + in_page;
     } else {
         row = (long long)seq * p.kv_batch_stride_rows + idx;
     }
@@ -195,16 +210,19 @@ __device__ __forceinline__ uint32_t e4m3x2_to_bf16x2(uint32_t hi_bytes) {
 // S_c (+)= Q_c K_c^T for one 32-row tile: NKB blocks of 64 columns, four K=16 steps each.  With an fp8
 // cache every scale group (two blocks) and the rope block get their own accumulator.
 template <bool kFp8, int NKB>
-__device__ __forceinline__ void issue_qk_mmas(uint32_t d0, uint64_t q_desc, uint32_t q_tmem, uint64_t k_desc, uint32_t el) {
+__device__ __forceinline__ void issue_qk_mmas(uint32_t d0, uint64_t q_rope_desc, uint32_t q_tmem, uint64_t k_desc, uint32_t el) {
     constexpr uint32_t idesc = make_idesc_bf16(kHeadsPerBlock, kTileRows, false);
 #pragma unroll
     for (int kb = 0; kb < NKB; ++kb) {
 #pragma unroll
         for (int kin = 0; kin < 4; ++kin) {
-            const uint64_t a = q_desc + static_cast<uint64_t>((kb * kQBlockBytes + kin * 32) >> 4);
             const uint64_t b = k_desc + static_cast<uint64_t>((kb * kKvBlockBytes + kin * 32) >> 4);
-            if (kFp8) umma_ss_el(d0 + (kb >> 1) * 32, a, b, idesc, ((kb & 1) | kin) ? 1u : 0u, el);
-            else umma_ts_el(d0, q_tmem + kb * 32 + kin * 8, b, idesc, (kb | kin) ? 1u : 0u, el);   // A = Q from TMEM
+            if (!kFp8)
+                umma_ts_el(d0, q_tmem + kb * 32 + kin * 8, b, idesc, (kb | kin) ? 1u : 0u, el);   // A = Q from TMEM
+            else if (kb < 4)
+                umma_ts_el(d0 + (kb >> 1) * 32, q_tmem + kb * 32 + kin * 8, b, idesc, ((kb & 1) | kin) ? 1u : 0u, el);
+            else   // rope block of an fp8 item: A from shared memory, its own accumulator
+                umma_ss_el(d0 + 64, q_rope_desc + static_cast<uint64_t>((kin * 32) >> 4), b, idesc, kin ? 1u : 0u, el);
         }
     }
 }
@@ -270,7 +288,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
     if (tid == 0) PROF(5, 0, 0);
     if (tid == 0) {
-        mbar_init(smem_u32(&ctl->q_full), C::kQInTmem ? kSoftmaxWarps : 1);
+        mbar_init(smem_u32(&ctl->q_full), kSoftmaxWarps + ((kFp8 && half) ? 1 : 0));   // + the rope block's TMA
         mbar_init(smem_u32(&ctl->q_empty), 1);
         mbar_init(smem_u32(&ctl->o_free), kSoftmaxWarps);
         mbar_init(smem_u32(&ctl->l_bar), kSoftmaxWarps);
@@ -278,7 +296,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             mbar_init(smem_u32(&ctl->kv_full[i]), kLoaderWarps);
             mbar_init(smem_u32(&ctl->kv_empty[i]), 1);
         }
-        for (int i = 0; i < 16; ++i) mbar_init(smem_u32(&ctl->raw_full[i]), 1);
+        for (int i = 0; i < 16; ++i) {
+            mbar_init(smem_u32(&ctl->raw_full[i]), 1 + 16);   // the expect_tx arrival + sixteen cp.async arrivals
+            mbar_init(smem_u32(&ctl->raw_empty[i]), 2);
+        }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&ctl->s_full[i]), 1);
             mbar_init(smem_u32(&ctl->s_empty[i]), kSoftmaxWarps / 2);   // one team
@@ -294,8 +315,6 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         fence_mbar_init();
     }
-    // no row has a reference maximum yet (a tile may take its snapshot before the item's first tile commits)
-    if (tid < kHeadsPerBlock) ctl->m_shared[tid] = -INFINITY;
     if (warp == kMmaWarp) {
         tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
         tmem_relinquish();
@@ -328,13 +347,17 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
             if (!warp_wait(smem_u32(&ctl->q_full), item_n & 1, abort_flag)) goto done;
             for (int t = 0; t < n_tiles; ++t, ++it) {
-                const int s = it % S, sb = it & 1;
+                const int s = it % S;
+                const uint32_t sb = buf_of<kFp8>(it);
                 if (!warp_wait(smem_u32(&ctl->kv_full[s]), (it / S) & 1, abort_flag)) goto done;
-                if (!warp_wait(smem_u32(&ctl->s_empty[sb]), ((it >> 1) & 1) ^ 1, abort_flag)) goto done;
+                // the softmax warps have drained the tile that used this score buffer last
+                if (it >= kBufReuse<kFp8>)
+                    if (!warp_wait(smem_u32(&ctl->s_empty[buf_of<kFp8>(it - kBufReuse<kFp8>)]), phase_of<kFp8>(it - kBufReuse<kFp8>), abort_flag))
+                        goto done;
                 tc_fence_after();
                 PROF(1, it, 0);
                 const uint64_t k_desc = k_desc0 + static_cast<uint64_t>((s * kKvTileBytes) >> 4);
-                const uint32_t d0 = tmem + col_s<kFp8>() + sb * s_stride<kFp8>();
+                const uint32_t d0 = tmem + s_col_of<kFp8>(it);
                 if (half) issue_qk_mmas<kFp8, 5>(d0, q_desc, tmem + kColQ, k_desc, el);
                 else issue_qk_mmas<kFp8, 4>(d0, q_desc, tmem + kColQ, k_desc, el);
                 PROF(7, it, 0);
@@ -345,8 +368,6 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
     } else if (warp == kPvWarp) {
         // ============================================================ P V MMA issuer
-        constexpr uint32_t kColP = col_p<kFp8>();
-        constexpr uint32_t kPStride = kFp8 ? 32 : 16;
         const uint32_t el = elect_one() ? 1u : 0u;
         const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(sKV), kKvBlockBytes, 1024); // MN-major view
         uint32_t it = 0;
@@ -355,13 +376,14 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             const dsa_v32_work_info wi = p.works[w];
             const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
             for (int t = 0; t < n_tiles; ++t, ++it) {
-                const int s = it % S, sb = it & 1;
-                if (!warp_wait(smem_u32(&ctl->p_full[sb]), (it >> 1) & 1, abort_flag)) goto done;
+                const int s = it % S;
+                const uint32_t sb = buf_of<kFp8>(it);
+                if (!warp_wait(smem_u32(&ctl->p_full[sb]), phase_of<kFp8>(it), abort_flag)) goto done;
                 if (t == 0 && item_n > 0)   // the previous item's O has been read out
                     if (!warp_wait(smem_u32(&ctl->o_free), (item_n - 1) & 1, abort_flag)) goto done;
                 tc_fence_after();
                 PROF(1, it, 2);
-                issue_pv_mmas<kFp8>(tmem + kColO, tmem + kColP + sb * kPStride,
+                issue_pv_mmas<kFp8>(tmem + kColO, tmem + p_col_of<kFp8>(it),
                                     v_desc0 + static_cast<uint64_t>((s * kKvTileBytes) >> 4), t == 0, el);
                 PROF(6, it, 0);
                 tc_commit_el(smem_u32(&ctl->kv_empty[s]), el);
@@ -376,11 +398,9 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         // index), so two tiles are in flight through the long part of a step (TMEM load, exchange, mask,
         // max, exp).  Inside a team, warpgroup `chalf` owns 16 of the tile's 32 columns; thread = (head
         // row, chalf).  Only the short commit of a tile is ordered after the commit of the tile before:
-        // there the shared reference maximum of the row is re-read, P (computed against a snapshot) is
-        // corrected to it, O is rescaled in the rare case the reference moves (lazy threshold 8), P is
-        // stored and the tile is released to the MMA warp.
-        constexpr uint32_t kColP = col_p<kFp8>();
-        constexpr uint32_t kPStride = kFp8 ? 32 : 16;
+        // there the shared reference maximum of the row is read, P (computed against the tile's own row
+        // maximum) is brought to it, O is rescaled in the rare case the reference moves (lazy threshold 8),
+        // P is stored and the tile is released to the MMA warp.
         constexpr int G = kGroups, CPT = 16, NP = CPT / 2, NCH = CPT / 4, OCOLS = kDvHalf / G;
         static_assert(kGroups == 4, "two teams x two column halves");
         const int cg = warp >> 2;            // warpgroup
@@ -389,7 +409,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const int quad = warp & 3;           // TMEM lane quadrant this warp may touch
         const int row = quad * 32 + lane;    // head row inside the block == TMEM lane
         const int c0 = chalf * CPT;
-        const int sb = team;                 // buffer index of everything double-buffered per tile
+        const int sb = team;                 // exchange buffer, row-maximum scratch and its barrier: one per team
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(quad * 32) << 16);
         // exchange buffer of a tile: [8 chunks of 4 columns][128 rows][16 bytes]
         const uint32_t x_off = static_cast<uint32_t>(sb * kXbufBytes) +
@@ -408,9 +428,9 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
         // bf16 cache: this thread's share of an item's Q slice (its head row, a quarter of the slice's
         // columns), read from global memory one item ahead and stored into TMEM when the item starts.
-        constexpr int kQRegs = C::kQInTmem ? 40 : 1;
+        constexpr int kQRegs = kFp8 ? 32 : 40;
         uint32_t qreg[kQRegs];
-        const int q_ncol = half ? 40 : 32;          // TMEM columns (bf16 pairs) per warp
+        const int q_ncol = (!kFp8 && half) ? 40 : 32;   // TMEM columns (bf16 pairs) per warp; fp8: latent columns only
         auto q_fetch = [&](const dsa_v32_work_info& wq) {
             if (C::kQInTmem) {
                 const int head = wq.head_block * kHeadsPerBlock + row;
@@ -442,10 +462,12 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             const dsa_v32_work_info wi = p.works[w];
             const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
             const uint32_t it_end = it_base + n_tiles;
-            if (C::kQInTmem) {
-                q_fetch(wi);   // from L2 when this is not the list's first item (prefetched before the last epilogue)
-                // the score MMAs of the previous item have all read its Q
-                if (!warp_wait(smem_u32(&ctl->q_empty), (item_n & 1) ^ 1, abort_flag)) goto done;
+            // Q of item n goes into TMEM once the score MMAs of item n - 1 have all read theirs: for the
+            // list's first item here, for every later item during the epilogue of the item before it (so
+            // the next item's scores start while this item's output is still being written).
+            auto q_store = [&](const dsa_v32_work_info& wq, int n) -> bool {
+                q_fetch(wq);
+                if (!warp_wait(smem_u32(&ctl->q_empty), (n & 1) ^ 1, abort_flag)) return false;
                 tc_fence_after();
                 const uint32_t qcol = lane_base + kColQ + cg * q_ncol;
 #pragma unroll
@@ -460,11 +482,18 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&ctl->q_full));
+                return true;
+            };
+            if (item_n == 0) {
+                if (!q_store(wi, 0)) goto done;
             }
+            if (w + 1 < w_end) q_prefetch_l2(p.works[w + 1]);   // on its way to L2 while this item runs
             float l_part = 0.0f;        // this thread's share of the row sum, expressed against l_ref
             float l_ref = 0.0f;
             for (uint32_t it = it_base + ((team - it_base) & 1u); it < it_end; it += 2) {
-                const uint32_t ph = (it >> 1) & 1;
+                const uint32_t ph = (it >> 1) & 1;            // phase of the team's own barriers
+                const uint32_t tb = buf_of<kFp8>(it);         // score / P buffer of this tile and its phase
+                const uint32_t tph = phase_of<kFp8>(it);
                 const bool first = (it == it_base);
                 // The tile's values live in pairs (64-bit registers) so that the fp32 arithmetic on them uses the
                 // two-wide forms (fma/mul/add .f32x2): half the instructions of the scalar forms.
@@ -473,11 +502,11 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (lane == 0) mbar_arrive_expect_tx(my_xfull, kXbufBytes / 8);
                 if (kFp8)
                     if (!warp_wait(smem_u32(&ctl->kv_full[it % S]), (it / S) & 1, abort_flag)) goto done;
-                if (!warp_wait(smem_u32(&ctl->s_full[sb]), ph, abort_flag)) goto done;
+                if (!warp_wait(smem_u32(&ctl->s_full[tb]), tph, abort_flag)) goto done;
                 tc_fence_after();
                 if (warp == 0 || warp == 8) PROF(2, it, 0);
                 {
-                    const uint32_t s0 = lane_base + col_s<kFp8>() + sb * s_stride<kFp8>() + c0;
+                    const uint32_t s0 = lane_base + s_col_of<kFp8>(it) + c0;
                     uint32_t sr[CPT];
                     if (kFp8) {
                         uint32_t sr2[CPT], sr3[CPT];
@@ -486,8 +515,8 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         if (half) tmem_ld_n<CPT>(s0 + 64, sr3);
                         tmem_wait_ld();
                         if (warp == 0 || warp == 8) PROF(4, it, 0);
-                        const float4* sa = reinterpret_cast<const float4*>(ctl->row_scale[it % S][0] + c0);
-                        const float4* sb4 = reinterpret_cast<const float4*>(ctl->row_scale[it % S][1] + c0);
+                        const float4* sa = reinterpret_cast<const float4*>(ctl->row_scale[it % kScaleSlots][0] + c0);
+                        const float4* sb4 = reinterpret_cast<const float4*>(ctl->row_scale[it % kScaleSlots][1] + c0);
 #pragma unroll
                         for (int j = 0; j < CPT / 4; ++j) {
                             const float4 wa = sa[j], wb = sb4[j];
@@ -510,7 +539,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[sb]));   // the MMA warp may overwrite the scores
+                if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[tb]));   // the MMA warp may overwrite the scores
                 // ---- exchange: send when the peer has read what was sent last, add what it sent
                 if (n_x > 0)
                     if (!warp_wait_cluster(my_xfree, (n_x - 1) & 1, abort_flag)) goto done;
@@ -573,9 +602,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (!warp_wait(smem_u32(&ctl->mx_bar[sb]), ph, abort_flag)) goto done;
                 mt = fmaxf(ctl->row_max[sb][0][row], ctl->row_max[sb][1][row]);
                 if (warp == 0 || warp == 8) PROF(7, it, 2);
-                // ---- P against a snapshot of the reference maximum (the other team may still move it)
-                const float m_snap = first ? -INFINITY : ctl->m_shared[row];
-                const float m_c = (mt > m_snap + 8.0f) ? mt : m_snap;
+                // ---- P against the tile's own row maximum.  The row's reference maximum is known only at the
+                // commit (the other team may still move it); P is brought to it there by one factor, so the
+                // result does not depend on which team was faster.
+                const float m_c = mt;
                 const float m_c_use = (m_c == -INFINITY) ? 0.0f : m_c;
                 float lsum;
                 {
@@ -595,18 +625,19 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (warp == 0 || warp == 8) PROF(4, it, 1);
                 // ---- commit, in tile order: after the previous tile's commit (its P is released) ...
                 if (!first)
-                    if (!warp_wait(smem_u32(&ctl->p_full[sb ^ 1]), ((it - 1) >> 1) & 1, abort_flag)) goto done;
-                // ... and after the P V product that last read this team's P buffer
-                if (it >= 2)
-                    if (!warp_wait(smem_u32(&ctl->pv_done[sb]), ((it - 2) >> 1) & 1, abort_flag)) goto done;
+                    if (!warp_wait(smem_u32(&ctl->p_full[buf_of<kFp8>(it - 1)]), phase_of<kFp8>(it - 1), abort_flag)) goto done;
+                // ... and after the P V product that last read this tile's P buffer
+                if (it >= kBufReuse<kFp8>)
+                    if (!warp_wait(smem_u32(&ctl->pv_done[buf_of<kFp8>(it - kBufReuse<kFp8>)]), phase_of<kFp8>(it - kBufReuse<kFp8>), abort_flag))
+                        goto done;
                 if (warp == 0 || warp == 8) PROF(7, it, 3);
                 const float m_cur = first ? -INFINITY : ctl->m_shared[row];
                 const bool raise = mt > m_cur + 8.0f;   // lazy: move the reference only past a margin of 8
                 const float m_fin = raise ? mt : m_cur;
                 const float m_fin_use = (m_fin == -INFINITY) ? 0.0f : m_fin;
-                float f1 = 1.0f;   // snapshot -> final reference
-                if (!__all_sync(0xffffffffu, m_c == m_fin)) {
-                    f1 = (m_c == m_fin) ? 1.0f : ex2_approx(m_c_use - m_fin_use);
+                // own maximum -> reference: at most 2^8 (the lazy margin); a fully masked row has P = 0
+                const float f1 = (m_c == -INFINITY) ? 0.0f : ((m_c == m_fin) ? 1.0f : ex2_approx(m_c_use - m_fin_use));
+                if (!__all_sync(0xffffffffu, f1 == 1.0f)) {
                     const uint64_t f12 = pack2(f1, f1);
 #pragma unroll
                     for (int j = 0; j < NP; ++j) tv2[j] = mul2(tv2[j], f12);
@@ -614,7 +645,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (__any_sync(0xffffffffu, raise)) {
                     if (!first) {
                         // O so far is complete once the previous tile's P V product has finished
-                        if (!warp_wait(smem_u32(&ctl->pv_done[sb ^ 1]), ((it - 1) >> 1) & 1, abort_flag)) goto done;
+                        if (!warp_wait(smem_u32(&ctl->pv_done[buf_of<kFp8>(it - 1)]), phase_of<kFp8>(it - 1), abort_flag)) goto done;
                         tc_fence_after();
                         const float f2 = (m_cur == -INFINITY) ? 0.0f : ex2_approx(m_cur - m_fin);
 #pragma unroll 1
@@ -634,10 +665,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 l_part = fmaf(lsum, f1, l_part);
                 l_ref = m_fin;
                 {
-                    const uint32_t p0col = lane_base + kColP + sb * kPStride + chalf * (CPT / 2);
+                    const uint32_t p0col = lane_base + p_col_of<kFp8>(it) + chalf * (CPT / 2);
                     if (kFp8) {
-                        const float4* sa = reinterpret_cast<const float4*>(ctl->row_scale[it % S][0] + c0);
-                        const float4* sb4 = reinterpret_cast<const float4*>(ctl->row_scale[it % S][1] + c0);
+                        const float4* sa = reinterpret_cast<const float4*>(ctl->row_scale[it % kScaleSlots][0] + c0);
+                        const float4* sb4 = reinterpret_cast<const float4*>(ctl->row_scale[it % kScaleSlots][1] + c0);
                         uint32_t pk0[NP], pk1[NP];
 #pragma unroll
                         for (int j = 0; j < CPT / 4; ++j) {
@@ -660,28 +691,25 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&ctl->p_full[sb]));
+                if (lane == 0) mbar_arrive(smem_u32(&ctl->p_full[tb]));
                 if (warp == 0 || warp == 8) PROF(2, it, 3);
             }
-            if (C::kQInTmem && w + 1 < w_end) q_prefetch_l2(p.works[w + 1]);   // on its way to L2 during the epilogue
             // ---- epilogue of the item (all sixteen warps)
             {
                 const uint32_t it_last = it_end - 1;
                 // every tile of the item has been committed: the row's reference maximum is final
-                if (!warp_wait(smem_u32(&ctl->p_full[it_last & 1]), (it_last >> 1) & 1, abort_flag)) goto done;
+                if (!warp_wait(smem_u32(&ctl->p_full[buf_of<kFp8>(it_last)]), phase_of<kFp8>(it_last), abort_flag)) goto done;
                 const float m_ref = ctl->m_shared[row];
                 ctl->l_part[cg][row] = (l_part != 0.0f && l_ref != m_ref) ? l_part * ex2_approx(l_ref - m_ref) : l_part;
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&ctl->l_bar));
+                if (w + 1 < w_end)
+                    if (!q_store(p.works[w + 1], item_n + 1)) goto done;
                 if (!warp_wait(smem_u32(&ctl->l_bar), item_n & 1, abort_flag)) goto done;
-                // every warp has read the item's final reference; the next item starts without one (its
-                // second tile may take its snapshot before its first tile commits).  The reset is ordered
-                // before any tile of the next item by this warp's arrival on q_full.
-                if (cg == 0) ctl->m_shared[row] = -INFINITY;
                 float l = 0.0f;
 #pragma unroll
                 for (int g = 0; g < G; ++g) l += ctl->l_part[g][row];
-                if (!warp_wait(smem_u32(&ctl->pv_done[it_last & 1]), (it_last >> 1) & 1, abort_flag)) goto done;
+                if (!warp_wait(smem_u32(&ctl->pv_done[buf_of<kFp8>(it_last)]), phase_of<kFp8>(it_last), abort_flag)) goto done;
                 tc_fence_after();
                 const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
                 const int head = wi.head_block * kHeadsPerBlock + row;
@@ -731,73 +759,57 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
             it_base = it_end;
         }
-    } else {
-        // ============================================================ loaders (and, for an fp8 cache, converters)
+    } else if (!kFp8) {
+        // ============================================================ loaders (bf16 cache)
         // Four warps; warp lw owns rows [8 lw, 8 lw + 8) of every tile: it reads their top-k slots,
         // translates them through the block table and gathers them with TMA tile::gather4 (two lanes, one
-        // per group of four rows).  One warp can start a gather4 only every ~70 cycles, several warps
-        // overlap, so the issue is spread over four.  With an fp8 cache the same warp converts the rows
-        // it gathered (raw bytes -> bf16 MMA tile), one tile behind its own gathers.
+        // per group of four rows) straight into the swizzled MMA tile.  One warp can start a gather4 only
+        // every ~70 cycles, several warps overlap, so the issue is spread over four.
         const int lw = warp - kLoaderWarp0;
-        const int l8 = lane & 7;
-        const int gsel = lane & 1;
-        const int g = 2 * lw + gsel;             // group of four rows an issuing lane gathers
-        const int oob_row = (int)p.num_kv_rows;  // first row outside the tensor: the gather zero-fills it
-        uint8_t* mask_bytes = reinterpret_cast<uint8_t*>(ctl->tile_mask);
-        // convert mapping (fp8): thread = (row, 64-column quarter) of this warp's eight rows
-        const int r = 8 * lw + (lane >> 2);
-        const int qd = lane & 3;
-        uint32_t it_base = 0;
-        int item_n = 0;
-        for (int w = w_begin; w < w_end; ++w, ++item_n) {
-            const dsa_v32_work_info wi = p.works[w];
-            const int seq = wi.q_row / p.s_q;
-            const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
-            if (!C::kQInTmem && lw == 0) {
-                if (!warp_wait(smem_u32(&ctl->q_empty), (item_n & 1) ^ 1, abort_flag)) goto done;
-                if (lane == 0) {
-                    const uint32_t bar = smem_u32(&ctl->q_full);
-                    mbar_arrive_expect_tx(bar, nkb * kQBlockBytes);
-                    for (int kb = 0; kb < nkb; ++kb)
-                        tma_load_3d(smem_u32(sQ + kb * kQBlockBytes), &tm_q, bar, col0 + kb * 64,
-                                    wi.head_block * kHeadsPerBlock, wi.q_row);
-                }
-            }
-            const int32_t* idx_row = p.indices + (size_t)wi.q_row * p.topk;
-            // Two-deep software pipeline over tiles so no load is consumed in the step that issues it:
-            // slots of tiles u+2, u+3 are in flight, block numbers of tiles u, u+1 are in flight.
-            auto load_slot = [&](int k0) -> int {
-                const int k = k0 + 8 * lw + l8;
-                return (k < wi.k_end) ? __ldg(idx_row + k) : -1;
-            };
-            int idx_a = load_slot(wi.k_begin), idx_b = load_slot(wi.k_begin + kTileRows);
-            int idx_c = load_slot(wi.k_begin + 2 * kTileRows), idx_d = load_slot(wi.k_begin + 3 * kTileRows);
-            int phys_a = block_of(idx_a, seq, p), phys_b = block_of(idx_b, seq, p);
-            // gathers of tile u of the item (global tile number itu); false when a wait gave up
-            auto issue = [&](int u, uint32_t itu) -> bool {
-                const int k0 = wi.k_begin + u * kTileRows;
-                const int row = row_of(idx_a, phys_a, seq, p);
-                {
-                    const int phys_n = block_of(idx_c, seq, p);
-                    const int idx_n = load_slot(k0 + 4 * kTileRows);
-                    idx_a = idx_b; phys_a = phys_b;
-                    idx_b = idx_c; phys_b = phys_n;
-                    idx_c = idx_d; idx_d = idx_n;
-                }
-                const uint32_t mask8 = __ballot_sync(0xffffffffu, row >= 0) & 0xFFu;
-                const int coord = row >= 0 ? row : oob_row;
-                const int r0 = __shfl_sync(0xffffffffu, coord, 4 * gsel + 0);
-                const int r1 = __shfl_sync(0xffffffffu, coord, 4 * gsel + 1);
-                const int r2 = __shfl_sync(0xffffffffu, coord, 4 * gsel + 2);
-                const int r3 = __shfl_sync(0xffffffffu, coord, 4 * gsel + 3);
-                if (!kFp8) {
-                    const int s = itu % S;
-                    PROF(0, itu, 1);
-                    if (!warp_wait(smem_u32(&ctl->kv_empty[s]), ((itu / S) & 1) ^ 1, abort_flag)) return false;
-                    PROF(0, itu, 2);
+        if (lw < kLoaderWarps) {
+            const int l8 = lane & 7;
+            const int gsel = lane & 1;
+            const int g = 2 * lw + gsel;             // group of four rows an issuing lane gathers
+            const int oob_row = (int)p.num_kv_rows;  // first row outside the tensor: the gather zero-fills it
+            uint8_t* mask_bytes = reinterpret_cast<uint8_t*>(ctl->tile_mask);
+            uint32_t it = 0;
+            for (int w = w_begin; w < w_end; ++w) {
+                const dsa_v32_work_info wi = p.works[w];
+                const int seq = wi.q_row / p.s_q;
+                const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
+                const int32_t* idx_row = p.indices + (size_t)wi.q_row * p.topk;
+                // Two-deep software pipeline over tiles so no load is consumed in the step that issues it:
+                // slots of tiles u+2, u+3 are in flight, block numbers of tiles u, u+1 are in flight.
+                auto load_slot = [&](int k0) -> int {
+                    const int k = k0 + 8 * lw + l8;
+                    return (k < wi.k_end) ? __ldg(idx_row + k) : -1;
+                };
+                int idx_a = load_slot(wi.k_begin), idx_b = load_slot(wi.k_begin + kTileRows);
+                int idx_c = load_slot(wi.k_begin + 2 * kTileRows), idx_d = load_slot(wi.k_begin + 3 * kTileRows);
+                int phys_a = block_of(idx_a, seq, p), phys_b = block_of(idx_b, seq, p);
+                for (int u = 0; u < n_tiles; ++u, ++it) {
+                    const int k0 = wi.k_begin + u * kTileRows;
+                    const int row = row_of(idx_a, phys_a, seq, p);
+                    {
+                        const int phys_n = block_of(idx_c, seq, p);
+                        const int idx_n = load_slot(k0 + 4 * kTileRows);
+                        idx_a = idx_b; phys_a = phys_b;
+                        idx_b = idx_c; phys_b = phys_n;
+                        idx_c = idx_d; idx_d = idx_n;
+                    }
+                    const uint32_t mask8 = __ballot_sync(0xffffffffu, row >= 0) & 0xFFu;
+                    const int coord = row >= 0 ? row : oob_row;
+                    const int r0 = __shfl_sync(0xffffffffu, coord, 4 * gsel + 0);
+                    const int r1 = __shfl_sync(0xffffffffu, coord, 4 * gsel + 1);
+                    const int r2 = __shfl_sync(0xffffffffu, coord, 4 * gsel + 2);
+                    const int r3 = __shfl_sync(0xffffffffu, coord, 4 * gsel + 3);
+                    const int s = it % S;
+                    if (lw == 0) PROF(0, it, 1);
+                    if (!warp_wait(smem_u32(&ctl->kv_empty[s]), ((it / S) & 1) ^ 1, abort_flag)) goto done;
+                    if (lw == 0) PROF(0, it, 2);
                     const uint32_t bar = smem_u32(&ctl->kv_full[s]);
                     if (lane == 0) {
-                        mask_bytes[(itu % kMaskSlots) * 4 + lw] = static_cast<uint8_t>(mask8);
+                        mask_bytes[(it % kMaskSlots) * 4 + lw] = static_cast<uint8_t>(mask8);
                         mbar_arrive_expect_tx(bar, nkb * 8 * 128);
                     }
                     __syncwarp();
@@ -806,79 +818,148 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         for (int kb = 0; kb < nkb; ++kb)
                             tma_gather4(dst + kb * kKvBlockBytes, &tm_kv, bar, col0 + kb * 64, r0, r1, r2, r3);
                     }
-                } else {
-                    const int rs = itu % R;
-                    const uint32_t bar = smem_u32(&ctl->raw_full[rs * 4 + lw]);
-                    PROF(0, itu, 2);
-                    if (lane == 0) {
-                        mask_bytes[(itu % kMaskSlots) * 4 + lw] = static_cast<uint8_t>(mask8);
-                        mbar_arrive_expect_tx(bar, 8 * (256 + 144));
-                    }
-                    __syncwarp();
-                    if (lane < 2) {
-                        const uint32_t dst = smem_u32(sRaw + rs * kRawTileBytes + g * kRawGroupBytes);
-                        tma_gather4(dst, &tm_kv, bar, col0, r0, r1, r2, r3);              // 256 latent bytes
-                        tma_gather4(dst + 1024, &tm_kv_tail, bar, 512, r0, r1, r2, r3);  // scales + rope
-                    }
-                }
-                if (lw == 0) PROF(0, itu, 0);
-                return true;
-            };
-            if (!kFp8) {
-                for (int u = 0; u < n_tiles; ++u)
-                    if (!issue(u, it_base + u)) goto done;
-            } else {
-                // gathers run R - 1 tiles ahead of the conversion; a raw buffer is reused by the warp that
-                // read it, in program order, so it needs no "empty" barrier
-                for (int u = 0; u < R - 1 && u < n_tiles; ++u)
-                    if (!issue(u, it_base + u)) goto done;
-                for (int t = 0; t < n_tiles; ++t) {
-                    const uint32_t it = it_base + t;
-                    const int rs = it % R, s = it % S;
-                    if (t + R - 1 < n_tiles)
-                        if (!issue(t + R - 1, it + R - 1)) goto done;
-                    if (!warp_wait(smem_u32(&ctl->raw_full[rs * 4 + lw]), (it / R) & 1, abort_flag)) goto done;
-                    if (lw == 0) PROF(3, it, 2);
-                    if (!warp_wait(smem_u32(&ctl->kv_empty[s]), ((it / S) & 1) ^ 1, abort_flag)) goto done;
-                    if (lw == 0) PROF(3, it, 0);
-                    const uint8_t* grp = sRaw + rs * kRawTileBytes + (r >> 2) * kRawGroupBytes;
-                    const int ri = r & 3;
-                    const uint8_t* src = grp + ri * 256 + qd * 64;
-                    const uint8_t* tail = grp + 1024 + ri * 144;
-                    // the row's scales are applied to the fp32 scores and to P by the softmax warps
-                    if ((qd & 1) == 0)
-                        ctl->row_scale[s][qd >> 1][r] = reinterpret_cast<const float*>(tail)[2 * half + (qd >> 1)];
-                    uint8_t* dst_row = sKV + s * kKvTileBytes + qd * kKvBlockBytes + r * 128;
-#pragma unroll
-                    for (int cc = 0; cc < 4; ++cc) {
-                        const int c = (cc + r) & 3;  // rotate so the rows of a warp hit different banks
-                        const uint4 raw = *reinterpret_cast<const uint4*>(src + c * 16);
-                        const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
-                        uint32_t o[8];
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            o[2 * k + 0] = e4m3x2_to_bf16x2(__byte_perm(wv[k], 0u, 0x1404u));
-                            o[2 * k + 1] = e4m3x2_to_bf16x2(__byte_perm(wv[k], 0u, 0x3424u));
-                        }
-                        // 16 bytes -> 16 bf16 = chunks 2c, 2c+1 of this thread's 128-byte block row
-                        *reinterpret_cast<uint4*>(dst_row + (((2 * c + 0) ^ (r & 7)) * 16)) = make_uint4(o[0], o[1], o[2], o[3]);
-                        *reinterpret_cast<uint4*>(dst_row + (((2 * c + 1) ^ (r & 7)) * 16)) = make_uint4(o[4], o[5], o[6], o[7]);
-                    }
-                    if (half) {
-                        // rope: 64 bf16 = 8 chunks into block 4; this thread copies chunks 2*qd, 2*qd+1
-                        const uint4 a = *reinterpret_cast<const uint4*>(tail + 16 + (2 * qd + 0) * 16);
-                        const uint4 b = *reinterpret_cast<const uint4*>(tail + 16 + (2 * qd + 1) * 16);
-                        uint8_t* d = sKV + s * kKvTileBytes + 4 * kKvBlockBytes + r * 128;
-                        *reinterpret_cast<uint4*>(d + (((2 * qd + 0) ^ (r & 7)) * 16)) = a;
-                        *reinterpret_cast<uint4*>(d + (((2 * qd + 1) ^ (r & 7)) * 16)) = b;
-                    }
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&ctl->kv_full[s]));
-                    if (lw == 0) PROF(3, it, 1);
+                    if (lw == 0) PROF(0, it, 0);
                 }
             }
-            it_base += n_tiles;
+        }
+    } else if (warp < kGatherWarp0 + kGatherWarps) {
+        // ============================================================ gather issuers (fp8 cache)
+        // Two warps; warp iw owns rows [16 iw, 16 iw + 16) of every tile: top-k slots -> physical rows, one
+        // TMA tile::gather4 per group of four rows (the row's bytes of this CTA's slice in one request: the
+        // cache is described as 32-bit elements so that a request may be wider than 256 bytes), and the
+        // row's two scales by cp.async straight into the scale table.  The issuers run ahead of the
+        // converters by the raw ring (kRawStages tiles), across items.
+        const int iw = warp - kGatherWarp0;
+        const int l16 = lane & 15;
+        const int gl = lane & 3;
+        const int oob_row = (int)p.num_kv_rows;
+        const uint32_t row_bytes = half ? 400u : 256u;   // latent half (+ scales + rope)
+        const CUtensorMap* tmap = half ? &tm_kv_tail : &tm_kv;
+        const int tcol = half ? 64 : 0;                  // first 32-bit element of the slice
+        uint16_t* mask_halves = reinterpret_cast<uint16_t*>(ctl->tile_mask);
+        const uint8_t* kv_bytes = reinterpret_cast<const uint8_t*>(p.kv);
+        uint32_t it = 0;
+        for (int w = w_begin; w < w_end; ++w) {
+            const dsa_v32_work_info wi = p.works[w];
+            const int seq = wi.q_row / p.s_q;
+            const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
+            const int32_t* idx_row = p.indices + (size_t)wi.q_row * p.topk;
+            auto load_slot = [&](int k0) -> int {
+                const int k = k0 + 16 * iw + l16;
+                return (k < wi.k_end) ? __ldg(idx_row + k) : -1;
+            };
+            int idx_a = load_slot(wi.k_begin), idx_b = load_slot(wi.k_begin + kTileRows);
+            int idx_c = load_slot(wi.k_begin + 2 * kTileRows), idx_d = load_slot(wi.k_begin + 3 * kTileRows);
+            int phys_a = block_of(idx_a, seq, p), phys_b = block_of(idx_b, seq, p);
+            for (int u = 0; u < n_tiles; ++u, ++it) {
+                const int k0 = wi.k_begin + u * kTileRows;
+                if (iw == 0) PROF(0, it, 1);
+                const int row = row_of(idx_a, phys_a, seq, p);
+                {
+                    const int phys_n = block_of(idx_c, seq, p);
+                    const int idx_n = load_slot(k0 + 4 * kTileRows);
+                    idx_a = idx_b; phys_a = phys_b;
+                    idx_b = idx_c; phys_b = phys_n;
+                    idx_c = idx_d; idx_d = idx_n;
+                }
+                const uint32_t mask16 = __ballot_sync(0xffffffffu, row >= 0) & 0xFFFFu;
+                const int coord = row >= 0 ? row : oob_row;
+                const int r0 = __shfl_sync(0xffffffffu, coord, 4 * gl + 0);
+                const int r1 = __shfl_sync(0xffffffffu, coord, 4 * gl + 1);
+                const int r2 = __shfl_sync(0xffffffffu, coord, 4 * gl + 2);
+                const int r3 = __shfl_sync(0xffffffffu, coord, 4 * gl + 3);
+                const int rs = it % R;
+                if (!warp_wait(smem_u32(&ctl->raw_empty[rs * 2 + iw]), ((it / R) & 1) ^ 1, abort_flag)) goto done;
+                if (iw == 0) PROF(0, it, 2);
+                const uint32_t bar = smem_u32(&ctl->raw_full[rs * 2 + iw]);
+                if (lane == 0) {
+                    mask_halves[(it % kMaskSlots) * 2 + iw] = static_cast<uint16_t>(mask16);
+                    mbar_arrive_expect_tx(bar, 16 * row_bytes);
+                }
+                __syncwarp();
+                if (lane < 16) {
+                    // the two fp32 scales of this CTA's groups: bytes 512 + 8 half of the row (zeros for padding)
+                    const uint8_t* src = kv_bytes + (size_t)(row >= 0 ? row : 0) * kFp8RowBytes + 512 + 8 * half;
+                    const uint32_t n = row >= 0 ? 4u : 0u;
+                    float* sc = &ctl->row_scale[it % kScaleSlots][0][16 * iw + l16];
+                    cp_async_4(smem_u32(sc), src, n);
+                    cp_async_4(smem_u32(sc + kTileRows), src + 4, n);
+                    cp_async_mbar_arrive_noinc(bar);
+                }
+                if (lane < 4) {
+                    const uint32_t dst = smem_u32(sRaw + rs * kRawTileBytes + (4 * iw + lane) * kRawGroupBytes);
+                    tma_gather4(dst, tmap, bar, tcol, r0, r1, r2, r3);
+                }
+                if (iw == 0) PROF(0, it, 0);
+            }
+        }
+    } else {
+        // ============================================================ converters (fp8 cache)
+        // Four warps; warp cw turns rows [8 cw, 8 cw + 8) of every raw tile into the bf16 MMA tile:
+        // e4m3 -> bf16 exactly (e4m3 has 4 significant bits; the reference's LDS round trip is
+        // ..mxfp8_16mx8_32nx1_template.hpp:852-864), and copies the rope columns.  The per-128 fp32
+        // scales never touch the operands (see the softmax warps).
+        const int cw = warp - kConvertWarp0;
+        const int iw = cw >> 1;                  // the issuer warp that gathers this warp's rows
+        const int r = 8 * cw + (lane >> 2);      // tile row
+        const int qd = lane & 3;                 // which 64 of this CTA's 256 latent columns
+        const uint32_t row_bytes = half ? 400u : 256u;
+        uint32_t it = 0;
+        int item_n = 0;
+        for (int w = w_begin; w < w_end; ++w, ++item_n) {
+            const dsa_v32_work_info wi = p.works[w];
+            const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
+            if (half && cw == 0) {
+                // rope block of the item's Q (the latent part goes to TMEM through the softmax warps)
+                if (!warp_wait(smem_u32(&ctl->q_empty), (item_n & 1) ^ 1, abort_flag)) goto done;
+                if (lane == 0) {
+                    const uint32_t bar = smem_u32(&ctl->q_full);
+                    mbar_arrive_expect_tx(bar, kQBlockBytes);
+                    tma_load_3d(smem_u32(sQ), &tm_q, bar, kDV, wi.head_block * kHeadsPerBlock, wi.q_row);
+                }
+            }
+            for (int t = 0; t < n_tiles; ++t, ++it) {
+                const int rs = it % R, s = it % S;
+                if (!warp_wait(smem_u32(&ctl->raw_full[rs * 2 + iw]), (it / R) & 1, abort_flag)) goto done;
+                if (cw == 0) PROF(3, it, 2);
+                if (!warp_wait(smem_u32(&ctl->kv_empty[s]), ((it / S) & 1) ^ 1, abort_flag)) goto done;
+                if (cw == 0) PROF(3, it, 0);
+                const uint8_t* row_raw = sRaw + rs * kRawTileBytes + (r >> 2) * kRawGroupBytes + (r & 3) * row_bytes;
+                const uint8_t* src = row_raw + qd * 64;
+                uint8_t* dst_row = sKV + s * kKvTileBytes + qd * kKvBlockBytes + r * 128;
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) {
+                    const int c = (cc + r) & 3;  // rotate so the rows of a warp hit different banks
+                    const uint4 raw = *reinterpret_cast<const uint4*>(src + c * 16);
+                    const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
+                    uint32_t o[8];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        o[2 * k + 0] = e4m3x2_to_bf16x2(__byte_perm(wv[k], 0u, 0x1404u));
+                        o[2 * k + 1] = e4m3x2_to_bf16x2(__byte_perm(wv[k], 0u, 0x3424u));
+                    }
+                    // 16 bytes -> 16 bf16 = chunks 2c, 2c+1 of this thread's 128-byte block row
+                    *reinterpret_cast<uint4*>(dst_row + (((2 * c + 0) ^ (r & 7)) * 16)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    *reinterpret_cast<uint4*>(dst_row + (((2 * c + 1) ^ (r & 7)) * 16)) = make_uint4(o[4], o[5], o[6], o[7]);
+                }
+                if (half) {
+                    // rope: 64 bf16 = 8 chunks into block 4 (after the 256 latent bytes and the 16 scale bytes
+                    // of the raw row); this thread copies chunks 2*qd, 2*qd+1
+                    const uint8_t* rope = row_raw + 272;
+                    const uint4 a = *reinterpret_cast<const uint4*>(rope + (2 * qd + 0) * 16);
+                    const uint4 b = *reinterpret_cast<const uint4*>(rope + (2 * qd + 1) * 16);
+                    uint8_t* d = sKV + s * kKvTileBytes + 4 * kKvBlockBytes + r * 128;
+                    *reinterpret_cast<uint4*>(d + (((2 * qd + 0) ^ (r & 7)) * 16)) = a;
+                    *reinterpret_cast<uint4*>(d + (((2 * qd + 1) ^ (r & 7)) * 16)) = b;
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(smem_u32(&ctl->kv_full[s]));
+                    mbar_arrive(smem_u32(&ctl->raw_empty[rs * 2 + iw]));
+                }
+                if (cw == 0) PROF(3, it, 1);
+            }
         }
     }
 

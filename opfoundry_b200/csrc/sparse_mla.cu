@@ -53,6 +53,13 @@
 #include "defs.h"
 #include "ptx.cuh"
 
+#ifndef DSA_FP8_KV_STAGES
+#define DSA_FP8_KV_STAGES 4
+#endif
+#ifndef DSA_FP8_RAW_STAGES
+#define DSA_FP8_RAW_STAGES 4
+#endif
+
 namespace dsa {
 
 
@@ -106,27 +113,27 @@ struct Cfg {
     // from global memory.  Only the rope block of an fp8 item stays in shared memory (TMEM is full).
     static constexpr bool kQInTmem = true;
     static constexpr int kQSmemBytes = kFp8 ? kQBlockBytes : 0;
-    static constexpr int kKvStages = kFp8 ? 5 : 8;   // MMA-ready bf16 tiles
-    static constexpr int kRawStages = kFp8 ? 5 : 0;  // raw fp8 tiles in flight (gathers run kRawStages - 1 tiles ahead)
+    static constexpr int kKvStages = kFp8 ? DSA_FP8_KV_STAGES : 6;   // MMA-ready bf16 tiles
+    static constexpr int kRawStages = kFp8 ? DSA_FP8_RAW_STAGES : 0; // raw fp8 tiles in flight
     static constexpr int kThreads = 32 * (kSoftmaxWarps + 2 + 6);
     static constexpr int kOffKv = kQSmemBytes;
     static constexpr int kOffRaw = kOffKv + kKvStages * kKvTileBytes;
     static constexpr int kOffX = kOffRaw + kRawStages * kRawTileBytes;
-    static constexpr int kOffCtl = kOffX + 2 * kXbufBytes;
+    static constexpr int kOffCtl = kOffX + kGroups * kXbufBytes;   // one exchange buffer per softmax team
     static constexpr int kCtlBytes = 12288;
     static constexpr int kSmemBytes = kOffCtl + kCtlBytes + 1024;  // + slack for 1024-byte alignment
 };
 
 struct Ctl {
-    float row_max[2][2][kHeadsPerBlock];        // per team: row maxima of the two column halves of a tile
     float l_part[kGroups][kHeadsPerBlock];      // per-group row sums at the end of an item
     float row_scale[kScaleSlots][2][kTileRows];  // fp8 cache: per tile buffer, the scales of this CTA's two groups for every tile row
     uint64_t q_full, q_empty, o_free;
     uint64_t kv_full[8], kv_empty[8];
     uint64_t raw_full[16];   // fp8 cache: [raw buffer][gather warp]: that warp's sixteen rows and their scales have landed
     uint64_t raw_empty[16];  // ... and both converter warps that read them are done
-    uint64_t s_full[2], s_empty[2], p_full[2], pv_done[2];
-    uint64_t mx_bar[2], l_bar;
+    uint64_t s_full[kGroups], s_empty[kGroups], p_full[kGroups], pv_done[kGroups];
+    uint64_t l_bar;
+    uint64_t m_bar[kGroups][4];        // [team][lane quadrant]: the tile's reference-maximum step is done
     uint64_t x_full[kSoftmaxWarps];    // bytes of the peer's partial scores for this warp's rows / columns
     uint64_t x_free[kSoftmaxWarps];    // credit (4 bytes): the peer's same warp has read what this warp sent last
     uint32_t x_sink[kSoftmaxWarps];    // where the credit word lands
@@ -148,11 +155,11 @@ constexpr uint32_t kColO = 0;
 constexpr uint32_t kColQ = 256;
 template <bool kFp8> __host__ __device__ constexpr uint32_t col_s() { return kFp8 ? 384 : 416; }
 template <bool kFp8> __host__ __device__ constexpr uint32_t col_p() { return 480; }
-// The per-tile barriers (s_full, s_empty, p_full, pv_done) always come in pairs indexed by the tile's
-// parity (= the softmax team that works on it), also where the TMEM buffer behind them is single: a team
-// that runs ahead must not take the other team's completion for its own.
-template <bool kFp8> __device__ __forceinline__ uint32_t buf_of(uint32_t it) { return it & 1u; }
-template <bool kFp8> __device__ __forceinline__ uint32_t phase_of(uint32_t it) { return (it >> 1) & 1u; }
+// The per-tile barriers (s_full, s_empty, p_full, pv_done) come in fours indexed by the softmax team that
+// works on the tile (tile number mod 4), also where the TMEM buffer behind them is single or double: a
+// team that runs ahead must not take another team's completion for its own.
+template <bool kFp8> __device__ __forceinline__ uint32_t buf_of(uint32_t it) { return it & (kGroups - 1u); }
+template <bool kFp8> __device__ __forceinline__ uint32_t phase_of(uint32_t it) { return (it / kGroups) & 1u; }
 template <bool kFp8> constexpr uint32_t kBufReuse = kFp8 ? 1u : 2u;   // tiles between two uses of a score / P buffer
 template <bool kFp8> __device__ __forceinline__ uint32_t s_col_of(uint32_t it) { return col_s<kFp8>() + (kFp8 ? 0u : (it & 1u) * 32u); }
 template <bool kFp8> __device__ __forceinline__ uint32_t p_col_of(uint32_t it) { return col_p<kFp8>() + (kFp8 ? 0u : (it & 1u) * 16u); }
@@ -300,13 +307,13 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             mbar_init(smem_u32(&ctl->raw_full[i]), 1 + 16);   // the expect_tx arrival + sixteen cp.async arrivals
             mbar_init(smem_u32(&ctl->raw_empty[i]), 2);
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < kGroups; ++i) {
             mbar_init(smem_u32(&ctl->s_full[i]), 1);
-            mbar_init(smem_u32(&ctl->s_empty[i]), kSoftmaxWarps / 2);   // one team
-            mbar_init(smem_u32(&ctl->p_full[i]), kSoftmaxWarps / 2);
-            mbar_init(smem_u32(&ctl->mx_bar[i]), kSoftmaxWarps / 2);
+            mbar_init(smem_u32(&ctl->s_empty[i]), kSoftmaxWarps / kGroups);   // one team
+            mbar_init(smem_u32(&ctl->p_full[i]), kSoftmaxWarps / kGroups);
             mbar_init(smem_u32(&ctl->pv_done[i]), 1);
         }
+        for (int i = 0; i < kGroups * 4; ++i) mbar_init(smem_u32(&ctl->m_bar[0][0]) + 8 * i, 1);
         ctl->abort_flag = 0;
         fence_mbar_init();
         for (int w = 0; w < kSoftmaxWarps; ++w) {
@@ -394,26 +401,24 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
     } else if (warp < kSoftmaxWarps) {
         // ============================================================ softmax + epilogue
-        // Two teams of eight warps take alternate tiles (team = tile parity = score / P / exchange buffer
-        // index), so two tiles are in flight through the long part of a step (TMEM load, exchange, mask,
-        // max, exp).  Inside a team, warpgroup `chalf` owns 16 of the tile's 32 columns; thread = (head
-        // row, chalf).  Only the short commit of a tile is ordered after the commit of the tile before:
-        // there the shared reference maximum of the row is read, P (computed against the tile's own row
-        // maximum) is brought to it, O is rescaled in the rare case the reference moves (lazy threshold 8),
-        // P is stored and the tile is released to the MMA warp.
-        constexpr int G = kGroups, CPT = 16, NP = CPT / 2, NCH = CPT / 4, OCOLS = kDvHalf / G;
-        static_assert(kGroups == 4, "two teams x two column halves");
+        // Four teams of four warps (one warp per TMEM lane quadrant) take the tiles round robin (team =
+        // tile number mod 4 = exchange buffer and barrier index), so four tiles are in flight through the
+        // long part of a step (TMEM load, exchange, mask, max, exp).  Thread = head row: it holds its row's
+        // 32 scores of the tile, so the row maximum and sum need no other thread.  Only the short commit
+        // of a tile is ordered after the commit of the tile before: there the shared reference maximum of
+        // the row is read, P (computed against the tile's own row maximum) is brought to it, O is
+        // rescaled in the rare case the reference moves (lazy threshold 8), P is stored and the tile is
+        // released to the MMA warp.
+        constexpr int G = kGroups, CPT = kTileRows, NP = CPT / 2, NCH = CPT / 4, OCOLS = kDvHalf / G;
+        static_assert(kGroups == 4 && kTileRows == 32, "four teams, one thread per row and tile");
         const int cg = warp >> 2;            // warpgroup
-        const int team = cg >> 1;            // tile parity this warp works on
-        const int chalf = cg & 1;            // which half of a tile's 32 columns
+        const int team = cg;                 // tiles this warp works on: it % 4 == team
         const int quad = warp & 3;           // TMEM lane quadrant this warp may touch
         const int row = quad * 32 + lane;    // head row inside the block == TMEM lane
-        const int c0 = chalf * CPT;
-        const int sb = team;                 // exchange buffer, row-maximum scratch and its barrier: one per team
+        const int sb = team;                 // exchange buffer of the team
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(quad * 32) << 16);
         // exchange buffer of a tile: [8 chunks of 4 columns][128 rows][16 bytes]
-        const uint32_t x_off = static_cast<uint32_t>(sb * kXbufBytes) +
-                               static_cast<uint32_t>((chalf * NCH) * kHeadsPerBlock + row) * 16u;
+        const uint32_t x_off = static_cast<uint32_t>(sb * kXbufBytes) + static_cast<uint32_t>(row) * 16u;
         const uint32_t peer_x = map_to_cta(smem_u32(sX), peer) + x_off;
         // the peer thread with the same (warp, lane) reads what this thread sends: one byte-counting
         // barrier per warp for arrival, one per warp for the credit "the peer has read the last one"
@@ -490,52 +495,57 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             if (w + 1 < w_end) q_prefetch_l2(p.works[w + 1]);   // on its way to L2 while this item runs
             float l_part = 0.0f;        // this thread's share of the row sum, expressed against l_ref
             float l_ref = 0.0f;
-            for (uint32_t it = it_base + ((team - it_base) & 1u); it < it_end; it += 2) {
-                const uint32_t ph = (it >> 1) & 1;            // phase of the team's own barriers
-                const uint32_t tb = buf_of<kFp8>(it);         // score / P buffer of this tile and its phase
+            for (uint32_t it = it_base + ((team - it_base) & (G - 1u)); it < it_end; it += G) {
+                const uint32_t tb = buf_of<kFp8>(it);         // barrier index (= team) and phase of this tile
                 const uint32_t tph = phase_of<kFp8>(it);
                 const bool first = (it == it_base);
                 // The tile's values live in pairs (64-bit registers) so that the fp32 arithmetic on them uses the
                 // two-wide forms (fma/mul/add .f32x2): half the instructions of the scalar forms.
                 uint64_t tv2[NP];
                 // ---- own partial scores out of TMEM
-                if (lane == 0) mbar_arrive_expect_tx(my_xfull, kXbufBytes / 8);
+                if (lane == 0) mbar_arrive_expect_tx(my_xfull, kXbufBytes / 4);
                 if (kFp8)
                     if (!warp_wait(smem_u32(&ctl->kv_full[it % S]), (it / S) & 1, abort_flag)) goto done;
                 if (!warp_wait(smem_u32(&ctl->s_full[tb]), tph, abort_flag)) goto done;
                 tc_fence_after();
-                if (warp == 0 || warp == 8) PROF(2, it, 0);
+                if (warp == 0 || warp == 4) PROF(2, it, 0);
                 {
-                    const uint32_t s0 = lane_base + s_col_of<kFp8>(it) + c0;
-                    uint32_t sr[CPT];
+                    const uint32_t s0 = lane_base + s_col_of<kFp8>(it);
                     if (kFp8) {
-                        uint32_t sr2[CPT], sr3[CPT];
-                        tmem_ld_n<CPT>(s0, sr);
-                        tmem_ld_n<CPT>(s0 + 32, sr2);
-                        if (half) tmem_ld_n<CPT>(s0 + 64, sr3);
-                        tmem_wait_ld();
-                        if (warp == 0 || warp == 8) PROF(4, it, 0);
-                        const float4* sa = reinterpret_cast<const float4*>(ctl->row_scale[it % kScaleSlots][0] + c0);
-                        const float4* sb4 = reinterpret_cast<const float4*>(ctl->row_scale[it % kScaleSlots][1] + c0);
+                        // 8 columns at a time (few live registers): accumulators of scale group a, scale group b
+                        // and, in the CTA that has them, the rope columns
 #pragma unroll
-                        for (int j = 0; j < CPT / 4; ++j) {
-                            const float4 wa = sa[j], wb = sb4[j];
-                            tv2[2 * j] = fma2(pack2(wb.x, wb.y), pack2u(sr2[4 * j], sr2[4 * j + 1]),
-                                              mul2(pack2(wa.x, wa.y), pack2u(sr[4 * j], sr[4 * j + 1])));
-                            tv2[2 * j + 1] = fma2(pack2(wb.z, wb.w), pack2u(sr2[4 * j + 2], sr2[4 * j + 3]),
-                                                  mul2(pack2(wa.z, wa.w), pack2u(sr[4 * j + 2], sr[4 * j + 3])));
+                        for (int hc = 0; hc < 4; ++hc) {
+                            uint32_t sr[8], sr2[8];
+                            tmem_ld_n<8>(s0 + 8 * hc, sr);
+                            tmem_ld_n<8>(s0 + 32 + 8 * hc, sr2);
+                            const float4* sa = reinterpret_cast<const float4*>(ctl->row_scale[it % kScaleSlots][0] + 8 * hc);
+                            const float4* sb4 = reinterpret_cast<const float4*>(ctl->row_scale[it % kScaleSlots][1] + 8 * hc);
+                            const float4 wa0 = sa[0], wa1 = sa[1], wb0 = sb4[0], wb1 = sb4[1];
+                            tmem_wait_ld();
+                            tv2[4 * hc + 0] = fma2(pack2(wb0.x, wb0.y), pack2u(sr2[0], sr2[1]), mul2(pack2(wa0.x, wa0.y), pack2u(sr[0], sr[1])));
+                            tv2[4 * hc + 1] = fma2(pack2(wb0.z, wb0.w), pack2u(sr2[2], sr2[3]), mul2(pack2(wa0.z, wa0.w), pack2u(sr[2], sr[3])));
+                            tv2[4 * hc + 2] = fma2(pack2(wb1.x, wb1.y), pack2u(sr2[4], sr2[5]), mul2(pack2(wa1.x, wa1.y), pack2u(sr[4], sr[5])));
+                            tv2[4 * hc + 3] = fma2(pack2(wb1.z, wb1.w), pack2u(sr2[6], sr2[7]), mul2(pack2(wa1.z, wa1.w), pack2u(sr[6], sr[7])));
                         }
                         if (half) {
 #pragma unroll
-                            for (int j = 0; j < NP; ++j) tv2[j] = add2(tv2[j], pack2u(sr3[2 * j], sr3[2 * j + 1]));
+                            for (int hc = 0; hc < 2; ++hc) {
+                                uint32_t sr3[16];
+                                tmem_ld_n<16>(s0 + 64 + 16 * hc, sr3);
+                                tmem_wait_ld();
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) tv2[8 * hc + j] = add2(tv2[8 * hc + j], pack2u(sr3[2 * j], sr3[2 * j + 1]));
+                            }
                         }
                     } else {
+                        uint32_t sr[CPT];
                         tmem_ld_n<CPT>(s0, sr);
                         tmem_wait_ld();
-                        if (warp == 0 || warp == 8) PROF(4, it, 0);
 #pragma unroll
                         for (int j = 0; j < NP; ++j) tv2[j] = pack2u(sr[2 * j], sr[2 * j + 1]);
                     }
+                    if (warp == 0 || warp == 4) PROF(4, it, 0);
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -544,7 +554,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (n_x > 0)
                     if (!warp_wait_cluster(my_xfree, (n_x - 1) & 1, abort_flag)) goto done;
                 if (lane == 0) mbar_arrive_expect_tx(my_xfree, 4);   // the credit for this send
-                if (warp == 0 || warp == 8) PROF(7, it, 1);
+                if (warp == 0 || warp == 4) PROF(7, it, 1);
 #pragma unroll
                 for (int c = 0; c < NCH; ++c) {
                     float v0, v1, v2, v3;
@@ -552,9 +562,9 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     unpack2(tv2[2 * c + 1], v2, v3);
                     st_async_f32x4(peer_x + c * (kHeadsPerBlock * 16), v0, v1, v2, v3, peer_xfull);
                 }
-                if (warp == 0 || warp == 8) PROF(2, it, 1);
+                if (warp == 0 || warp == 4) PROF(2, it, 1);
                 if (!warp_wait_cluster(my_xfull, n_x & 1, abort_flag)) goto done;
-                if (warp == 0 || warp == 8) PROF(2, it, 2);
+                if (warp == 0 || warp == 4) PROF(2, it, 2);
                 {
                     // credit: the peer may overwrite the buffer.  The credit word is computed from every lane's
                     // loaded values, so it cannot leave before all of the warp's reads have returned.
@@ -574,8 +584,8 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (!kFp8)
                     if (!warp_wait(smem_u32(&ctl->kv_full[it % S]), (it / S) & 1, abort_flag)) goto done;
                 // ---- mask (padding slots; the mask is the same for every row, so a full tile skips this)
-                const uint32_t mask = (ctl->tile_mask[it % kMaskSlots] >> c0) & 0xFFFFu;
-                if (mask != 0xFFFFu) {
+                const uint32_t mask = ctl->tile_mask[it % kMaskSlots];
+                if (mask != 0xFFFFFFFFu) {
 #pragma unroll
                     for (int j = 0; j < NP; ++j) {
                         float v0, v1;
@@ -585,31 +595,40 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         tv2[j] = pack2(v0, v1);
                     }
                 }
-                // ---- row maximum over the tile's 32 columns (the two warpgroups of the team), in the log2
-                // domain; the scale is positive, so the maximum is taken on the raw scores and scaled once
+                // ---- row maximum over the tile's 32 columns, in the log2 domain; the scale is positive, so
+                // the maximum is taken on the raw scores and scaled once
                 float mt;
                 {
-                    float v[CPT];
+                    float t[NP];
 #pragma unroll
-                    for (int j = 0; j < NP; ++j) unpack2(tv2[j], v[2 * j], v[2 * j + 1]);
-                    const float t0 = max3(v[0], v[1], v[2]), t1 = max3(v[3], v[4], v[5]), t2 = max3(v[6], v[7], v[8]);
-                    const float t3 = max3(v[9], v[10], v[11]), t4 = max3(v[12], v[13], v[14]);
-                    mt = fmaxf(max3(t0, t1, v[15]), max3(t2, t3, t4)) * p.scale_log2;
+                    for (int j = 0; j < NP; ++j) {
+                        float v0, v1;
+                        unpack2(tv2[j], v0, v1);
+                        t[j] = fmaxf(v0, v1);
+                    }
+                    const float u0 = max3(t[0], t[1], t[2]), u1 = max3(t[3], t[4], t[5]), u2 = max3(t[6], t[7], t[8]);
+                    const float u3 = max3(t[9], t[10], t[11]), u4 = max3(t[12], t[13], t[14]);
+                    mt = fmaxf(max3(u0, u1, t[15]), max3(u2, u3, u4)) * p.scale_log2;
                 }
-                ctl->row_max[sb][chalf][row] = mt;
+                if (warp == 0 || warp == 4) PROF(7, it, 2);
+                // ---- the row's reference maximum, moved in tile order.  This is the only step that waits
+                // for the tile before (per lane quadrant: the warp of the previous team with the same rows),
+                // and it is a handful of instructions: read the reference, move it if the tile's maximum
+                // exceeds it by more than the lazy margin of 8, publish.
+                if (!first)
+                    if (!warp_wait(smem_u32(&ctl->m_bar[buf_of<kFp8>(it - 1)][quad]), phase_of<kFp8>(it - 1), abort_flag)) goto done;
+                const float m_cur = first ? -INFINITY : ctl->m_shared[row];
+                const bool raise = mt > m_cur + 8.0f;
+                const float m_fin = raise ? mt : m_cur;
+                if (raise || first) ctl->m_shared[row] = m_fin;
                 __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&ctl->mx_bar[sb]));
-                if (!warp_wait(smem_u32(&ctl->mx_bar[sb]), ph, abort_flag)) goto done;
-                mt = fmaxf(ctl->row_max[sb][0][row], ctl->row_max[sb][1][row]);
-                if (warp == 0 || warp == 8) PROF(7, it, 2);
-                // ---- P against the tile's own row maximum.  The row's reference maximum is known only at the
-                // commit (the other team may still move it); P is brought to it there by one factor, so the
-                // result does not depend on which team was faster.
-                const float m_c = mt;
-                const float m_c_use = (m_c == -INFINITY) ? 0.0f : m_c;
+                if (lane == 0) mbar_arrive(smem_u32(&ctl->m_bar[tb][quad]));
+                if (warp == 0 || warp == 4) PROF(7, it, 3);
+                // ---- P = 2^(score - reference): at most 2^8; a masked slot gives 0
+                const float m_fin_use = (m_fin == -INFINITY) ? 0.0f : m_fin;
                 float lsum;
                 {
-                    const uint64_t c2 = pack2(p.scale_log2, p.scale_log2), nm2 = pack2(-m_c_use, -m_c_use);
+                    const uint64_t c2 = pack2(p.scale_log2, p.scale_log2), nm2 = pack2(-m_fin_use, -m_fin_use);
                     uint64_t ls2 = pack2(0.0f, 0.0f);
 #pragma unroll
                     for (int j = 0; j < NP; ++j) {
@@ -622,77 +641,61 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     unpack2(ls2, l0, l1);
                     lsum = l0 + l1;
                 }
-                if (warp == 0 || warp == 8) PROF(4, it, 1);
-                // ---- commit, in tile order: after the previous tile's commit (its P is released) ...
-                if (!first)
-                    if (!warp_wait(smem_u32(&ctl->p_full[buf_of<kFp8>(it - 1)]), phase_of<kFp8>(it - 1), abort_flag)) goto done;
-                // ... and after the P V product that last read this tile's P buffer
+                if (l_part != 0.0f && l_ref != m_fin) l_part *= ex2_approx(l_ref - m_fin);
+                l_part += lsum;
+                l_ref = m_fin;
+                // P as the MMA wants it: bf16 pairs; fp8 cache: two copies, each pre-multiplied by one scale
+                // group's row scales
+                constexpr int kPVariants = kFp8 ? 2 : 1;
+                uint32_t pk[kPVariants][NP];
+                if (kFp8) {
+#pragma unroll
+                    for (int v = 0; v < 2; ++v) {
+                        const float4* sc = reinterpret_cast<const float4*>(ctl->row_scale[it % kScaleSlots][v]);
+#pragma unroll
+                        for (int j = 0; j < CPT / 4; ++j) {
+                            const float4 w4 = sc[j];
+                            pk[v][2 * j] = pack_bf16x2_from2(mul2(tv2[2 * j], pack2(w4.x, w4.y)));
+                            pk[v][2 * j + 1] = pack_bf16x2_from2(mul2(tv2[2 * j + 1], pack2(w4.z, w4.w)));
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < NP; ++j) pk[0][j] = pack_bf16x2_from2(tv2[j]);
+                }
+                if (warp == 0 || warp == 4) PROF(4, it, 1);
+                // ---- hand P to the MMA warp: after the P V product that last read this tile's P buffer
                 if (it >= kBufReuse<kFp8>)
                     if (!warp_wait(smem_u32(&ctl->pv_done[buf_of<kFp8>(it - kBufReuse<kFp8>)]), phase_of<kFp8>(it - kBufReuse<kFp8>), abort_flag))
                         goto done;
-                if (warp == 0 || warp == 8) PROF(7, it, 3);
-                const float m_cur = first ? -INFINITY : ctl->m_shared[row];
-                const bool raise = mt > m_cur + 8.0f;   // lazy: move the reference only past a margin of 8
-                const float m_fin = raise ? mt : m_cur;
-                const float m_fin_use = (m_fin == -INFINITY) ? 0.0f : m_fin;
-                // own maximum -> reference: at most 2^8 (the lazy margin); a fully masked row has P = 0
-                const float f1 = (m_c == -INFINITY) ? 0.0f : ((m_c == m_fin) ? 1.0f : ex2_approx(m_c_use - m_fin_use));
-                if (!__all_sync(0xffffffffu, f1 == 1.0f)) {
-                    const uint64_t f12 = pack2(f1, f1);
-#pragma unroll
-                    for (int j = 0; j < NP; ++j) tv2[j] = mul2(tv2[j], f12);
-                }
-                if (__any_sync(0xffffffffu, raise)) {
-                    if (!first) {
-                        // O so far is complete once the previous tile's P V product has finished
-                        if (!warp_wait(smem_u32(&ctl->pv_done[buf_of<kFp8>(it - 1)]), phase_of<kFp8>(it - 1), abort_flag)) goto done;
-                        tc_fence_after();
-                        const float f2 = (m_cur == -INFINITY) ? 0.0f : ex2_approx(m_cur - m_fin);
+                if (__any_sync(0xffffffffu, raise) && !first) {
+                    // the reference moved: O so far (complete once the previous tile's P V product has finished)
+                    // is brought to the new reference before this tile's product is added
+                    if (!warp_wait(smem_u32(&ctl->pv_done[buf_of<kFp8>(it - 1)]), phase_of<kFp8>(it - 1), abort_flag)) goto done;
+                    tc_fence_after();
+                    const float f2 = raise ? ((m_cur == -INFINITY) ? 0.0f : ex2_approx(m_cur - m_fin)) : 1.0f;
 #pragma unroll 1
-                        for (int oc = chalf * (kDvHalf / 2); oc < (chalf + 1) * (kDvHalf / 2); oc += 32) {
-                            uint32_t o[32];
-                            tmem_ld32(lane_base + kColO + oc, o);
-                            tmem_wait_ld();
+                    for (int oc = 0; oc < kDvHalf; oc += 32) {
+                        uint32_t o[32];
+                        tmem_ld32(lane_base + kColO + oc, o);
+                        tmem_wait_ld();
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * f2);
-                            tmem_st32(lane_base + kColO + oc, o);
-                        }
-                        tmem_wait_st();
+                        for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * f2);
+                        tmem_st32(lane_base + kColO + oc, o);
                     }
+                    tmem_wait_st();
                 }
-                if (chalf == 0 && (raise || first)) ctl->m_shared[row] = m_fin;
-                if (l_part != 0.0f && l_ref != m_fin) l_part *= ex2_approx(l_ref - m_fin);
-                l_part = fmaf(lsum, f1, l_part);
-                l_ref = m_fin;
                 {
-                    const uint32_t p0col = lane_base + p_col_of<kFp8>(it) + chalf * (CPT / 2);
-                    if (kFp8) {
-                        const float4* sa = reinterpret_cast<const float4*>(ctl->row_scale[it % kScaleSlots][0] + c0);
-                        const float4* sb4 = reinterpret_cast<const float4*>(ctl->row_scale[it % kScaleSlots][1] + c0);
-                        uint32_t pk0[NP], pk1[NP];
+                    const uint32_t p0col = lane_base + p_col_of<kFp8>(it);
 #pragma unroll
-                        for (int j = 0; j < CPT / 4; ++j) {
-                            const float4 wa = sa[j], wb = sb4[j];
-                            pk0[2 * j] = pack_bf16x2_from2(mul2(tv2[2 * j], pack2(wa.x, wa.y)));
-                            pk0[2 * j + 1] = pack_bf16x2_from2(mul2(tv2[2 * j + 1], pack2(wa.z, wa.w)));
-                            pk1[2 * j] = pack_bf16x2_from2(mul2(tv2[2 * j], pack2(wb.x, wb.y)));
-                            pk1[2 * j + 1] = pack_bf16x2_from2(mul2(tv2[2 * j + 1], pack2(wb.z, wb.w)));
-                        }
-                        tmem_st_n<NP>(p0col, pk0);
-                        tmem_st_n<NP>(p0col + 16, pk1);
-                    } else {
-                        uint32_t pk[NP];
-#pragma unroll
-                        for (int j = 0; j < NP; ++j) pk[j] = pack_bf16x2_from2(tv2[j]);
-                        tmem_st_n<NP>(p0col, pk);
-                    }
+                    for (int v = 0; v < kPVariants; ++v) tmem_st_n<NP>(p0col + 16 * v, pk[v]);
                 }
-                if (warp == 0 || warp == 8) PROF(4, it, 2);
+                if (warp == 0 || warp == 4) PROF(4, it, 2);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&ctl->p_full[tb]));
-                if (warp == 0 || warp == 8) PROF(2, it, 3);
+                if (warp == 0 || warp == 4) PROF(2, it, 3);
             }
             // ---- epilogue of the item (all sixteen warps)
             {

@@ -100,11 +100,17 @@ constexpr int kGroups = 4;                                // softmax warpgroups 
 constexpr int kSoftmaxWarps = 4 * kGroups;
 constexpr int kMmaWarp = kSoftmaxWarps;                   // issues the score MMAs (and owns the TMEM allocation)
 constexpr int kPvWarp = kSoftmaxWarps + 1;                // issues the P V MMAs
-constexpr int kLoaderWarp0 = kSoftmaxWarps + 2;           // bf16 cache: four loader warps (two more stay idle)
-constexpr int kLoaderWarps = 4;
-constexpr int kGatherWarp0 = kSoftmaxWarps + 2;           // fp8 cache: two gather issuers ...
+constexpr int kGatherWarp0 = kSoftmaxWarps + 2;           // fp8 cache: two gather issuers (idle for a bf16 cache) ...
 constexpr int kGatherWarps = 2;
-constexpr int kConvertWarp0 = kGatherWarp0 + kGatherWarps; // ... and four converters
+constexpr int kConvertWarp0 = kGatherWarp0 + kGatherWarps; // ... and eight converters (two warpgroups)
+constexpr int kConvertWarps = 8;
+constexpr int kLoaderWarp0 = kConvertWarp0;               // bf16 cache: four loader warps (the next four stay idle)
+constexpr int kLoaderWarps = 4;
+constexpr int kWarps = kConvertWarp0 + kConvertWarps;     // 28: seven warpgroups
+// Registers per thread after the role split (setmaxnreg, per warpgroup): the softmax warpgroups hold a
+// tile row in registers, everything else is light.  4 x 128 x 88 + 3 x 128 x 48 = 63 488 <= 65 536.
+constexpr int kRegsSoftmax = 88;
+constexpr int kRegsOther = 48;
 constexpr int kScaleSlots = 16;                           // tiles whose row scales are kept (raw ring + tile ring <= 16)
 
 template <bool kFp8>
@@ -115,7 +121,7 @@ struct Cfg {
     static constexpr int kQSmemBytes = kFp8 ? kQBlockBytes : 0;
     static constexpr int kKvStages = kFp8 ? DSA_FP8_KV_STAGES : 6;   // MMA-ready bf16 tiles
     static constexpr int kRawStages = kFp8 ? DSA_FP8_RAW_STAGES : 0; // raw fp8 tiles in flight
-    static constexpr int kThreads = 32 * (kSoftmaxWarps + 2 + 6);
+    static constexpr int kThreads = 32 * kWarps;
     static constexpr int kOffKv = kQSmemBytes;
     static constexpr int kOffRaw = kOffKv + kKvStages * kKvTileBytes;
     static constexpr int kOffX = kOffRaw + kRawStages * kRawTileBytes;
@@ -129,8 +135,8 @@ struct Ctl {
     float row_scale[kScaleSlots][2][kTileRows];  // fp8 cache: per tile buffer, the scales of this CTA's two groups for every tile row
     uint64_t q_full, q_empty, o_free;
     uint64_t kv_full[8], kv_empty[8];
-    uint64_t raw_full[16];   // fp8 cache: [raw buffer][gather warp]: that warp's sixteen rows and their scales have landed
-    uint64_t raw_empty[16];  // ... and both converter warps that read them are done
+    uint64_t raw_full[16];   // fp8 cache, per raw buffer: the tile's rows and their scales have landed
+    uint64_t raw_empty[16];  // ... and the four converter warps that read them are done
     uint64_t s_full[kGroups], s_empty[kGroups], p_full[kGroups], pv_done[kGroups];
     uint64_t l_bar;
     uint64_t m_bar[kGroups][4];        // [team][lane quadrant]: the tile's reference-maximum step is done
@@ -300,12 +306,12 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         mbar_init(smem_u32(&ctl->o_free), kSoftmaxWarps);
         mbar_init(smem_u32(&ctl->l_bar), kSoftmaxWarps);
         for (int i = 0; i < 8; ++i) {
-            mbar_init(smem_u32(&ctl->kv_full[i]), kLoaderWarps);
+            mbar_init(smem_u32(&ctl->kv_full[i]), kFp8 ? kConvertWarps / 2 : kLoaderWarps);
             mbar_init(smem_u32(&ctl->kv_empty[i]), 1);
         }
         for (int i = 0; i < 16; ++i) {
-            mbar_init(smem_u32(&ctl->raw_full[i]), 1 + 16);   // the expect_tx arrival + sixteen cp.async arrivals
-            mbar_init(smem_u32(&ctl->raw_empty[i]), 2);
+            mbar_init(smem_u32(&ctl->raw_full[i]), 1 + 32);   // the expect_tx arrival + one cp.async arrival per row
+            mbar_init(smem_u32(&ctl->raw_empty[i]), 4);       // the four converter warps (one group) that read it
         }
         for (int i = 0; i < kGroups; ++i) {
             mbar_init(smem_u32(&ctl->s_full[i]), 1);
@@ -339,67 +345,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     if (tid == 0) PROF(5, 0, 1);
     const uint32_t peer_abort = map_to_cta(smem_u32(&ctl->abort_flag), peer);
 
-    if (warp == kMmaWarp) {
-        // ============================================================ score MMA issuer
-        // The whole warp runs the loop converged (descriptors stay warp-uniform); one elected lane issues.
-        // Scores and P V products are issued by two different warps, each blocking on its own inputs, so
-        // neither waits behind the other's barrier round trips; the tensor pipe runs them in issue order.
-        const uint32_t el = elect_one() ? 1u : 0u;
-        const uint64_t q_desc = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);
-        const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(sKV), 16, 1024);            // K-major view
-        uint32_t it = 0;
-        int item_n = 0;
-        for (int w = w_begin; w < w_end; ++w, ++item_n) {
-            const dsa_v32_work_info wi = p.works[w];
-            const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
-            if (!warp_wait(smem_u32(&ctl->q_full), item_n & 1, abort_flag)) goto done;
-            for (int t = 0; t < n_tiles; ++t, ++it) {
-                const int s = it % S;
-                const uint32_t sb = buf_of<kFp8>(it);
-                if (!warp_wait(smem_u32(&ctl->kv_full[s]), (it / S) & 1, abort_flag)) goto done;
-                // the softmax warps have drained the tile that used this score buffer last
-                if (it >= kBufReuse<kFp8>)
-                    if (!warp_wait(smem_u32(&ctl->s_empty[buf_of<kFp8>(it - kBufReuse<kFp8>)]), phase_of<kFp8>(it - kBufReuse<kFp8>), abort_flag))
-                        goto done;
-                tc_fence_after();
-                PROF(1, it, 0);
-                const uint64_t k_desc = k_desc0 + static_cast<uint64_t>((s * kKvTileBytes) >> 4);
-                const uint32_t d0 = tmem + s_col_of<kFp8>(it);
-                if (half) issue_qk_mmas<kFp8, 5>(d0, q_desc, tmem + kColQ, k_desc, el);
-                else issue_qk_mmas<kFp8, 4>(d0, q_desc, tmem + kColQ, k_desc, el);
-                PROF(7, it, 0);
-                tc_commit_el(smem_u32(&ctl->s_full[sb]), el);
-                if (t + 1 == n_tiles) tc_commit_el(smem_u32(&ctl->q_empty), el);
-                PROF(1, it, 1);
-            }
-        }
-    } else if (warp == kPvWarp) {
-        // ============================================================ P V MMA issuer
-        const uint32_t el = elect_one() ? 1u : 0u;
-        const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(sKV), kKvBlockBytes, 1024); // MN-major view
-        uint32_t it = 0;
-        int item_n = 0;
-        for (int w = w_begin; w < w_end; ++w, ++item_n) {
-            const dsa_v32_work_info wi = p.works[w];
-            const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
-            for (int t = 0; t < n_tiles; ++t, ++it) {
-                const int s = it % S;
-                const uint32_t sb = buf_of<kFp8>(it);
-                if (!warp_wait(smem_u32(&ctl->p_full[sb]), phase_of<kFp8>(it), abort_flag)) goto done;
-                if (t == 0 && item_n > 0)   // the previous item's O has been read out
-                    if (!warp_wait(smem_u32(&ctl->o_free), (item_n - 1) & 1, abort_flag)) goto done;
-                tc_fence_after();
-                PROF(1, it, 2);
-                issue_pv_mmas<kFp8>(tmem + kColO, tmem + p_col_of<kFp8>(it),
-                                    v_desc0 + static_cast<uint64_t>((s * kKvTileBytes) >> 4), t == 0, el);
-                PROF(6, it, 0);
-                tc_commit_el(smem_u32(&ctl->kv_empty[s]), el);
-                PROF(6, it, 1);
-                tc_commit_el(smem_u32(&ctl->pv_done[sb]), el);
-                PROF(1, it, 3);
-            }
-        }
-    } else if (warp < kSoftmaxWarps) {
+    if (warp < kSoftmaxWarps) {
+        // the four softmax warpgroups take the registers the light warpgroups give up (setmaxnreg is
+        // per warpgroup; each class of warpgroups executes one instruction at the top of its branch)
+        setmaxnreg_inc<kRegsSoftmax>();
         // ============================================================ softmax + epilogue
         // Four teams of four warps (one warp per TMEM lane quadrant) take the tiles round robin (team =
         // tile number mod 4 = exchange buffer and barrier index), so four tiles are in flight through the
@@ -762,6 +711,68 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
             it_base = it_end;
         }
+    } else {
+    setmaxnreg_dec<kRegsOther>();
+    if (warp == kMmaWarp) {
+        // ============================================================ score MMA issuer
+        // The whole warp runs the loop converged (descriptors stay warp-uniform); one elected lane issues.
+        // Scores and P V products are issued by two different warps, each blocking on its own inputs, so
+        // neither waits behind the other's barrier round trips; the tensor pipe runs them in issue order.
+        const uint32_t el = elect_one() ? 1u : 0u;
+        const uint64_t q_desc = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);
+        const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(sKV), 16, 1024);            // K-major view
+        uint32_t it = 0;
+        int item_n = 0;
+        for (int w = w_begin; w < w_end; ++w, ++item_n) {
+            const dsa_v32_work_info wi = p.works[w];
+            const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
+            if (!warp_wait(smem_u32(&ctl->q_full), item_n & 1, abort_flag)) goto done;
+            for (int t = 0; t < n_tiles; ++t, ++it) {
+                const int s = it % S;
+                const uint32_t sb = buf_of<kFp8>(it);
+                if (!warp_wait(smem_u32(&ctl->kv_full[s]), (it / S) & 1, abort_flag)) goto done;
+                // the softmax warps have drained the tile that used this score buffer last
+                if (it >= kBufReuse<kFp8>)
+                    if (!warp_wait(smem_u32(&ctl->s_empty[buf_of<kFp8>(it - kBufReuse<kFp8>)]), phase_of<kFp8>(it - kBufReuse<kFp8>), abort_flag))
+                        goto done;
+                tc_fence_after();
+                PROF(1, it, 0);
+                const uint64_t k_desc = k_desc0 + static_cast<uint64_t>((s * kKvTileBytes) >> 4);
+                const uint32_t d0 = tmem + s_col_of<kFp8>(it);
+                if (half) issue_qk_mmas<kFp8, 5>(d0, q_desc, tmem + kColQ, k_desc, el);
+                else issue_qk_mmas<kFp8, 4>(d0, q_desc, tmem + kColQ, k_desc, el);
+                PROF(7, it, 0);
+                tc_commit_el(smem_u32(&ctl->s_full[sb]), el);
+                if (t + 1 == n_tiles) tc_commit_el(smem_u32(&ctl->q_empty), el);
+                PROF(1, it, 1);
+            }
+        }
+    } else if (warp == kPvWarp) {
+        // ============================================================ P V MMA issuer
+        const uint32_t el = elect_one() ? 1u : 0u;
+        const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(sKV), kKvBlockBytes, 1024); // MN-major view
+        uint32_t it = 0;
+        int item_n = 0;
+        for (int w = w_begin; w < w_end; ++w, ++item_n) {
+            const dsa_v32_work_info wi = p.works[w];
+            const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
+            for (int t = 0; t < n_tiles; ++t, ++it) {
+                const int s = it % S;
+                const uint32_t sb = buf_of<kFp8>(it);
+                if (!warp_wait(smem_u32(&ctl->p_full[sb]), phase_of<kFp8>(it), abort_flag)) goto done;
+                if (t == 0 && item_n > 0)   // the previous item's O has been read out
+                    if (!warp_wait(smem_u32(&ctl->o_free), (item_n - 1) & 1, abort_flag)) goto done;
+                tc_fence_after();
+                PROF(1, it, 2);
+                issue_pv_mmas<kFp8>(tmem + kColO, tmem + p_col_of<kFp8>(it),
+                                    v_desc0 + static_cast<uint64_t>((s * kKvTileBytes) >> 4), t == 0, el);
+                PROF(6, it, 0);
+                tc_commit_el(smem_u32(&ctl->kv_empty[s]), el);
+                PROF(6, it, 1);
+                tc_commit_el(smem_u32(&ctl->pv_done[sb]), el);
+                PROF(1, it, 3);
+            }
+        }
     } else if (!kFp8) {
         // ============================================================ loaders (bf16 cache)
         // Four warps; warp lw owns rows [8 lw, 8 lw + 8) of every tile: it reads their top-k slots,
@@ -769,7 +780,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         // per group of four rows) straight into the swizzled MMA tile.  One warp can start a gather4 only
         // every ~70 cycles, several warps overlap, so the issue is spread over four.
         const int lw = warp - kLoaderWarp0;
-        if (lw < kLoaderWarps) {
+        if (lw >= 0 && lw < kLoaderWarps) {
             const int l8 = lane & 7;
             const int gsel = lane & 1;
             const int g = 2 * lw + gsel;             // group of four rows an issuing lane gathers
@@ -827,84 +838,92 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
     } else if (warp < kGatherWarp0 + kGatherWarps) {
         // ============================================================ gather issuers (fp8 cache)
-        // Two warps; warp iw owns rows [16 iw, 16 iw + 16) of every tile: top-k slots -> physical rows, one
-        // TMA tile::gather4 per group of four rows (the row's bytes of this CTA's slice in one request: the
-        // cache is described as 32-bit elements so that a request may be wider than 256 bytes), and the
-        // row's two scales by cp.async straight into the scale table.  The issuers run ahead of the
-        // converters by the raw ring (kRawStages tiles), across items.
+        // Two warps that take alternate tiles (an issue is a chain of latencies: slot and block-table loads,
+        // shuffles, the gather4 instructions themselves at ~70 cycles each; two tiles in flight hide it).
+        // Lane = row of the tile: top-k slot -> physical row; lanes 0-7 each issue ONE TMA tile::gather4 for a
+        // group of four rows (the row's bytes of this CTA's slice in one request: the cache is described as
+        // 32-bit elements so that a request may be wider than 256 bytes); every lane fetches its row's two
+        // scales by cp.async straight into the scale table.  The issuers run ahead of the converters by the
+        // raw ring (kRawStages tiles), across items.
         const int iw = warp - kGatherWarp0;
-        const int l16 = lane & 15;
-        const int gl = lane & 3;
+        const int gl = lane & 7;
         const int oob_row = (int)p.num_kv_rows;
         const uint32_t row_bytes = half ? 400u : 256u;   // latent half (+ scales + rope)
         const CUtensorMap* tmap = half ? &tm_kv_tail : &tm_kv;
         const int tcol = half ? 64 : 0;                  // first 32-bit element of the slice
-        uint16_t* mask_halves = reinterpret_cast<uint16_t*>(ctl->tile_mask);
         const uint8_t* kv_bytes = reinterpret_cast<const uint8_t*>(p.kv);
-        uint32_t it = 0;
+        uint32_t it_base = 0;
         for (int w = w_begin; w < w_end; ++w) {
             const dsa_v32_work_info wi = p.works[w];
             const int seq = wi.q_row / p.s_q;
             const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
             const int32_t* idx_row = p.indices + (size_t)wi.q_row * p.topk;
             auto load_slot = [&](int k0) -> int {
-                const int k = k0 + 16 * iw + l16;
+                const int k = k0 + lane;
                 return (k < wi.k_end) ? __ldg(idx_row + k) : -1;
             };
-            int idx_a = load_slot(wi.k_begin), idx_b = load_slot(wi.k_begin + kTileRows);
-            int idx_c = load_slot(wi.k_begin + 2 * kTileRows), idx_d = load_slot(wi.k_begin + 3 * kTileRows);
+            // this warp's tiles of the item: u0, u0 + 2, ...; two-deep software pipeline over them
+            const int u0 = (iw - (int)it_base) & 1;
+            const int kb0 = wi.k_begin + u0 * kTileRows;
+            int idx_a = load_slot(kb0), idx_b = load_slot(kb0 + 2 * kTileRows);
+            int idx_c = load_slot(kb0 + 4 * kTileRows), idx_d = load_slot(kb0 + 6 * kTileRows);
             int phys_a = block_of(idx_a, seq, p), phys_b = block_of(idx_b, seq, p);
-            for (int u = 0; u < n_tiles; ++u, ++it) {
+            for (int u = u0; u < n_tiles; u += 2) {
+                const uint32_t it = it_base + u;
                 const int k0 = wi.k_begin + u * kTileRows;
                 if (iw == 0) PROF(0, it, 1);
                 const int row = row_of(idx_a, phys_a, seq, p);
                 {
                     const int phys_n = block_of(idx_c, seq, p);
-                    const int idx_n = load_slot(k0 + 4 * kTileRows);
+                    const int idx_n = load_slot(k0 + 8 * kTileRows);
                     idx_a = idx_b; phys_a = phys_b;
                     idx_b = idx_c; phys_b = phys_n;
                     idx_c = idx_d; idx_d = idx_n;
                 }
-                const uint32_t mask16 = __ballot_sync(0xffffffffu, row >= 0) & 0xFFFFu;
+                const uint32_t mask = __ballot_sync(0xffffffffu, row >= 0);
                 const int coord = row >= 0 ? row : oob_row;
                 const int r0 = __shfl_sync(0xffffffffu, coord, 4 * gl + 0);
                 const int r1 = __shfl_sync(0xffffffffu, coord, 4 * gl + 1);
                 const int r2 = __shfl_sync(0xffffffffu, coord, 4 * gl + 2);
                 const int r3 = __shfl_sync(0xffffffffu, coord, 4 * gl + 3);
                 const int rs = it % R;
-                if (!warp_wait(smem_u32(&ctl->raw_empty[rs * 2 + iw]), ((it / R) & 1) ^ 1, abort_flag)) goto done;
+                if (!warp_wait(smem_u32(&ctl->raw_empty[rs]), ((it / R) & 1) ^ 1, abort_flag)) goto done;
                 if (iw == 0) PROF(0, it, 2);
-                const uint32_t bar = smem_u32(&ctl->raw_full[rs * 2 + iw]);
+                const uint32_t bar = smem_u32(&ctl->raw_full[rs]);
                 if (lane == 0) {
-                    mask_halves[(it % kMaskSlots) * 2 + iw] = static_cast<uint16_t>(mask16);
-                    mbar_arrive_expect_tx(bar, 16 * row_bytes);
+                    ctl->tile_mask[it % kMaskSlots] = mask;
+                    mbar_arrive_expect_tx(bar, kTileRows * row_bytes);
                 }
                 __syncwarp();
-                if (lane < 16) {
+                {
                     // the two fp32 scales of this CTA's groups: bytes 512 + 8 half of the row (zeros for padding)
                     const uint8_t* src = kv_bytes + (size_t)(row >= 0 ? row : 0) * kFp8RowBytes + 512 + 8 * half;
                     const uint32_t n = row >= 0 ? 4u : 0u;
-                    float* sc = &ctl->row_scale[it % kScaleSlots][0][16 * iw + l16];
+                    float* sc = &ctl->row_scale[it % kScaleSlots][0][lane];
                     cp_async_4(smem_u32(sc), src, n);
                     cp_async_4(smem_u32(sc + kTileRows), src + 4, n);
                     cp_async_mbar_arrive_noinc(bar);
                 }
-                if (lane < 4) {
-                    const uint32_t dst = smem_u32(sRaw + rs * kRawTileBytes + (4 * iw + lane) * kRawGroupBytes);
+                if (lane < 8) {
+                    const uint32_t dst = smem_u32(sRaw + rs * kRawTileBytes + lane * kRawGroupBytes);
                     tma_gather4(dst, tmap, bar, tcol, r0, r1, r2, r3);
                 }
                 if (iw == 0) PROF(0, it, 0);
             }
+            it_base += n_tiles;
         }
     } else {
         // ============================================================ converters (fp8 cache)
-        // Four warps; warp cw turns rows [8 cw, 8 cw + 8) of every raw tile into the bf16 MMA tile:
+        // Eight warps in two groups that take alternate tiles (a tile's conversion is a chain of latencies:
+        // raw bytes in, arithmetic, tile bytes out, proxy fence; two tiles in flight hide it).  In a group,
+        // warp c4 turns rows [8 c4, 8 c4 + 8) of the raw tile into the bf16 MMA tile:
         // e4m3 -> bf16 exactly (e4m3 has 4 significant bits; the reference's LDS round trip is
         // ..mxfp8_16mx8_32nx1_template.hpp:852-864), and copies the rope columns.  The per-128 fp32
         // scales never touch the operands (see the softmax warps).
         const int cw = warp - kConvertWarp0;
-        const int iw = cw >> 1;                  // the issuer warp that gathers this warp's rows
-        const int r = 8 * cw + (lane >> 2);      // tile row
+        const int grp = cw >> 2;                 // tiles this warp converts: it % 2 == grp
+        const int c4 = cw & 3;                   // rows [8 c4, 8 c4 + 8) of those tiles
+        const int r = 8 * c4 + (lane >> 2);      // tile row
         const int qd = lane & 3;                 // which 64 of this CTA's 256 latent columns
         const uint32_t row_bytes = half ? 400u : 256u;
         uint32_t it = 0;
@@ -922,8 +941,9 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 }
             }
             for (int t = 0; t < n_tiles; ++t, ++it) {
+                if ((it & 1u) != static_cast<uint32_t>(grp)) continue;
                 const int rs = it % R, s = it % S;
-                if (!warp_wait(smem_u32(&ctl->raw_full[rs * 2 + iw]), (it / R) & 1, abort_flag)) goto done;
+                if (!warp_wait(smem_u32(&ctl->raw_full[rs]), (it / R) & 1, abort_flag)) goto done;
                 if (cw == 0) PROF(3, it, 2);
                 if (!warp_wait(smem_u32(&ctl->kv_empty[s]), ((it / S) & 1) ^ 1, abort_flag)) goto done;
                 if (cw == 0) PROF(3, it, 0);
@@ -955,15 +975,17 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     *reinterpret_cast<uint4*>(d + (((2 * qd + 0) ^ (r & 7)) * 16)) = a;
                     *reinterpret_cast<uint4*>(d + (((2 * qd + 1) ^ (r & 7)) * 16)) = b;
                 }
+                if (cw == 0) PROF(3, it, 3);
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(smem_u32(&ctl->kv_full[s]));
-                    mbar_arrive(smem_u32(&ctl->raw_empty[rs * 2 + iw]));
+                    mbar_arrive(smem_u32(&ctl->raw_empty[rs]));
                 }
                 if (cw == 0) PROF(3, it, 1);
             }
         }
+    }
     }
 
 done:

@@ -140,8 +140,9 @@ struct Ctl {
     uint64_t s_full[kGroups], s_empty[kGroups], p_full[kGroups], pv_done[kGroups];
     uint64_t l_bar;
     uint64_t m_bar[kGroups][4];        // [team][lane quadrant]: the tile's reference-maximum step is done
-    uint64_t x_full[kSoftmaxWarps];    // bytes of the peer's partial scores for this warp's rows / columns
-    uint64_t x_free[kSoftmaxWarps];    // credit (4 bytes): the peer's same warp has read what this warp sent last
+    // Exchange of partial scores with the peer CTA: one buffer per team, barriers per softmax warp.
+    uint64_t x_full[kSoftmaxWarps];    // the peer's partial scores for this warp's rows have arrived (bytes)
+    uint64_t x_free[kSoftmaxWarps];    // credit (4 bytes): the peer's same warp has read what this warp sent
     uint32_t x_sink[kSoftmaxWarps];    // where the credit word lands
     float m_shared[kHeadsPerBlock];    // reference maximum of every row, moved only at a tile's commit
     uint32_t tile_mask[kMaskSlots];
@@ -364,11 +365,9 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const int team = cg;                 // tiles this warp works on: it % 4 == team
         const int quad = warp & 3;           // TMEM lane quadrant this warp may touch
         const int row = quad * 32 + lane;    // head row inside the block == TMEM lane
-        const int sb = team;                 // exchange buffer of the team
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(quad * 32) << 16);
         // exchange buffer of a tile: [8 chunks of 4 columns][128 rows][16 bytes]
-        const uint32_t x_off = static_cast<uint32_t>(sb * kXbufBytes) + static_cast<uint32_t>(row) * 16u;
-        const uint32_t peer_x = map_to_cta(smem_u32(sX), peer) + x_off;
+        const uint32_t peer_sx = map_to_cta(smem_u32(sX), peer);
         // the peer thread with the same (warp, lane) reads what this thread sends: one byte-counting
         // barrier per warp for arrival, one per warp for the credit "the peer has read the last one"
         const uint32_t my_xfull = smem_u32(&ctl->x_full[warp]);
@@ -377,7 +376,6 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const uint32_t peer_xfree = map_to_cta(my_xfree, peer);
         const uint32_t peer_xsink = map_to_cta(smem_u32(&ctl->x_sink[warp]), peer);
         uint32_t it_base = 0;   // global tile counter at the start of the item
-        uint32_t n_x = 0;       // exchanges this warp has done (phases of its two exchange barriers)
         int item_n = 0;
 
         // bf16 cache: this thread's share of an item's Q slice (its head row, a quarter of the slice's
@@ -452,6 +450,9 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 // two-wide forms (fma/mul/add .f32x2): half the instructions of the scalar forms.
                 uint64_t tv2[NP];
                 // ---- own partial scores out of TMEM
+                // exchange buffer of the team; the warp's own barriers advance once per tile of its team
+                const uint32_t x_off = static_cast<uint32_t>(team) * kXbufBytes + static_cast<uint32_t>(row) * 16u;
+                const uint32_t xph = (it / G) & 1u;
                 if (lane == 0) mbar_arrive_expect_tx(my_xfull, kXbufBytes / 4);
                 if (kFp8)
                     if (!warp_wait(smem_u32(&ctl->kv_full[it % S]), (it / S) & 1, abort_flag)) goto done;
@@ -461,31 +462,39 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 {
                     const uint32_t s0 = lane_base + s_col_of<kFp8>(it);
                     if (kFp8) {
-                        // 8 columns at a time (few live registers): accumulators of scale group a, scale group b
-                        // and, in the CTA that has them, the rope columns
+                        // 16 columns at a time: the accumulators of scale group a and scale group b, then (in the
+                        // CTA that has them) the rope columns.  The score buffer is single, so it is handed back
+                        // to the MMA warp the moment the last load has returned.
 #pragma unroll
-                        for (int hc = 0; hc < 4; ++hc) {
-                            uint32_t sr[8], sr2[8];
-                            tmem_ld_n<8>(s0 + 8 * hc, sr);
-                            tmem_ld_n<8>(s0 + 32 + 8 * hc, sr2);
-                            const float4* sa = reinterpret_cast<const float4*>(ctl->row_scale[it % kScaleSlots][0] + 8 * hc);
-                            const float4* sb4 = reinterpret_cast<const float4*>(ctl->row_scale[it % kScaleSlots][1] + 8 * hc);
-                            const float4 wa0 = sa[0], wa1 = sa[1], wb0 = sb4[0], wb1 = sb4[1];
+                        for (int hc = 0; hc < 2; ++hc) {
+                            uint32_t sr[16], sr2[16];
+                            tmem_ld_n<16>(s0 + 16 * hc, sr);
+                            tmem_ld_n<16>(s0 + 32 + 16 * hc, sr2);
+                            const float4* sa = reinterpret_cast<const float4*>(ctl->row_scale[it % kScaleSlots][0] + 16 * hc);
+                            const float4* sb4 = reinterpret_cast<const float4*>(ctl->row_scale[it % kScaleSlots][1] + 16 * hc);
                             tmem_wait_ld();
-                            tv2[4 * hc + 0] = fma2(pack2(wb0.x, wb0.y), pack2u(sr2[0], sr2[1]), mul2(pack2(wa0.x, wa0.y), pack2u(sr[0], sr[1])));
-                            tv2[4 * hc + 1] = fma2(pack2(wb0.z, wb0.w), pack2u(sr2[2], sr2[3]), mul2(pack2(wa0.z, wa0.w), pack2u(sr[2], sr[3])));
-                            tv2[4 * hc + 2] = fma2(pack2(wb1.x, wb1.y), pack2u(sr2[4], sr2[5]), mul2(pack2(wa1.x, wa1.y), pack2u(sr[4], sr[5])));
-                            tv2[4 * hc + 3] = fma2(pack2(wb1.z, wb1.w), pack2u(sr2[6], sr2[7]), mul2(pack2(wa1.z, wa1.w), pack2u(sr[6], sr[7])));
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const float4 wa = sa[j], wb = sb4[j];
+                                tv2[8 * hc + 2 * j] = fma2(pack2(wb.x, wb.y), pack2u(sr2[4 * j], sr2[4 * j + 1]),
+                                                           mul2(pack2(wa.x, wa.y), pack2u(sr[4 * j], sr[4 * j + 1])));
+                                tv2[8 * hc + 2 * j + 1] = fma2(pack2(wb.z, wb.w), pack2u(sr2[4 * j + 2], sr2[4 * j + 3]),
+                                                               mul2(pack2(wa.z, wa.w), pack2u(sr[4 * j + 2], sr[4 * j + 3])));
+                            }
                         }
                         if (half) {
+                            uint32_t sr3[32];
+                            tmem_ld_n<32>(s0 + 64, sr3);
+                            tmem_wait_ld();
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[tb]));
 #pragma unroll
-                            for (int hc = 0; hc < 2; ++hc) {
-                                uint32_t sr3[16];
-                                tmem_ld_n<16>(s0 + 64 + 16 * hc, sr3);
-                                tmem_wait_ld();
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) tv2[8 * hc + j] = add2(tv2[8 * hc + j], pack2u(sr3[2 * j], sr3[2 * j + 1]));
-                            }
+                            for (int j = 0; j < NP; ++j) tv2[j] = add2(tv2[j], pack2u(sr3[2 * j], sr3[2 * j + 1]));
+                        } else {
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[tb]));
                         }
                     } else {
                         uint32_t sr[CPT];
@@ -496,12 +505,14 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     }
                     if (warp == 0 || warp == 4) PROF(4, it, 0);
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[tb]));   // the MMA warp may overwrite the scores
+                if (!kFp8) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[tb]));   // the MMA warp may overwrite the scores
+                }
                 // ---- exchange: send when the peer has read what was sent last, add what it sent
-                if (n_x > 0)
-                    if (!warp_wait_cluster(my_xfree, (n_x - 1) & 1, abort_flag)) goto done;
+                if (it >= G)   // the peer has read what this warp sent last (its credit has arrived)
+                    if (!warp_wait_cluster(my_xfree, xph ^ 1u, abort_flag)) goto done;
                 if (lane == 0) mbar_arrive_expect_tx(my_xfree, 4);   // the credit for this send
                 if (warp == 0 || warp == 4) PROF(7, it, 1);
 #pragma unroll
@@ -509,10 +520,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     float v0, v1, v2, v3;
                     unpack2(tv2[2 * c], v0, v1);
                     unpack2(tv2[2 * c + 1], v2, v3);
-                    st_async_f32x4(peer_x + c * (kHeadsPerBlock * 16), v0, v1, v2, v3, peer_xfull);
+                    st_async_f32x4(peer_sx + x_off + c * (kHeadsPerBlock * 16), v0, v1, v2, v3, peer_xfull);
                 }
                 if (warp == 0 || warp == 4) PROF(2, it, 1);
-                if (!warp_wait_cluster(my_xfull, n_x & 1, abort_flag)) goto done;
+                if (!warp_wait_cluster(my_xfull, xph, abort_flag)) goto done;
                 if (warp == 0 || warp == 4) PROF(2, it, 2);
                 {
                     // credit: the peer may overwrite the buffer.  The credit word is computed from every lane's
@@ -529,7 +540,6 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     dep = __reduce_or_sync(0xffffffffu, dep);
                     if (lane == 0) st_async_u32(peer_xsink, dep, peer_xfree);
                 }
-                ++n_x;
                 if (!kFp8)
                     if (!warp_wait(smem_u32(&ctl->kv_full[it % S]), (it / S) & 1, abort_flag)) goto done;
                 // ---- mask (padding slots; the mask is the same for every row, so a full tile skips this)
@@ -909,6 +919,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     tma_gather4(dst, tmap, bar, tcol, r0, r1, r2, r3);
                 }
                 if (iw == 0) PROF(0, it, 0);
+                if (iw == 1) PROF(5, it, 3);
             }
             it_base += n_tiles;
         }
@@ -945,8 +956,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const int rs = it % R, s = it % S;
                 if (!warp_wait(smem_u32(&ctl->raw_full[rs]), (it / R) & 1, abort_flag)) goto done;
                 if (cw == 0) PROF(3, it, 2);
+                if (cw == 4) PROF(5, it, 2);
                 if (!warp_wait(smem_u32(&ctl->kv_empty[s]), ((it / S) & 1) ^ 1, abort_flag)) goto done;
                 if (cw == 0) PROF(3, it, 0);
+                if (cw == 4) PROF(5, it, 0);
                 const uint8_t* row_raw = sRaw + rs * kRawTileBytes + (r >> 2) * kRawGroupBytes + (r & 3) * row_bytes;
                 const uint8_t* src = row_raw + qd * 64;
                 uint8_t* dst_row = sKV + s * kKvTileBytes + qd * kKvBlockBytes + r * 128;
@@ -983,6 +996,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     mbar_arrive(smem_u32(&ctl->raw_empty[rs]));
                 }
                 if (cw == 0) PROF(3, it, 1);
+                if (cw == 4) PROF(5, it, 1);
             }
         }
     }

@@ -33,7 +33,40 @@ struct HostPlan {
 
 inline int64_t align256(int64_t x) { return (x + 255) & ~int64_t(255); }
 
-inline int build_plan(const dsa_v32_shape& sh, int num_sms, HostPlan& P) {
+// Header and byte offsets of a plan whose tables are filled in.
+inline void finish_plan(const dsa_v32_shape& sh, int L, int n_hb, int next_slot, HostPlan& P) {
+    WorkspaceHeader& h = P.hdr;
+    std::memset(&h, 0, sizeof(h));
+    h.magic = kWorkspaceMagic;
+    h.total_q = sh.total_q;
+    h.H = sh.H;
+    h.topk = sh.topk;
+    h.s_q = sh.s_q;
+    h.num_lists = L;
+    h.num_works = int(P.works.size());
+    h.num_partials = next_slot;
+    h.num_reduce_rows = int(P.reduce_dst.size());
+    h.num_head_blocks = n_hb;
+    int64_t off = 256;
+    h.off_list_indptr = off;
+    off = align256(off + int64_t(L + 1) * 4);
+    h.off_works = off;
+    off = align256(off + int64_t(P.works.size()) * sizeof(dsa_v32_work_info));
+    h.off_reduce_indptr = off;
+    off = align256(off + int64_t(P.reduce_indptr.size()) * 4);
+    h.off_reduce_slots = off;
+    off = align256(off + int64_t(std::max<size_t>(P.reduce_slots.size(), 1)) * 4);
+    h.off_reduce_dst = off;
+    off = align256(off + int64_t(std::max<size_t>(P.reduce_dst.size(), 1)) * sizeof(ReduceDst));
+    h.off_o_accum = off;
+    off = align256(off + int64_t(next_slot) * kHeadsPerBlock * kDV * 4);
+    h.off_lse_accum = off;
+    off = align256(off + int64_t(next_slot) * kHeadsPerBlock * 4);
+    h.total_bytes = off;
+}
+
+// Balanced plan: every list gets the same cost; units are cut where a list's share ends.
+inline int build_plan_split(const dsa_v32_shape& sh, int num_sms, HostPlan& P) {
     if (sh.total_q <= 0 || sh.H <= 0 || sh.topk <= 0 || sh.s_q <= 0) return DSA_V32_ERR_SHAPE;
     if (sh.total_q % sh.s_q != 0) return DSA_V32_ERR_SHAPE;
     if (num_sms < 2) return DSA_V32_ERR_SHAPE;
@@ -144,34 +177,87 @@ inline int build_plan(const dsa_v32_shape& sh, int num_sms, HostPlan& P) {
         P.list_indptr[list + 1] = int(P.works.size());
     }
 
-    WorkspaceHeader& h = P.hdr;
-    std::memset(&h, 0, sizeof(h));
-    h.magic = kWorkspaceMagic;
-    h.total_q = sh.total_q;
-    h.H = sh.H;
-    h.topk = sh.topk;
-    h.s_q = sh.s_q;
-    h.num_lists = L;
-    h.num_works = int(P.works.size());
-    h.num_partials = next_slot;
-    h.num_reduce_rows = int(P.reduce_dst.size());
-    h.num_head_blocks = n_hb;
-    int64_t off = 256;
-    h.off_list_indptr = off;
-    off = align256(off + int64_t(L + 1) * 4);
-    h.off_works = off;
-    off = align256(off + int64_t(P.works.size()) * sizeof(dsa_v32_work_info));
-    h.off_reduce_indptr = off;
-    off = align256(off + int64_t(P.reduce_indptr.size()) * 4);
-    h.off_reduce_slots = off;
-    off = align256(off + int64_t(std::max<size_t>(P.reduce_slots.size(), 1)) * 4);
-    h.off_reduce_dst = off;
-    off = align256(off + int64_t(std::max<size_t>(P.reduce_dst.size(), 1)) * sizeof(ReduceDst));
-    h.off_o_accum = off;
-    off = align256(off + int64_t(next_slot) * kHeadsPerBlock * kDV * 4);
-    h.off_lse_accum = off;
-    off = align256(off + int64_t(next_slot) * kHeadsPerBlock * 4);
-    h.total_bytes = off;
+    finish_plan(sh, L, n_hb, next_slot, P);
+    return DSA_V32_OK;
+}
+
+// Largest cost (tile steps + per-piece overhead) any list of the plan carries.
+inline int64_t plan_makespan(const HostPlan& P) {
+    int64_t worst = 0;
+    for (size_t l = 0; l + 1 < P.list_indptr.size(); ++l) {
+        int64_t c = 0;
+        for (int w = P.list_indptr[l]; w < P.list_indptr[l + 1]; ++w)
+            c += (P.works[w].k_end - P.works[w].k_begin + kTileRows - 1) / kTileRows + kPieceOverheadTiles;
+        worst = std::max(worst, c);
+    }
+    return worst;
+}
+
+// Plan without any split: whole units, longest first, each to the list that is least loaded so far.
+// No partial results, no merge; its lists are less even than those of the balanced plan.
+inline int build_plan_whole(const dsa_v32_shape& sh, int num_sms, HostPlan& P) {
+    if (sh.total_q <= 0 || sh.H <= 0 || sh.topk <= 0 || sh.s_q <= 0) return DSA_V32_ERR_SHAPE;
+    if (sh.total_q % sh.s_q != 0) return DSA_V32_ERR_SHAPE;
+    if (num_sms < 2) return DSA_V32_ERR_SHAPE;
+    const int L = num_sms / 2;
+    const int n_hb = (sh.H + kHeadsPerBlock - 1) / kHeadsPerBlock;
+    const int64_t n_units = int64_t(sh.total_q) * n_hb;
+    auto unit_len = [&](int64_t u) -> int {
+        int len = sh.topk;
+        if (sh.valid_len_hint) len = std::max(0, std::min(sh.topk, sh.valid_len_hint[u / n_hb]));
+        return len;
+    };
+    std::vector<int64_t> order(n_units);
+    for (int64_t u = 0; u < n_units; ++u) order[u] = u;
+    std::stable_sort(order.begin(), order.end(), [&](int64_t a, int64_t b) { return unit_len(a) > unit_len(b); });
+    // (load, list) min-heap
+    std::vector<std::pair<int64_t, int>> heap;
+    for (int l = 0; l < L; ++l) heap.emplace_back(0, l);
+    auto cmp = [](const std::pair<int64_t, int>& a, const std::pair<int64_t, int>& b) { return a > b; };
+    std::make_heap(heap.begin(), heap.end(), cmp);
+    std::vector<std::vector<dsa_v32_work_info>> per_list(L);
+    for (int64_t k = 0; k < n_units; ++k) {
+        const int64_t u = order[k];
+        const int len = std::max(unit_len(u), 1);
+        std::pop_heap(heap.begin(), heap.end(), cmp);
+        auto& top = heap.back();
+        dsa_v32_work_info w;
+        std::memset(&w, 0, sizeof(w));
+        w.q_row = int(u / n_hb);
+        w.head_block = int(u % n_hb);
+        w.k_begin = 0;
+        w.k_end = std::min(len, sh.topk);
+        w.partial_slot = -1;
+        w.reduce_row = -1;
+        per_list[top.second].push_back(w);
+        top.first += (len + kTileRows - 1) / kTileRows + kPieceOverheadTiles;
+        std::push_heap(heap.begin(), heap.end(), cmp);
+    }
+    P.list_indptr.assign(L + 1, 0);
+    P.works.clear();
+    P.reduce_indptr.assign(1, 0);
+    P.reduce_slots.clear();
+    P.reduce_dst.clear();
+    for (int l = 0; l < L; ++l) {
+        for (const auto& w : per_list[l]) P.works.push_back(w);
+        P.list_indptr[l + 1] = int(P.works.size());
+    }
+    finish_plan(sh, L, n_hb, 0, P);
+    return DSA_V32_OK;
+}
+
+// The plan a shape gets: the balanced one, unless the plan without splits is nearly as even.  A split
+// costs what the makespan does not show: fp32 partial results written and read back (4x the bytes of
+// the bf16 output) and the merge after the attention kernel, together worth about kMergeCostTiles steps.
+constexpr int kMergeCostTiles = 6;
+inline int build_plan(const dsa_v32_shape& sh, int num_sms, HostPlan& P) {
+    int rc = build_plan_split(sh, num_sms, P);
+    if (rc) return rc;
+    if (P.reduce_dst.empty()) return DSA_V32_OK;
+    HostPlan W;
+    rc = build_plan_whole(sh, num_sms, W);
+    if (rc) return rc;
+    if (plan_makespan(W) <= plan_makespan(P) + kMergeCostTiles) P = W;
     return DSA_V32_OK;
 }
 

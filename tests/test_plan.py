@@ -66,7 +66,17 @@ def check_plan(total_q, H, topk, s_q=1, num_sms=148, hint=None):
 
 
 def test_decode_config2_shape():
+    # 64 units on 74 lists: whole units (one list each, ten lists idle) are within the merge cost of the
+    # balanced plan, so the planner does not split at all - no partial results, no merge
     h, cost = check_plan(64, 128, 2048)
+    used = [c for c in cost if c > 0]
+    assert h["num_partials"] == 0 and len(used) == 64 and max(used) == min(used)
+
+
+def test_decode_split_when_it_pays():
+    # 16 units on 74 lists: whole units would leave 58 lists idle, so they are cut and merged
+    h, cost = check_plan(16, 128, 2048)
+    assert h["num_partials"] > 16
     assert max(cost) <= 1.25 * (sum(cost) / len(cost)) + 8
     assert min(cost) > 0
 

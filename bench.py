@@ -242,7 +242,7 @@ def run_prefill(args, rank, world, local_rank, torch, dist, api, workloads):
             roofline=dict(bound="tensor", achieved=tf, peak=pk["bf16_tflops"], unit="TFLOP/s", frac=tf / pk["bf16_tflops"],
                           traffic=None, peak_source=pk["source"], kernel="sparse_mla_kernel<bf16>",
                           flops_per_launch=flops, gathered_bytes_per_launch=total_pairs * 1152.0),
-            gpu_launches=K, clocks=sampler.summary())), flush=True)
+            gpu_launches=K * (2 if plan.info.num_partials > 0 else 1), clocks=sampler.summary())), flush=True)
 
 
 def e2e_leg(api, torch, W, plan, sm_scale, out, lse, K, barrier):
@@ -403,7 +403,7 @@ def main():
                                   t_mem_us=gathered / (pk["hbm_gbs"] * 1e9) * 1e6),
                     e2e=None if args.no_e2e else dict(value=world * step_flops / (e2e_ms / K * 1e-3) / 1e12, unit="TFLOP/s",
                                                       ms_per_step=e2e_ms / K, h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
-                    gpu_launches=2 * K, clocks=clocks)
+                    gpu_launches=K * (2 if plan.info.num_partials > 0 else 1), clocks=clocks)
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_block()
         print(json.dumps(line), flush=True)

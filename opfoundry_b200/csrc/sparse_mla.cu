@@ -74,7 +74,10 @@ __device__ __forceinline__ long long prof_now() {   // SM-local cycle counter (c
 // Stamps go to a shared-memory table (a clock read and one store, no global traffic on the path being
 // measured) that the CTA copies out when it exits: tiles [kProfTile0, kProfTile0 + 12) of the list,
 // 32-bit cycle counts, in the unused tail of the control block.
-constexpr int kProfTiles = 12, kProfTile0 = 6;
+#ifndef DSA_PROF_TILE0
+#define DSA_PROF_TILE0 6
+#endif
+constexpr int kProfTiles = 12, kProfTile0 = DSA_PROF_TILE0;
 #define PROF(role, tile, slot)                                                                      \
     do {                                                                                            \
         const uint32_t pt_ = static_cast<uint32_t>(tile) - kProfTile0;                              \
@@ -300,7 +303,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int w_begin = __ldg(p.list_indptr + list);
     const int w_end = __ldg(p.list_indptr + list + 1);
 
-    if (tid == 0) PROF(5, 0, 0);
+    if (tid == 0) PROF(5, kProfTile0 + 10, 0);
     if (tid == 0) {
         mbar_init(smem_u32(&ctl->q_full), kSoftmaxWarps + ((kFp8 && half) ? 1 : 0));   // + the rope block's TMA
         mbar_init(smem_u32(&ctl->q_empty), 1);
@@ -343,7 +346,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     cluster_sync_all();   // the peer's barriers exist before anything is sent to it
     tc_fence_after();
     const uint32_t tmem = ctl->tmem_base;
-    if (tid == 0) PROF(5, 0, 1);
+    if (tid == 0) PROF(5, kProfTile0 + 10, 1);
     const uint32_t peer_abort = map_to_cta(smem_u32(&ctl->abort_flag), peer);
 
     if (warp < kSoftmaxWarps) {
@@ -1007,13 +1010,13 @@ done:
     tc_fence_before();
     __syncthreads();
     if (tid == 0 && ctl->abort_flag) atomicExch(p.status, DSA_V32_ERR_DEVICE_WAIT);
-    if (tid == 0) PROF(5, 0, 2);
+    if (tid == 0) PROF(5, kProfTile0 + 10, 2);
 #ifdef DSA_PROFILE
     if (prof_on)
         for (int i = tid; i < 8 * kProfTiles * 4; i += blockDim.x) g_prof[(blockIdx.x & 1) * 8 * kProfTiles * 4 + i] = s_prof[i];
 #endif
     cluster_sync_all();
-    if (tid == 0) PROF(5, 0, 3);   // nobody leaves while the peer may still store into this CTA's shared memory
+    if (tid == 0) PROF(5, kProfTile0 + 10, 3);   // nobody leaves while the peer may still store into this CTA's shared memory
     if (warp == kMmaWarp) {
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);

@@ -18,30 +18,30 @@
 // softmax thread stores its row of partials into the peer's exchange buffer and arrives on the
 // peer's mbarrier); both CTAs then run the same softmax on the same numbers.
 //
-// Warp roles inside a CTA (23 warps for an fp8 cache, 19 for bf16):
-//   warps 0-15  softmax, as two teams of eight warps that take alternate 32-slot tiles (team = tile
-//              parity).  A team is two warpgroups; each owns 16 of the tile's 32 score columns and
-//              one thread per head row (= TMEM lane): tcgen05.ld of its partial scores, exchange
-//              with the peer CTA, log2-domain online softmax with lazy rescaling (the reference's
-//              threshold of 8: ..16mx4_64nx1_template.hpp:700-725), P -> bf16 -> tcgen05.st.  The
-//              teams work ahead of each other on scores but commit in tile order: the running
-//              maximum lives in shared memory, and a team that finds it moved while it worked
-//              corrects its P by the difference before storing.  Epilogue: O / l -> bf16, or the
-//              fp32 partial + lse of a split item.
-//   warp 16    producer: reads 32 top-k slots, translates them through the block table and
-//              gathers the rows with TMA tile::gather4 (bf16 cache: straight into the 128-byte
-//              swizzled MMA tile; fp8 cache: raw bytes), two tiles of index reads ahead; loads the
-//              Q slice once per item
-//   warp 17    score MMA issuer: S_c = Q_c K_c^T (tcgen05.mma M=128, N=32, K=16, accumulator in TMEM;
-//              bf16 cache: A = the Q slice held in TMEM, fp8 cache: A = Q in shared memory)
-//   warp 18    P V MMA issuer: O_c += P V_c (A = P in TMEM, B = the same gathered tile described
+// Warp roles inside a CTA (28 warps = seven warpgroups; after the role split setmaxnreg gives the four
+// softmax warpgroups 88 registers per thread and the others 48):
+//   warps 0-15  softmax, as four teams of four warps (one per TMEM lane quadrant) that take the 32-slot
+//              tiles round robin; thread = head row, holding its row's 32 scores of the tile: tcgen05.ld
+//              of the partial scores, exchange with the peer CTA, row maximum; then the only ordered
+//              step - the row's reference maximum in shared memory is read and moved when the tile's
+//              maximum exceeds it by more than the lazy margin (the reference's threshold of 8:
+//              ..16mx4_64nx1_template.hpp:700-725); P = 2^(s - reference) -> bf16 -> tcgen05.st.
+//              Epilogue: O / l -> bf16, or the fp32 partial + lse of a split item; during its waits the
+//              next item's Q slice is stored into TMEM (A operand of the score MMAs).
+//   warp 16    score MMA issuer: S_c = Q_c K_c^T (tcgen05.mma M=128, N=32, K=16, A = the Q slice in TMEM,
+//              accumulator in TMEM; fp8 cache: the 64 rope columns of Q stay in shared memory)
+//   warp 17    P V MMA issuer: O_c += P V_c (A = P in TMEM, B = the same gathered tile described
 //              MN-major).  Two issuers so that neither stream waits behind the other's barriers.
-//   warps 19-22 fp8 cache only: convert e4m3 -> bf16 exactly (e4m3 has 4 significant bits) into
-//              the swizzled MMA tile (the reference's LDS round trip:
-//              ..mxfp8_16mx8_32nx1_template.hpp:852-864).  The per-128 fp32 scales never touch the
-//              operands: Q K^T keeps one fp32 accumulator per scale group (plus one for rope) and
-//              the softmax warps form sum_g scale_g S_g in fp32 before the exchange; for P V they
-//              store one copy of P per scale group, pre-multiplied by that group's scale, and each
+//   bf16 cache: warps 20-23 loaders: 8 rows of every tile each: top-k slots -> block table -> TMA
+//              tile::gather4 straight into the 128-byte swizzled MMA tile (one warp can start a gather4
+//              only every ~70 cycles, so the issue is spread over four warps)
+//   fp8 cache: warps 18-19 gather issuers on alternate tiles (lane = row; one gather4 per four rows, the
+//              row's two scales by cp.async), warps 20-27 converters, two groups of four on alternate
+//              tiles: e4m3 -> bf16 exactly (e4m3 has 4 significant bits) into the swizzled MMA tile (the
+//              reference's LDS round trip: ..mxfp8_16mx8_32nx1_template.hpp:852-864).  The per-128 fp32
+//              scales never touch the operands: Q K^T keeps one fp32 accumulator per scale group (plus one
+//              for rope) and the softmax warps form sum_g scale_g S_g in fp32 before the exchange; for P V
+//              they store one copy of P per scale group, pre-multiplied by that group's scale, and each
 //              copy multiplies its own 128 output columns.
 //
 // Every mbarrier wait is bounded; on expiry the CTA raises its own and its peer's abort flag,

@@ -32,9 +32,9 @@
 //              accumulator in TMEM; fp8 cache: the 64 rope columns of Q stay in shared memory)
 //   warp 17    P V MMA issuer: O_c += P V_c (A = P in TMEM, B = the same gathered tile described
 //              MN-major).  Two issuers so that neither stream waits behind the other's barriers.
-//   bf16 cache: warps 20-23 loaders: 8 rows of every tile each: top-k slots -> block table -> TMA
-//              tile::gather4 straight into the 128-byte swizzled MMA tile (one warp can start a gather4
-//              only every ~70 cycles, so the issue is spread over four warps)
+//   bf16 cache: warps 20-27 loaders, two groups of four on alternate tiles, 8 rows of the tile per warp:
+//              top-k slots -> block table -> TMA tile::gather4 straight into the 128-byte swizzled MMA
+//              tile (one warp can start a gather4 only every ~70 cycles, so the issue is spread over warps)
 //   fp8 cache: warps 18-19 gather issuers on alternate tiles (lane = row; one gather4 per four rows, the
 //              row's two scales by cp.async), warps 20-27 converters, two groups of four on alternate
 //              tiles: e4m3 -> bf16 exactly (e4m3 has 4 significant bits) into the swizzled MMA tile (the
@@ -107,8 +107,8 @@ constexpr int kGatherWarp0 = kSoftmaxWarps + 2;           // fp8 cache: two gath
 constexpr int kGatherWarps = 2;
 constexpr int kConvertWarp0 = kGatherWarp0 + kGatherWarps; // ... and eight converters (two warpgroups)
 constexpr int kConvertWarps = 8;
-constexpr int kLoaderWarp0 = kConvertWarp0;               // bf16 cache: four loader warps (the next four stay idle)
-constexpr int kLoaderWarps = 4;
+constexpr int kLoaderWarp0 = kConvertWarp0;               // bf16 cache: eight loader warps, two groups of four
+constexpr int kLoaderWarps = 8;
 constexpr int kWarps = kConvertWarp0 + kConvertWarps;     // 28: seven warpgroups
 // Registers per thread after the role split (setmaxnreg, per warpgroup): the softmax warpgroups hold a
 // tile row in registers, everything else is light.  4 x 128 x 88 + 3 x 128 x 48 = 63 488 <= 65 536.
@@ -310,7 +310,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         mbar_init(smem_u32(&ctl->o_free), kSoftmaxWarps);
         mbar_init(smem_u32(&ctl->l_bar), kSoftmaxWarps);
         for (int i = 0; i < 8; ++i) {
-            mbar_init(smem_u32(&ctl->kv_full[i]), kFp8 ? kConvertWarps / 2 : kLoaderWarps);
+            mbar_init(smem_u32(&ctl->kv_full[i]), kFp8 ? kConvertWarps / 2 : kLoaderWarps / 2);   // one group per tile
             mbar_init(smem_u32(&ctl->kv_empty[i]), 1);
         }
         for (int i = 0; i < 16; ++i) {
@@ -788,38 +788,45 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
     } else if (!kFp8) {
         // ============================================================ loaders (bf16 cache)
-        // Four warps; warp lw owns rows [8 lw, 8 lw + 8) of every tile: it reads their top-k slots,
-        // translates them through the block table and gathers them with TMA tile::gather4 (two lanes, one
-        // per group of four rows) straight into the swizzled MMA tile.  One warp can start a gather4 only
-        // every ~70 cycles, several warps overlap, so the issue is spread over four.
+        // Eight warps in two groups that take alternate tiles; in a group, warp l4 owns rows [8 l4, 8 l4 + 8)
+        // of the tile: it reads their top-k slots, translates them through the block table and gathers them
+        // with TMA tile::gather4 (two lanes, one per group of four rows, one request per 64-column block)
+        // straight into the swizzled MMA tile.  One warp can start a gather4 only every ~70 cycles and the
+        // slot -> row translation is a chain of dependent loads, so the issue is spread over warps and
+        // over two tiles in flight.
         const int lw = warp - kLoaderWarp0;
         if (lw >= 0 && lw < kLoaderWarps) {
+            const int grp = lw >> 2;                 // tiles this warp loads: it % 2 == grp
+            const int l4 = lw & 3;
             const int l8 = lane & 7;
             const int gsel = lane & 1;
-            const int g = 2 * lw + gsel;             // group of four rows an issuing lane gathers
+            const int g = 2 * l4 + gsel;             // group of four rows an issuing lane gathers
             const int oob_row = (int)p.num_kv_rows;  // first row outside the tensor: the gather zero-fills it
             uint8_t* mask_bytes = reinterpret_cast<uint8_t*>(ctl->tile_mask);
-            uint32_t it = 0;
+            uint32_t it_base = 0;
             for (int w = w_begin; w < w_end; ++w) {
                 const dsa_v32_work_info wi = p.works[w];
                 const int seq = wi.q_row / p.s_q;
                 const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
                 const int32_t* idx_row = p.indices + (size_t)wi.q_row * p.topk;
-                // Two-deep software pipeline over tiles so no load is consumed in the step that issues it:
-                // slots of tiles u+2, u+3 are in flight, block numbers of tiles u, u+1 are in flight.
                 auto load_slot = [&](int k0) -> int {
-                    const int k = k0 + 8 * lw + l8;
+                    const int k = k0 + 8 * l4 + l8;
                     return (k < wi.k_end) ? __ldg(idx_row + k) : -1;
                 };
-                int idx_a = load_slot(wi.k_begin), idx_b = load_slot(wi.k_begin + kTileRows);
-                int idx_c = load_slot(wi.k_begin + 2 * kTileRows), idx_d = load_slot(wi.k_begin + 3 * kTileRows);
+                // this warp's tiles of the item: u0, u0 + 2, ...; two-deep software pipeline over them so no
+                // load is consumed in the step that issues it
+                const int u0 = (grp - (int)it_base) & 1;
+                const int kb0 = wi.k_begin + u0 * kTileRows;
+                int idx_a = load_slot(kb0), idx_b = load_slot(kb0 + 2 * kTileRows);
+                int idx_c = load_slot(kb0 + 4 * kTileRows), idx_d = load_slot(kb0 + 6 * kTileRows);
                 int phys_a = block_of(idx_a, seq, p), phys_b = block_of(idx_b, seq, p);
-                for (int u = 0; u < n_tiles; ++u, ++it) {
+                for (int u = u0; u < n_tiles; u += 2) {
+                    const uint32_t it = it_base + u;
                     const int k0 = wi.k_begin + u * kTileRows;
                     const int row = row_of(idx_a, phys_a, seq, p);
                     {
                         const int phys_n = block_of(idx_c, seq, p);
-                        const int idx_n = load_slot(k0 + 4 * kTileRows);
+                        const int idx_n = load_slot(k0 + 8 * kTileRows);
                         idx_a = idx_b; phys_a = phys_b;
                         idx_b = idx_c; phys_b = phys_n;
                         idx_c = idx_d; idx_d = idx_n;
@@ -836,7 +843,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     if (lw == 0) PROF(0, it, 2);
                     const uint32_t bar = smem_u32(&ctl->kv_full[s]);
                     if (lane == 0) {
-                        mask_bytes[(it % kMaskSlots) * 4 + lw] = static_cast<uint8_t>(mask8);
+                        mask_bytes[(it % kMaskSlots) * 4 + l4] = static_cast<uint8_t>(mask8);
                         mbar_arrive_expect_tx(bar, nkb * 8 * 128);
                     }
                     __syncwarp();
@@ -847,6 +854,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     }
                     if (lw == 0) PROF(0, it, 0);
                 }
+                it_base += n_tiles;
             }
         }
     } else if (warp < kGatherWarp0 + kGatherWarps) {

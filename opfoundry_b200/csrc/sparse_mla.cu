@@ -310,7 +310,8 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         mbar_init(smem_u32(&ctl->o_free), kSoftmaxWarps);
         mbar_init(smem_u32(&ctl->l_bar), kSoftmaxWarps);
         for (int i = 0; i < 8; ++i) {
-            mbar_init(smem_u32(&ctl->kv_full[i]), kFp8 ? kConvertWarps / 2 : kLoaderWarps / 2);   // one group per tile
+            // fp8: the four converter warps of a group; bf16: every lane of the four loader warps of a group
+            mbar_init(smem_u32(&ctl->kv_full[i]), kFp8 ? kConvertWarps / 2 : (kLoaderWarps / 2) * 32);
             mbar_init(smem_u32(&ctl->kv_empty[i]), 1);
         }
         for (int i = 0; i < 16; ++i) {
@@ -744,6 +745,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const int s = it % S;
                 const uint32_t sb = buf_of<kFp8>(it);
                 if (!warp_wait(smem_u32(&ctl->kv_full[s]), (it / S) & 1, abort_flag)) goto done;
+                if (!kFp8) fence_proxy_async_smem();   // the tile was written by cp.async (generic proxy)
                 // the softmax warps have drained the tile that used this score buffer last
                 if (it >= kBufReuse<kFp8>)
                     if (!warp_wait(smem_u32(&ctl->s_empty[buf_of<kFp8>(it - kBufReuse<kFp8>)]), phase_of<kFp8>(it - kBufReuse<kFp8>), abort_flag))
@@ -773,6 +775,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const int s = it % S;
                 const uint32_t sb = buf_of<kFp8>(it);
                 if (!warp_wait(smem_u32(&ctl->p_full[sb]), phase_of<kFp8>(it), abort_flag)) goto done;
+                if (!kFp8) {   // the tile was written by cp.async (generic proxy): observe its barrier, then fence
+                    if (!warp_wait(smem_u32(&ctl->kv_full[s]), (it / S) & 1, abort_flag)) goto done;
+                    fence_proxy_async_smem();
+                }
                 if (t == 0 && item_n > 0)   // the previous item's O has been read out
                     if (!warp_wait(smem_u32(&ctl->o_free), (item_n - 1) & 1, abort_flag)) goto done;
                 tc_fence_after();
@@ -789,20 +795,22 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     } else if (!kFp8) {
         // ============================================================ loaders (bf16 cache)
         // Eight warps in two groups that take alternate tiles; in a group, warp l4 owns rows [8 l4, 8 l4 + 8)
-        // of the tile: it reads their top-k slots, translates them through the block table and gathers them
-        // with TMA tile::gather4 (two lanes, one per group of four rows, one request per 64-column block)
-        // straight into the swizzled MMA tile.  One warp can start a gather4 only every ~70 cycles and the
-        // slot -> row translation is a chain of dependent loads, so the issue is spread over warps and
-        // over two tiles in flight.
+        // of the tile, four lanes per row: top-k slot -> block table -> physical row, then the row's 512
+        // or 640 bytes of this CTA's slice go straight into the 128-byte swizzled MMA tile as 16-byte
+        // cp.async copies (8-10 per lane), completion counted on the tile's barrier.  A TMA tile::gather4
+        // here moves one 128-byte block of four rows per request, 40 requests per tile, and the TMA unit
+        // takes a request only every ~25-37 cycles whatever the number of issuing warps (measured): that
+        // was the period of the whole bf16 pipeline.  (The fp8 path, 8 requests per tile, keeps gather4.)
         const int lw = warp - kLoaderWarp0;
         if (lw >= 0 && lw < kLoaderWarps) {
             const int grp = lw >> 2;                 // tiles this warp loads: it % 2 == grp
             const int l4 = lw & 3;
-            const int l8 = lane & 7;
-            const int gsel = lane & 1;
-            const int g = 2 * l4 + gsel;             // group of four rows an issuing lane gathers
-            const int oob_row = (int)p.num_kv_rows;  // first row outside the tensor: the gather zero-fills it
+            const int rloc = lane >> 2;              // row of the warp's eight this lane copies
+            const int r = 8 * l4 + rloc;             // tile row
+            const int c4 = lane & 3;                 // its 16-byte chunks: c4, c4 + 4, ...
             uint8_t* mask_bytes = reinterpret_cast<uint8_t*>(ctl->tile_mask);
+            const uint8_t* kv_bytes = reinterpret_cast<const uint8_t*>(p.kv);
+            const int n_chunks = nkb * 8;            // 16-byte chunks of a row's slice
             uint32_t it_base = 0;
             for (int w = w_begin; w < w_end; ++w) {
                 const dsa_v32_work_info wi = p.works[w];
@@ -810,7 +818,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
                 const int32_t* idx_row = p.indices + (size_t)wi.q_row * p.topk;
                 auto load_slot = [&](int k0) -> int {
-                    const int k = k0 + 8 * l4 + l8;
+                    const int k = k0 + r;
                     return (k < wi.k_end) ? __ldg(idx_row + k) : -1;
                 };
                 // this warp's tiles of the item: u0, u0 + 2, ...; two-deep software pipeline over them so no
@@ -831,27 +839,26 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         idx_b = idx_c; phys_b = phys_n;
                         idx_c = idx_d; idx_d = idx_n;
                     }
-                    const uint32_t mask8 = __ballot_sync(0xffffffffu, row >= 0) & 0xFFu;
-                    const int coord = row >= 0 ? row : oob_row;
-                    const int r0 = __shfl_sync(0xffffffffu, coord, 4 * gsel + 0);
-                    const int r1 = __shfl_sync(0xffffffffu, coord, 4 * gsel + 1);
-                    const int r2 = __shfl_sync(0xffffffffu, coord, 4 * gsel + 2);
-                    const int r3 = __shfl_sync(0xffffffffu, coord, 4 * gsel + 3);
+                    // one mask bit per row (lanes 0, 4, 8, ... hold the eight rows)
+                    const int row_of_lane8 = __shfl_sync(0xffffffffu, row, (lane & 7) * 4);
+                    const uint32_t mask8 = __ballot_sync(0xffffffffu, row_of_lane8 >= 0) & 0xFFu;
                     const int s = it % S;
                     if (lw == 0) PROF(0, it, 1);
                     if (!warp_wait(smem_u32(&ctl->kv_empty[s]), ((it / S) & 1) ^ 1, abort_flag)) goto done;
                     if (lw == 0) PROF(0, it, 2);
                     const uint32_t bar = smem_u32(&ctl->kv_full[s]);
-                    if (lane == 0) {
-                        mask_bytes[(it % kMaskSlots) * 4 + l4] = static_cast<uint8_t>(mask8);
-                        mbar_arrive_expect_tx(bar, nkb * 8 * 128);
+                    if (lane == 0) mask_bytes[(it % kMaskSlots) * 4 + l4] = static_cast<uint8_t>(mask8);
+                    // padding / out-of-range rows: nothing is read, the row is filled with zeros
+                    const uint8_t* src = kv_bytes + (size_t)(row >= 0 ? row : 0) * (kDQK * 2) + col0 * 2;
+                    const uint32_t nbytes = row >= 0 ? 16u : 0u;
+                    const uint32_t dst_row = smem_u32(sKV + s * kKvTileBytes) + r * 128;
+#pragma unroll
+                    for (int j = 0; j < 10; ++j) {
+                        const int cc = c4 + 4 * j;           // chunk of the slice: block cc / 8, chunk cc % 8 of its row
+                        if (cc < n_chunks)
+                            cp_async_16(dst_row + (cc >> 3) * kKvBlockBytes + (((cc & 7) ^ (r & 7)) << 4), src + cc * 16, nbytes);
                     }
-                    __syncwarp();
-                    if (lane < 2) {
-                        const uint32_t dst = smem_u32(sKV + s * kKvTileBytes + g * 512);
-                        for (int kb = 0; kb < nkb; ++kb)
-                            tma_gather4(dst + kb * kKvBlockBytes, &tm_kv, bar, col0 + kb * 64, r0, r1, r2, r3);
-                    }
+                    cp_async_mbar_arrive_noinc(bar);
                     if (lw == 0) PROF(0, it, 0);
                 }
                 it_base += n_tiles;

@@ -401,6 +401,50 @@ __device__ __forceinline__ void umma_ts_el(uint32_t d_tmem, uint32_t a_tmem, uin
         : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(elected)
         : "memory");
 }
+// Four MMAs of one 64-column block (K = 16 each) in one piece of assembly: the election predicate is
+// set up once and the operands of the steps differ by immediates (A: +8 TMEM columns or +32 bytes,
+// B: +32 bytes = +2 in descriptor units), so a step costs the issuing warp three instructions instead
+// of eight.  `first_accumulates` = 0 lets the first step overwrite D.  b_lo / b_hi (a_lo / a_hi): the two
+// halves of the shared-memory descriptor; adding to the low half cannot carry out of its 14-bit address
+// field because shared memory ends below 2^18 bytes.
+__device__ __forceinline__ void umma_ts_x4_el(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                              uint32_t first_accumulates, uint32_t elected) {
+    asm volatile(
+        "{\n\t.reg .pred q, pt, pf;\n\t.reg .b32 a, l;\n\t.reg .b64 bd;\n\t"
+        "setp.ne.b32 q, %6, 0;\n\t"
+        "setp.ne.b32 pf, %5, 0;\n\t"
+        "setp.eq.b32 pt, %6, %6;\n\t"
+        "mov.b64 bd, {%2, %3};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], bd, %4, pf;\n\t"
+        "add.u32 a, %1, 8;\n\tadd.u32 l, %2, 2;\n\tmov.b64 bd, {l, %3};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [a], bd, %4, pt;\n\t"
+        "add.u32 a, %1, 16;\n\tadd.u32 l, %2, 4;\n\tmov.b64 bd, {l, %3};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [a], bd, %4, pt;\n\t"
+        "add.u32 a, %1, 24;\n\tadd.u32 l, %2, 6;\n\tmov.b64 bd, {l, %3};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [a], bd, %4, pt;\n\t}"
+        :
+        : "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(first_accumulates), "r"(elected)
+        : "memory");
+}
+__device__ __forceinline__ void umma_ss_x4_el(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                              uint32_t idesc, uint32_t first_accumulates, uint32_t elected) {
+    asm volatile(
+        "{\n\t.reg .pred q, pt, pf;\n\t.reg .b32 la, lb;\n\t.reg .b64 ad, bd;\n\t"
+        "setp.ne.b32 q, %7, 0;\n\t"
+        "setp.ne.b32 pf, %6, 0;\n\t"
+        "setp.eq.b32 pt, %7, %7;\n\t"
+        "mov.b64 ad, {%1, %2};\n\tmov.b64 bd, {%3, %4};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], ad, bd, %5, pf;\n\t"
+        "add.u32 la, %1, 2;\n\tadd.u32 lb, %3, 2;\n\tmov.b64 ad, {la, %2};\n\tmov.b64 bd, {lb, %4};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], ad, bd, %5, pt;\n\t"
+        "add.u32 la, %1, 4;\n\tadd.u32 lb, %3, 4;\n\tmov.b64 ad, {la, %2};\n\tmov.b64 bd, {lb, %4};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], ad, bd, %5, pt;\n\t"
+        "add.u32 la, %1, 6;\n\tadd.u32 lb, %3, 6;\n\tmov.b64 ad, {la, %2};\n\tmov.b64 bd, {lb, %4};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], ad, bd, %5, pt;\n\t}"
+        :
+        : "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(first_accumulates), "r"(elected)
+        : "memory");
+}
 __device__ __forceinline__ void tc_commit_el(uint32_t bar, uint32_t elected) {
     asm volatile(
         "{\n\t.reg .pred q;\n\t"

@@ -229,18 +229,17 @@ __device__ __forceinline__ uint32_t e4m3x2_to_bf16x2(uint32_t hi_bytes) {
 template <bool kFp8, int NKB>
 __device__ __forceinline__ void issue_qk_mmas(uint32_t d0, uint64_t q_rope_desc, uint32_t q_tmem, uint64_t k_desc, uint32_t el) {
     constexpr uint32_t idesc = make_idesc_bf16(kHeadsPerBlock, kTileRows, false);
+    const uint32_t k_lo = static_cast<uint32_t>(k_desc), k_hi = static_cast<uint32_t>(k_desc >> 32);
 #pragma unroll
     for (int kb = 0; kb < NKB; ++kb) {
-#pragma unroll
-        for (int kin = 0; kin < 4; ++kin) {
-            const uint64_t b = k_desc + static_cast<uint64_t>((kb * kKvBlockBytes + kin * 32) >> 4);
-            if (!kFp8)
-                umma_ts_el(d0, q_tmem + kb * 32 + kin * 8, b, idesc, (kb | kin) ? 1u : 0u, el);   // A = Q from TMEM
-            else if (kb < 4)
-                umma_ts_el(d0 + (kb >> 1) * 32, q_tmem + kb * 32 + kin * 8, b, idesc, ((kb & 1) | kin) ? 1u : 0u, el);
-            else   // rope block of an fp8 item: A from shared memory, its own accumulator
-                umma_ss_el(d0 + 64, q_rope_desc + static_cast<uint64_t>((kin * 32) >> 4), b, idesc, kin ? 1u : 0u, el);
-        }
+        const uint32_t b_lo = k_lo + static_cast<uint32_t>((kb * kKvBlockBytes) >> 4);
+        if (!kFp8)   // A = Q from TMEM, one accumulator
+            umma_ts_x4_el(d0, q_tmem + kb * 32, b_lo, k_hi, idesc, kb ? 1u : 0u, el);
+        else if (kb < 4)   // one accumulator per scale group (two blocks)
+            umma_ts_x4_el(d0 + (kb >> 1) * 32, q_tmem + kb * 32, b_lo, k_hi, idesc, (kb & 1) ? 1u : 0u, el);
+        else   // rope block of an fp8 item: A from shared memory, its own accumulator
+            umma_ss_x4_el(d0 + 64, static_cast<uint32_t>(q_rope_desc), static_cast<uint32_t>(q_rope_desc >> 32), b_lo, k_hi,
+                          idesc, 0u, el);
     }
 }
 

@@ -124,6 +124,11 @@ struct Cfg {
     static constexpr int kQSmemBytes = kFp8 ? kQBlockBytes : 0;
     static constexpr int kKvStages = kFp8 ? DSA_FP8_KV_STAGES : 6;   // MMA-ready bf16 tiles
     static constexpr int kRawStages = kFp8 ? DSA_FP8_RAW_STAGES : 0; // raw fp8 tiles in flight
+    // The raw ring must have an even number of buffers: a buffer is then always filled by the same issuer
+    // warp and read by the same converter group, so a warp that waits for it to come back is never more
+    // than one phase ahead of its barrier (with an odd ring the users alternate and a parity wait could
+    // pass on the phase before last).
+    static_assert(!kFp8 || kRawStages % 2 == 0, "even raw ring");
     static constexpr int kThreads = 32 * kWarps;
     static constexpr int kOffKv = kQSmemBytes;
     static constexpr int kOffRaw = kOffKv + kKvStages * kKvTileBytes;

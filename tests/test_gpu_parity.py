@@ -149,6 +149,38 @@ def test_decode_bf16_golden_reference_vectors(oracle):
     check_lse(g_lse, g["lse"])
 
 
+@pytest.mark.parametrize("fp8", [False, True])
+def test_decode_padded_q_and_out_strides(oracle, fp8):
+    """Q and out are views with padded head and row strides (the library takes element strides, as the
+    reference's kargs do): the kernels read Q and write out through them."""
+    from gpu_util import to_dev, run_oracle
+    case = synth.make_decode_case(3, 128, 512, 150, fp8=fp8, paged=True, pad_frac=0.1, seed=61)
+    d = to_dev(case)
+    B, H = 3, 128
+    q_big = torch.zeros(B, H + 3, 640, dtype=torch.bfloat16, device="cuda")
+    q_big[:, :H, :576] = d["q"]
+    q = q_big[:, :H, :576]
+    out_big = torch.full((B, H + 1, 768), float("nan"), dtype=torch.bfloat16, device="cuda")
+    out = out_big[:, :H, :512]
+    lse = torch.empty(B, H, dtype=torch.float32, device="cuda")
+    plan = api.mla_decode_plan_create(B, H, 150, 1)
+    api.mla_decode_launch_pipeline(q, d["kv"], d["indices"], plan, SCALE, block_table=d["block_table"], page_block_size=64,
+                                   out=out, lse=lse)
+    torch.cuda.synchronize()
+    r_out, r_lse = run_oracle(oracle, case, SCALE)
+    g_out = out.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+    check_out(g_out, r_out, **(TOL_FP8 if fp8 else TOL_BF16))
+    check_lse(lse.cpu().numpy(), r_lse)
+    assert torch.isnan(out_big[:, H:, :].float()).all() and torch.isnan(out_big[:, :, 512:].float()).all()   # nothing written outside
+
+
+@pytest.mark.parametrize("fp8,page", [(False, 48), (True, 80), (True, 16)])
+def test_decode_page_sizes(oracle, fp8, page):
+    """Page sizes that are not powers of two take the divide / modulo translation; 16 the shift / mask one."""
+    case = synth.make_decode_case(3, 128, 960, 200, fp8=fp8, paged=True, page_block_size=page, pad_frac=0.05, seed=70 + page)
+    compare(case, oracle, TOL_FP8 if fp8 else TOL_BF16)
+
+
 def test_prefill_bf16_small_causal(oracle):
     T, topk = 300, 128
     case = synth.make_prefill_case(T, 128, topk, seed=21)

@@ -245,6 +245,87 @@ def run_prefill(args, rank, world, local_rank, torch, dist, api, workloads):
             gpu_launches=K * (2 if plan.info.num_partials > 0 else 1), clocks=sampler.summary())), flush=True)
 
 
+def run_decode_tp(args, rank, world, local_rank, torch, dist, api, workloads):
+    """fp8 decode with one MTP token, head-sharded (the TP layout of a serving stack): batch 128, two
+    query rows per sequence (half of the sequences share one index list between their rows), 128 heads in
+    total of which every rank attends 128 / N, kv_len 65536 in 64-token pages, top-k 2048, the latent cache
+    replicated on every rank; a step = attention on the local heads + one NCCL all-gather of the outputs.
+    Strong scaling: the total work is fixed.  Note what the layout costs: the tensor-core tile has 128 rows
+    (heads), so a rank with 128 / N heads still pays for 128, while its gathered bytes stay the same."""
+    from opfoundry_b200 import shard
+    B, s_q, H_all, kv_len, topk, page = args.batch if args.batch != 64 else 128, 2, 128, 65536, 2048, 64
+    h0, h1 = shard.shard_heads(H_all, world, rank)
+    Hl = h1 - h0
+    W = workloads.decode_fp8(B=B, H=H_all, kv_len=kv_len, topk=topk, page=page, pad_frac=0.0, n_batches=2, seed=2026, s_q=s_q)
+    total_q = B * s_q
+    g = torch.Generator(device="cuda")
+    g.manual_seed(99)
+    share = torch.rand(B, generator=g, device="cuda") < 0.5          # sequences whose two rows share a list
+    steps = []
+    for q, idx in W["steps"]:
+        idx = idx.clone().view(B, s_q, topk)
+        idx[share, 1] = idx[share, 0]
+        steps.append((q[:, h0:h1].contiguous(), idx.view(total_q, topk).contiguous()))
+    plan = api.mla_decode_plan_create(total_q, Hl, topk, s_q)
+    out = torch.empty(total_q, Hl, D_V, dtype=torch.bfloat16, device="cuda")
+    lse = torch.empty(total_q, Hl, dtype=torch.float32, device="cuda")
+    gathered = torch.empty(world, total_q, Hl, D_V, dtype=torch.bfloat16, device="cuda")   # rank-major; heads of rank r = block r
+    arg_sets = [api.make_args(q, W["cache"], idx, plan, 1.0 / math.sqrt(192.0), out=out, lse=lse, block_table=W["block_table"],
+                              page_block_size=page) for q, idx in steps]
+    L = api.lib()
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def step(i):
+        api._check(L.dsa_v32_decode_pipeline(C.byref(arg_sets[i % len(arg_sets)]), 0, stream), "decode step")
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, out)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    api._check(L.dsa_v32_device_status(C.byref(arg_sets[0]), stream), "device status")
+    K = args.steps
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    e0.record()
+    for i in range(K):
+        step(i)
+    e1.record()
+    barrier()
+    sampler.stop()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item()) / K
+    if rank == 0:
+        pk = peaks()
+        pairs = float(total_q * topk)
+        flops = flops_of(pairs, H_all)
+        tf = flops / (ms * 1e-3) / 1e12
+        launches = (2 if plan.info.num_partials > 0 else 1)
+        print(json.dumps(dict(
+            metric="sparse_mla_decode_fp8_mtp_tp_tflops", value=tf, unit="TFLOP/s", n_gpus=world, steps=K, warmup=args.warmup,
+            ms_per_step=ms, higher_is_better=True, scaling="strong", vs_baseline=None,
+            dtype="bf16 MMA, fp32 accumulate (fp8 e4m3 cache)", data="synthetic",
+            config=dict(workload="decode_fp8_mtp_b%d_sq2_h128_topk2048_kv65536_paged64_tp%d" % (B, world), batch=B, s_q=s_q,
+                        heads_total=H_all, heads_per_gpu=Hl, topk=topk, kv_len=kv_len,
+                        sharding="heads sharded %d per GPU, latent cache replicated, one NCCL all-gather of the outputs per step" % Hl,
+                        l2="every step gathers %.0f MB of rows > 126 MB L2" % (pairs * 656 / 1e6)),
+            roofline=dict(bound="tensor", achieved=tf, peak=world * pk["bf16_tflops"], unit="TFLOP/s",
+                          frac=tf / (world * pk["bf16_tflops"]), traffic=None, peak_source=pk["source"],
+                          kernel="sparse_mla_kernel<fp8> + all-gather", flops_per_launch=flops / world,
+                          gathered_bytes_per_launch=pairs * 656.0),
+            gpu_launches=K * launches, clocks=sampler.summary())), flush=True)
+
+
 def e2e_leg(api, torch, W, plan, sm_scale, out, lse, K, barrier):
     """K steps through the host-buffer C-ABI call: pinned host q / index lists in, out / lse back,
     the caller synchronising on every step's result."""
@@ -282,8 +363,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--batch", type=int, default=CFG["B"], help="sequences per GPU (smaller only for profiler captures)")
-    ap.add_argument("--workload", default="decode_fp8", choices=["decode_fp8", "prefill_bf16"],
-                    help="decode_fp8: the headline; prefill_bf16: one 4096-token causal prefill (second half of the metric)")
+    ap.add_argument("--workload", default="decode_fp8", choices=["decode_fp8", "prefill_bf16", "decode_fp8_tp"],
+                    help="decode_fp8: the headline; prefill_bf16: one causal prefill (second half of the metric; --tokens 131072 "
+                         "with --gpus 8 is the query-chunk-sharded long prefill); decode_fp8_tp: MTP decode with the heads "
+                         "sharded over the GPUs and an all-gather of the outputs")
     ap.add_argument("--tokens", type=int, default=4096, help="prefill_bf16: sequence length")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -311,6 +394,11 @@ def main():
     api.lib()
     if args.workload == "prefill_bf16":
         run_prefill(args, rank, world, local_rank, torch, dist, api, workloads)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    if args.workload == "decode_fp8_tp":
+        run_decode_tp(args, rank, world, local_rank, torch, dist, api, workloads)
         if world > 1:
             dist.destroy_process_group()
         return

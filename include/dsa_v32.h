@@ -221,7 +221,7 @@ int dsa_v32_device_status(const dsa_v32_attn_args* args, void* stream);
 /*
  * Debug entry point for index parity: writes, for every (query row, slot), the physical KV row
  * the kernel's translation resolves to (-1 for padding or an out-of-range row), using the
- * same device function as the attention kernel's producer warp.
+ * same device function as the attention kernel's loader warps.
  */
 int dsa_v32_debug_rows(const dsa_v32_attn_args* args, int32_t* rows_out, void* stream);
 

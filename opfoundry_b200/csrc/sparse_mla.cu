@@ -181,7 +181,7 @@ template <bool kFp8> __device__ __forceinline__ uint32_t p_col_of(uint32_t it) {
 
 // ------------------------------------------------------------------ index translation
 // Top-k slot value -> physical cache row, or -1 when the slot is padding / unusable.  Split in two so
-// the producer can issue the block-table load of one tile and finish the arithmetic tiles later:
+// the loader warps can issue the block-table load of one tile and finish the arithmetic tiles later:
 //   block_of(idx)        issues the block-table load (0 when there is nothing to load)
 //   row_of(idx, phys)    the physical row from the loaded block number
 __device__ __forceinline__ int block_of(int idx, int seq, const AttnParams& p) {

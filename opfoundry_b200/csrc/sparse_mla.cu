@@ -308,33 +308,35 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int w_end = __ldg(p.list_indptr + list + 1);
 
     if (tid == 0) PROF(5, kProfTile0 + 10, 0);
-    if (tid == 0) {
+    // Barrier initialisation, spread over threads (about 120 barriers; one thread doing them all took
+    // 2 000 cycles of every launch): thread i < 16 takes the i-th barrier of every 16-element family,
+    // threads 32-39 the tile barriers, 64-67 the per-team ones, 96 the singles.
+    if (tid < 16) {
+        mbar_init(smem_u32(&ctl->raw_full[tid]), 1 + 32);   // the expect_tx arrival + one cp.async arrival per row
+        mbar_init(smem_u32(&ctl->raw_empty[tid]), 4);       // the four converter warps (one group) that read it
+        mbar_init(smem_u32(&ctl->m_bar[0][0]) + 8 * tid, 1);
+        mbar_init(smem_u32(&ctl->x_full[tid]), 1);
+        mbar_init(smem_u32(&ctl->x_free[tid]), 1);
+        fence_mbar_init();
+    } else if (tid >= 32 && tid < 40) {
+        const int i = tid - 32;
+        // fp8: the four converter warps of a group; bf16: every lane of the four loader warps of a group
+        mbar_init(smem_u32(&ctl->kv_full[i]), kFp8 ? kConvertWarps / 2 : (kLoaderWarps / 2) * 32);
+        mbar_init(smem_u32(&ctl->kv_empty[i]), 1);
+        fence_mbar_init();
+    } else if (tid >= 64 && tid < 64 + kGroups) {
+        const int i = tid - 64;
+        mbar_init(smem_u32(&ctl->s_full[i]), 1);
+        mbar_init(smem_u32(&ctl->s_empty[i]), kSoftmaxWarps / kGroups);   // one team
+        mbar_init(smem_u32(&ctl->p_full[i]), kSoftmaxWarps / kGroups);
+        mbar_init(smem_u32(&ctl->pv_done[i]), 1);
+        fence_mbar_init();
+    } else if (tid == 96) {
         mbar_init(smem_u32(&ctl->q_full), kSoftmaxWarps + ((kFp8 && half) ? 1 : 0));   // + the rope block's TMA
         mbar_init(smem_u32(&ctl->q_empty), 1);
         mbar_init(smem_u32(&ctl->o_free), kSoftmaxWarps);
         mbar_init(smem_u32(&ctl->l_bar), kSoftmaxWarps);
-        for (int i = 0; i < 8; ++i) {
-            // fp8: the four converter warps of a group; bf16: every lane of the four loader warps of a group
-            mbar_init(smem_u32(&ctl->kv_full[i]), kFp8 ? kConvertWarps / 2 : (kLoaderWarps / 2) * 32);
-            mbar_init(smem_u32(&ctl->kv_empty[i]), 1);
-        }
-        for (int i = 0; i < 16; ++i) {
-            mbar_init(smem_u32(&ctl->raw_full[i]), 1 + 32);   // the expect_tx arrival + one cp.async arrival per row
-            mbar_init(smem_u32(&ctl->raw_empty[i]), 4);       // the four converter warps (one group) that read it
-        }
-        for (int i = 0; i < kGroups; ++i) {
-            mbar_init(smem_u32(&ctl->s_full[i]), 1);
-            mbar_init(smem_u32(&ctl->s_empty[i]), kSoftmaxWarps / kGroups);   // one team
-            mbar_init(smem_u32(&ctl->p_full[i]), kSoftmaxWarps / kGroups);
-            mbar_init(smem_u32(&ctl->pv_done[i]), 1);
-        }
-        for (int i = 0; i < kGroups * 4; ++i) mbar_init(smem_u32(&ctl->m_bar[0][0]) + 8 * i, 1);
         ctl->abort_flag = 0;
-        fence_mbar_init();
-        for (int w = 0; w < kSoftmaxWarps; ++w) {
-            mbar_init(smem_u32(&ctl->x_full[w]), 1);
-            mbar_init(smem_u32(&ctl->x_free[w]), 1);
-        }
         fence_mbar_init();
     }
     if (warp == kMmaWarp) {

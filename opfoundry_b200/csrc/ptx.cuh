@@ -128,6 +128,11 @@ __device__ __forceinline__ void st_async_f32x4(uint32_t caddr, float a, float b,
                  "f"(a), "f"(b), "f"(c), "f"(d), "r"(cbar)
                  : "memory");
 }
+__device__ __forceinline__ void st_async_b32x4(uint32_t caddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t cbar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(caddr),
+                 "r"(a), "r"(b), "r"(c), "r"(d), "r"(cbar)
+                 : "memory");
+}
 __device__ __forceinline__ void st_async_u32(uint32_t caddr, uint32_t v, uint32_t cbar) {
     asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.u32 [%0], %1, [%2];" ::"r"(caddr), "r"(v), "r"(cbar)
                  : "memory");

@@ -56,6 +56,9 @@
 #ifndef DSA_FP8_KV_STAGES
 #define DSA_FP8_KV_STAGES 4
 #endif
+#ifndef DSA_BF16_KV_STAGES
+#define DSA_BF16_KV_STAGES 6
+#endif
 #ifndef DSA_FP8_RAW_STAGES
 #define DSA_FP8_RAW_STAGES 4
 #endif
@@ -97,7 +100,10 @@ constexpr int kKvBlockBytes = kTileRows * 128;            // 4096: one 64-column
 constexpr int kKvTileBytes = kMaxKBlocks * kKvBlockBytes; // 20480
 constexpr int kRawGroupBytes = 1024 + 640;                // 4 rows: 4 x 256 latent bytes | 4 x 144 tail (+pad)
 constexpr int kRawTileBytes = (kTileRows / 4) * kRawGroupBytes;   // 13312
-constexpr int kXbufBytes = kHeadsPerBlock * kTileRows * 4;        // 16384: one tile of fp32 partial scores
+constexpr int kXRowBytes = kTileRows * 2 + 4;                     // a row's partial scores as 16-bit fixed point + its step (fp32)
+constexpr int kXInvOff = kHeadsPerBlock * kTileRows * 2;          // the steps follow the 4 chunks x 128 rows x 16 bytes
+constexpr int kXbufBytes = kHeadsPerBlock * kXRowBytes;           // 8704: one tile of partial scores
+constexpr float kQuantBias = 8421376.0f;                          // 2^23 + 2^15: adding it leaves round(x) + 32768 in the low mantissa bits
 constexpr int kMaskSlots = 16;
 constexpr int kGroups = 4;                                // softmax warpgroups sharing a tile's columns
 constexpr int kSoftmaxWarps = 4 * kGroups;
@@ -122,7 +128,7 @@ struct Cfg {
     // from global memory.  Only the rope block of an fp8 item stays in shared memory (TMEM is full).
     static constexpr bool kQInTmem = true;
     static constexpr int kQSmemBytes = kFp8 ? kQBlockBytes : 0;
-    static constexpr int kKvStages = kFp8 ? DSA_FP8_KV_STAGES : 6;   // MMA-ready bf16 tiles
+    static constexpr int kKvStages = kFp8 ? DSA_FP8_KV_STAGES : DSA_BF16_KV_STAGES;   // MMA-ready bf16 tiles
     static constexpr int kRawStages = kFp8 ? DSA_FP8_RAW_STAGES : 0; // raw fp8 tiles in flight
     // The raw ring must have an even number of buffers: a buffer is then always filled by the same issuer
     // warp and read by the same converter group, so a warp that waits for it to come back is never more
@@ -463,7 +469,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 // exchange buffer of the team; the warp's own barriers advance once per tile of its team
                 const uint32_t x_off = static_cast<uint32_t>(team) * kXbufBytes + static_cast<uint32_t>(row) * 16u;
                 const uint32_t xph = (it / G) & 1u;
-                if (lane == 0) mbar_arrive_expect_tx(my_xfull, kXbufBytes / 4);
+                if (lane == 0) mbar_arrive_expect_tx(my_xfull, 32 * kXRowBytes);
                 if (kFp8)
                     if (!warp_wait(smem_u32(&ctl->kv_full[it % S]), (it / S) & 1, abort_flag)) goto done;
                 if (!warp_wait(smem_u32(&ctl->s_full[tb]), tph, abort_flag)) goto done;
@@ -520,32 +526,71 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[tb]));   // the MMA warp may overwrite the scores
                 }
-                // ---- exchange: send when the peer has read what was sent last, add what it sent
+                // ---- exchange: the two CTAs' partial scores are summed through distributed shared memory.  The
+                // link between the two SMs carries only ~11-17 bytes per clock and direction, so the partials
+                // cross it as 16-bit fixed point with one power-of-two step per row and tile (step = 2^-15 of
+                // the row's largest partial: <= 3e-4 in the exponent for scores up to 128, against P rounded
+                // to bf16 afterwards), 68 bytes per row instead of 128.  Both CTAs add the two *quantised*
+                // partials, so they hold the same scores bit for bit.
+                uint32_t own_inv_bits;
+                {
+                    float amax = 0.0f;
+#pragma unroll
+                    for (int j = 0; j < NP; ++j) {
+                        float v0, v1;
+                        unpack2(tv2[j], v0, v1);
+                        amax = fmaxf(amax, fmaxf(fabsf(v0), fabsf(v1)));
+                    }
+                    // e = biased exponent of the largest partial (NaN/Inf -> the step becomes NaN and so do the scores)
+                    uint32_t e = __float_as_uint(amax) >> 23;
+                    e = e < 20u ? 20u : e;
+                    const float q_scale = __uint_as_float((268u - e) << 23) * 0.99996948f;   // largest partial -> < 32767.5
+                    own_inv_bits = e >= 255u ? 0x7FC00000u : __float_as_uint(__uint_as_float((e - 14u) << 23) * 1.0000305f);
+                    const uint64_t qs2 = pack2(q_scale, q_scale), qc2 = pack2(kQuantBias, kQuantBias);
+#pragma unroll
+                    for (int j = 0; j < NP; ++j) tv2[j] = fma2(tv2[j], qs2, qc2);   // 2^23 + 32768 + n: n in the low 16 bits
+                }
                 if (it >= G)   // the peer has read what this warp sent last (its credit has arrived)
                     if (!warp_wait_cluster(my_xfree, xph ^ 1u, abort_flag)) goto done;
                 if (lane == 0) mbar_arrive_expect_tx(my_xfree, 4);   // the credit for this send
                 if (warp == 0 || warp == 4) PROF(7, it, 1);
 #pragma unroll
-                for (int c = 0; c < NCH; ++c) {
-                    float v0, v1, v2, v3;
-                    unpack2(tv2[2 * c], v0, v1);
-                    unpack2(tv2[2 * c + 1], v2, v3);
-                    st_async_f32x4(peer_sx + x_off + c * (kHeadsPerBlock * 16), v0, v1, v2, v3, peer_xfull);
+                for (int c = 0; c < NCH / 2; ++c) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        w[k] = __byte_perm(static_cast<uint32_t>(tv2[4 * c + k]), static_cast<uint32_t>(tv2[4 * c + k] >> 32), 0x5410u);
+                    st_async_b32x4(peer_sx + x_off + c * (kHeadsPerBlock * 16), w[0], w[1], w[2], w[3], peer_xfull);
                 }
+                st_async_u32(peer_sx + static_cast<uint32_t>(team) * kXbufBytes + kXInvOff + static_cast<uint32_t>(row) * 4u, own_inv_bits,
+                             peer_xfull);
                 if (warp == 0 || warp == 4) PROF(2, it, 1);
+                {
+                    // own partials back from their quantised form while the peer's are on their way
+                    const float own_inv = __uint_as_float(own_inv_bits);
+                    const uint64_t oi2 = pack2(own_inv, own_inv), nb2 = pack2(-kQuantBias, -kQuantBias);
+#pragma unroll
+                    for (int j = 0; j < NP; ++j) tv2[j] = mul2(add2(tv2[j], nb2), oi2);
+                }
                 if (!warp_wait_cluster(my_xfull, xph, abort_flag)) goto done;
                 if (warp == 0 || warp == 4) PROF(2, it, 2);
                 {
                     // credit: the peer may overwrite the buffer.  The credit word is computed from every lane's
                     // loaded values, so it cannot leave before all of the warp's reads have returned.
-                    const ulonglong2* src = reinterpret_cast<const ulonglong2*>(sX + x_off);
-                    uint32_t dep = 0;
+                    const uint4* src = reinterpret_cast<const uint4*>(sX + x_off);
+                    const float peer_inv = *reinterpret_cast<const float*>(sX + team * kXbufBytes + kXInvOff + row * 4);
+                    const uint64_t pi2 = pack2(peer_inv, peer_inv), nb2 = pack2(-kQuantBias, -kQuantBias);
+                    uint32_t dep = __float_as_uint(peer_inv);
 #pragma unroll
-                    for (int c = 0; c < NCH; ++c) {
-                        const ulonglong2 o = src[c * kHeadsPerBlock];
-                        tv2[2 * c] = add2(tv2[2 * c], o.x);
-                        tv2[2 * c + 1] = add2(tv2[2 * c + 1], o.y);
-                        dep |= static_cast<uint32_t>(o.x);
+                    for (int c = 0; c < NCH / 2; ++c) {
+                        const uint4 o = src[c * kHeadsPerBlock];
+                        const uint32_t w[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const uint64_t b2 = pack2u(__byte_perm(w[k], 0x4B00u, 0x5410u), __byte_perm(w[k], 0x4B00u, 0x5432u));
+                            tv2[4 * c + k] = fma2(add2(b2, nb2), pi2, tv2[4 * c + k]);
+                        }
+                        dep |= o.x;
                     }
                     dep = __reduce_or_sync(0xffffffffu, dep);
                     if (lane == 0) st_async_u32(peer_xsink, dep, peer_xfree);

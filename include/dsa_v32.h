@@ -151,6 +151,14 @@ int dsa_v32_plan_read(const void* workspace, int64_t workspace_bytes, dsa_v32_wo
                       int32_t* list_indptr_out, int32_t max_lists_plus1, void* stream);
 
 /*
+ * Forgets the plan recorded for `workspace` (call before freeing or re-using the memory for something
+ * else; the library keeps the headers of the 256 most recently used plans).  The reference frees its plan
+ * with mla_decode_plan_destroy (common/host.cc:180-189); here the memory is the caller's, only the
+ * host-side record goes.  Returns DSA_V32_ERR_WORKSPACE when no plan is recorded for the pointer.
+ */
+int dsa_v32_plan_release(const void* workspace);
+
+/*
  * The attention kernel alone (final rows written directly, split rows as fp32 partials).
  * Replaces mla_decode_launch for the bf16 traits (common/host.cc:39-65) / the mxfp8 traits
  * (common/host.cc:32-37).  Prefill is the same kernel with one query row per token and no
@@ -166,7 +174,9 @@ int dsa_v32_combine(const dsa_v32_attn_args* args, void* stream);
 
 /*
  * plan (optional) -> attention -> combine on one stream: the drop-in for
- * mla_decode_launch_pipeline (common/host.cc:114-138).
+ * mla_decode_launch_pipeline (common/host.cc:114-138).  The return code covers argument checks and
+ * launch errors only: the launches are asynchronous, so a bounded device-side wait that ran out
+ * (DSA_V32_ERR_DEVICE_WAIT) is reported by dsa_v32_device_status, not here.
  */
 int dsa_v32_decode_pipeline(const dsa_v32_attn_args* args, int run_plan, void* stream);
 

@@ -52,7 +52,7 @@ class HostIO(C.Structure):
 
 
 EXPORTS = ["dsa_v32_abi_version", "dsa_v32_error_string", "dsa_v32_plan_info_get", "dsa_v32_plan",
-           "dsa_v32_plan_host", "dsa_v32_plan_read", "dsa_v32_decode_bf16", "dsa_v32_decode_fp8",
+           "dsa_v32_plan_host", "dsa_v32_plan_read", "dsa_v32_plan_release", "dsa_v32_decode_bf16", "dsa_v32_decode_fp8",
            "dsa_v32_prefill_bf16", "dsa_v32_combine", "dsa_v32_decode_pipeline", "dsa_v32_device_status",
            "dsa_v32_debug_rows", "dsa_v32_pack_fp8_rows", "dsa_v32_decode_pipeline_host",
            "dsa_v32_decode_pipeline_static", "dsa_v32_static_scratch_address"]
@@ -81,6 +81,7 @@ def lib():
         L.dsa_v32_plan.argtypes = [C.POINTER(Shape), C.c_void_p, C.c_int64, C.c_void_p]
         L.dsa_v32_plan_host.argtypes = [C.POINTER(Shape), C.c_void_p, C.c_int64, C.POINTER(C.c_int64)]
         L.dsa_v32_plan_read.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]
+        L.dsa_v32_plan_release.argtypes = [C.c_void_p]
         for name in ("dsa_v32_decode_bf16", "dsa_v32_decode_fp8", "dsa_v32_prefill_bf16", "dsa_v32_combine",
                      "dsa_v32_device_status"):
             getattr(L, name).argtypes = [C.POINTER(AttnArgs), C.c_void_p]

@@ -31,23 +31,42 @@ struct Registry {
     struct Entry {
         const void* ws;
         WorkspaceHeader hdr;
+        uint64_t last_use;
     };
     std::vector<Entry> entries;
+    uint64_t clock = 0;
+    static constexpr size_t kMaxEntries = 256;
     void put(const void* ws, const WorkspaceHeader& h) {
         std::lock_guard<std::mutex> g(mu);
         for (auto& e : entries)
             if (e.ws == ws) {
                 e.hdr = h;
+                e.last_use = ++clock;
                 return;
             }
-        if (entries.size() >= 256) entries.erase(entries.begin());
-        entries.push_back(Entry{ws, h});
+        if (entries.size() >= kMaxEntries) {   // drop the plan that has gone unused the longest
+            size_t victim = 0;
+            for (size_t i = 1; i < entries.size(); ++i)
+                if (entries[i].last_use < entries[victim].last_use) victim = i;
+            entries.erase(entries.begin() + victim);
+        }
+        entries.push_back(Entry{ws, h, ++clock});
     }
     bool get(const void* ws, WorkspaceHeader* h) {
         std::lock_guard<std::mutex> g(mu);
         for (auto& e : entries)
             if (e.ws == ws) {
                 *h = e.hdr;
+                e.last_use = ++clock;
+                return true;
+            }
+        return false;
+    }
+    bool drop(const void* ws) {
+        std::lock_guard<std::mutex> g(mu);
+        for (size_t i = 0; i < entries.size(); ++i)
+            if (entries[i].ws == ws) {
+                entries.erase(entries.begin() + i);
                 return true;
             }
         return false;
@@ -82,7 +101,7 @@ int resolve_sms(const dsa_v32_shape* shape, int* sms) {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-int check_args(const dsa_v32_attn_args* a, int want_dtype, WorkspaceHeader* hdr) {
+int check_args(const dsa_v32_attn_args* a, int want_dtype, WorkspaceHeader* hdr, const WorkspaceHeader* known = nullptr) {
     if (!a || !a->q || !a->kv || !a->out || !a->indices || !a->workspace) return DSA_V32_ERR_NULL;
     if (a->kv_dtype != want_dtype) return DSA_V32_ERR_DTYPE;
     if (a->total_q <= 0 || a->H <= 0 || a->topk <= 0 || a->s_q <= 0 || a->total_q % a->s_q != 0) return DSA_V32_ERR_SHAPE;
@@ -96,7 +115,8 @@ int check_args(const dsa_v32_attn_args* a, int want_dtype, WorkspaceHeader* hdr)
     if (!aligned16(a->q) || !aligned16(a->kv) || !aligned16(a->out)) return DSA_V32_ERR_ALIGN;
     if ((a->stride_q_head % 8) || (a->stride_q_row % 8) || (a->stride_o_head % 8) || (a->stride_o_row % 8)) return DSA_V32_ERR_ALIGN;
     if (reinterpret_cast<uintptr_t>(a->workspace) & 255u) return DSA_V32_ERR_ALIGN;
-    if (!registry().get(a->workspace, hdr)) return DSA_V32_ERR_WORKSPACE;
+    if (known) *hdr = *known;
+    else if (!registry().get(a->workspace, hdr)) return DSA_V32_ERR_WORKSPACE;
     if (hdr->total_q != a->total_q || hdr->H != a->H || hdr->topk != a->topk || hdr->s_q != a->s_q) return DSA_V32_ERR_WORKSPACE;
     if (hdr->total_bytes > a->workspace_bytes) return DSA_V32_ERR_WORKSPACE;
     return DSA_V32_OK;
@@ -137,29 +157,76 @@ void fill_params(const dsa_v32_attn_args* a, const WorkspaceHeader& h, AttnParam
     p->scale_log2 = a->sm_scale * 1.4426950408889634f;
 }
 
-int launch_attention(const dsa_v32_attn_args* a, int want_dtype, cudaStream_t stream) {
+// Encoded tensor maps depend only on (base pointer, extents, strides): a serving loop passes the same
+// buffers every step, so the last few are kept instead of calling the driver's encoder on every launch.
+struct TmapCache {
+    struct Key {
+        const void* base;
+        uint64_t d0, d1, d2, s0, s1;
+        uint32_t b0, b1, b2;
+        int dtype, rank, swizzle;
+        bool operator==(const Key& o) const {
+            return base == o.base && d0 == o.d0 && d1 == o.d1 && d2 == o.d2 && s0 == o.s0 && s1 == o.s1 && b0 == o.b0 &&
+                   b1 == o.b1 && b2 == o.b2 && dtype == o.dtype && rank == o.rank && swizzle == o.swizzle;
+        }
+    };
+    struct Entry {
+        Key key;
+        CUtensorMap map;
+        uint64_t last_use;
+    };
+    std::mutex mu;
+    std::vector<Entry> entries;
+    uint64_t clock = 0;
+    int get(CUtensorMap* out, CUtensorMapDataType dtype, int rank, const void* base, const uint64_t* dims, const uint64_t* str,
+            const uint32_t* box, CUtensorMapSwizzle swizzle) {
+        Key k{base, dims[0], rank > 1 ? dims[1] : 0, rank > 2 ? dims[2] : 0, rank > 1 ? str[0] : 0, rank > 2 ? str[1] : 0,
+              box[0], rank > 1 ? box[1] : 0, rank > 2 ? box[2] : 0, (int)dtype, rank, (int)swizzle};
+        std::lock_guard<std::mutex> g(mu);
+        for (auto& e : entries)
+            if (e.key == k) {
+                e.last_use = ++clock;
+                *out = e.map;
+                return 0;
+            }
+        CUtensorMap m;
+        if (make_tmap(&m, dtype, rank, base, dims, str, box, swizzle)) return -1;
+        if (entries.size() >= 32) {
+            size_t victim = 0;
+            for (size_t i = 1; i < entries.size(); ++i)
+                if (entries[i].last_use < entries[victim].last_use) victim = i;
+            entries.erase(entries.begin() + victim);
+        }
+        entries.push_back(Entry{k, m, ++clock});
+        *out = m;
+        return 0;
+    }
+};
+TmapCache& tmap_cache() {
+    static TmapCache c;
+    return c;
+}
+
+int launch_attention(const dsa_v32_attn_args* a, int want_dtype, cudaStream_t stream, const WorkspaceHeader* known = nullptr) {
     WorkspaceHeader h;
-    int rc = check_args(a, want_dtype, &h);
+    int rc = check_args(a, want_dtype, &h, known);
     if (rc) return rc;
     AttnParams p;
     fill_params(a, h, &p);
+    // bf16 cache: the kernel reads Q and the cache rows with plain loads and takes no tensor map
     CUtensorMap tq, tkv, ttail;
-    {
-        const uint64_t dims[3] = {uint64_t(kDQK), uint64_t(a->H), uint64_t(a->total_q)};
-        const uint64_t str[2] = {uint64_t(a->stride_q_head) * 2, uint64_t(a->stride_q_row) * 2};
-        const uint32_t box[3] = {64, uint32_t(kHeadsPerBlock), 1};
-        if (make_tmap(&tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a->q, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
-            return DSA_V32_ERR_DRIVER;
-    }
+    std::memset(&tq, 0, sizeof(tq));
+    std::memset(&tkv, 0, sizeof(tkv));
+    std::memset(&ttail, 0, sizeof(ttail));
     const bool fp8 = want_dtype == DSA_V32_KV_FP8;
-    if (!fp8) {
-        const uint64_t dims[2] = {uint64_t(kDQK), uint64_t(a->num_kv_rows)};
-        const uint64_t str[1] = {uint64_t(DSA_V32_BF16_ROW_BYTES)};
-        const uint32_t box[2] = {64, 1};
-        if (make_tmap(&tkv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a->kv, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
-            return DSA_V32_ERR_DRIVER;
-        ttail = tkv;
-    } else {
+    if (fp8) {
+        {   // Q: the 64 rope columns of a head block, 128-byte swizzle (the latent columns go to TMEM by plain loads)
+            const uint64_t dims[3] = {uint64_t(kDQK), uint64_t(a->H), uint64_t(a->total_q)};
+            const uint64_t str[2] = {uint64_t(a->stride_q_head) * 2, uint64_t(a->stride_q_row) * 2};
+            const uint32_t box[3] = {64, uint32_t(kHeadsPerBlock), 1};
+            if (tmap_cache().get(&tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a->q, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+                return DSA_V32_ERR_DRIVER;
+        }
         // the 656-byte rows seen as 164 32-bit elements (a box may then be wider than 256 bytes):
         // CTA 0 gathers elements [0, 64) = its 256 latent bytes, CTA 1 elements [64, 164) = its 256 latent
         // bytes + the 16 scale bytes + the 128 rope bytes
@@ -167,12 +234,27 @@ int launch_attention(const dsa_v32_attn_args* a, int want_dtype, cudaStream_t st
         const uint64_t str[1] = {uint64_t(kFp8RowBytes)};
         const uint32_t box_a[2] = {64, 1};
         const uint32_t box_b[2] = {100, 1};
-        if (make_tmap(&tkv, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, a->kv, dims, str, box_a, CU_TENSOR_MAP_SWIZZLE_NONE))
+        if (tmap_cache().get(&tkv, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, a->kv, dims, str, box_a, CU_TENSOR_MAP_SWIZZLE_NONE))
             return DSA_V32_ERR_DRIVER;
-        if (make_tmap(&ttail, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, a->kv, dims, str, box_b, CU_TENSOR_MAP_SWIZZLE_NONE))
+        if (tmap_cache().get(&ttail, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, a->kv, dims, str, box_b, CU_TENSOR_MAP_SWIZZLE_NONE))
             return DSA_V32_ERR_DRIVER;
     }
     cudaError_t e = launch_attn(fp8, h.num_lists, tq, tkv, ttail, p, stream);
+    return e == cudaSuccess ? DSA_V32_OK : (int)e;
+}
+
+int launch_merge(const dsa_v32_attn_args* a, cudaStream_t stream, const WorkspaceHeader* known = nullptr) {
+    WorkspaceHeader h;
+    if (!a) return DSA_V32_ERR_NULL;
+    int rc = check_args(a, a->kv_dtype, &h, known);
+    if (rc) return rc;
+    uint8_t* ws = reinterpret_cast<uint8_t*>(a->workspace);
+    cudaError_t e = launch_combine(reinterpret_cast<const float*>(ws + h.off_o_accum),
+                                   reinterpret_cast<const float*>(ws + h.off_lse_accum),
+                                   reinterpret_cast<const int32_t*>(ws + h.off_reduce_indptr),
+                                   reinterpret_cast<const int32_t*>(ws + h.off_reduce_slots),
+                                   reinterpret_cast<const ReduceDst*>(ws + h.off_reduce_dst), h.num_reduce_rows, a->out, a->lse,
+                                   a->stride_o_row, a->stride_o_head, a->H, stream);
     return e == cudaSuccess ? DSA_V32_OK : (int)e;
 }
 
@@ -284,19 +366,11 @@ int dsa_v32_prefill_bf16(const dsa_v32_attn_args* args, void* stream) {
     return launch_attention(args, DSA_V32_KV_BF16, (cudaStream_t)stream);
 }
 
-int dsa_v32_combine(const dsa_v32_attn_args* a, void* stream) {
-    WorkspaceHeader h;
-    if (!a) return DSA_V32_ERR_NULL;
-    int rc = check_args(a, a->kv_dtype, &h);
-    if (rc) return rc;
-    uint8_t* ws = reinterpret_cast<uint8_t*>(a->workspace);
-    cudaError_t e = launch_combine(reinterpret_cast<const float*>(ws + h.off_o_accum),
-                                   reinterpret_cast<const float*>(ws + h.off_lse_accum),
-                                   reinterpret_cast<const int32_t*>(ws + h.off_reduce_indptr),
-                                   reinterpret_cast<const int32_t*>(ws + h.off_reduce_slots),
-                                   reinterpret_cast<const ReduceDst*>(ws + h.off_reduce_dst), h.num_reduce_rows, a->out, a->lse,
-                                   a->stride_o_row, a->stride_o_head, a->H, (cudaStream_t)stream);
-    return e == cudaSuccess ? DSA_V32_OK : (int)e;
+int dsa_v32_combine(const dsa_v32_attn_args* a, void* stream) { return launch_merge(a, (cudaStream_t)stream); }
+
+int dsa_v32_plan_release(const void* workspace) {
+    if (!workspace) return DSA_V32_ERR_NULL;
+    return registry().drop(workspace) ? DSA_V32_OK : DSA_V32_ERR_WORKSPACE;
 }
 
 int dsa_v32_decode_pipeline(const dsa_v32_attn_args* a, int run_plan, void* stream) {
@@ -353,6 +427,7 @@ namespace {
 struct StaticScratchState {
     void* dev_ptr = nullptr;   // device address of g_static_scratch on this device
     dsa_v32_shape planned{};   // shape the array is currently planned for
+    WorkspaceHeader hdr{};     // header of that plan (kept here: the static path does not depend on the plan registry)
     bool has_plan = false;
 };
 std::mutex g_static_mu;
@@ -385,13 +460,20 @@ int dsa_v32_decode_pipeline_static(const dsa_v32_attn_args* a, void* stream) {
         sh.H = a->H;
         sh.topk = a->topk;
         sh.s_q = a->s_q;
-        dsa_v32_plan_info info;
-        int rc = dsa_v32_plan_info_get(&sh, &info);
+        int sms = 0;
+        int rc = resolve_sms(&sh, &sms);
         if (rc) return rc;
-        if (info.workspace_bytes > (int64_t)DSA_V32_STATIC_SCRATCH_BYTES) return DSA_V32_ERR_SCRATCH_TOO_SMALL;
+        HostPlan P;
+        rc = build_plan(sh, sms, P);
+        if (rc) return rc;
+        if (P.hdr.total_bytes > (int64_t)DSA_V32_STATIC_SCRATCH_BYTES) return DSA_V32_ERR_SCRATCH_TOO_SMALL;
         S.has_plan = false;
-        rc = dsa_v32_plan(&sh, S.dev_ptr, DSA_V32_STATIC_SCRATCH_BYTES, stream);
-        if (rc) return rc;
+        std::vector<uint8_t> blob((size_t)plan_meta_bytes(P));
+        serialize_plan(P, blob.data());
+        // pageable source: the runtime stages the bytes before returning, so `blob` may go away
+        e = cudaMemcpyAsync(S.dev_ptr, blob.data(), blob.size(), cudaMemcpyHostToDevice, st);
+        if (e != cudaSuccess) return (int)e;
+        S.hdr = P.hdr;
         S.planned = sh;
         S.has_plan = true;
     }
@@ -401,9 +483,9 @@ int dsa_v32_decode_pipeline_static(const dsa_v32_attn_args* a, void* stream) {
     dsa_v32_attn_args b = *a;
     b.workspace = S.dev_ptr;
     b.workspace_bytes = DSA_V32_STATIC_SCRATCH_BYTES;
-    int rc = launch_attention(&b, b.kv_dtype, st);
+    int rc = launch_attention(&b, b.kv_dtype, st, &S.hdr);
     if (rc) return rc;
-    return dsa_v32_combine(&b, stream);
+    return launch_merge(&b, st, &S.hdr);
 }
 
 // Device address of the static scratch on the current device (after the first static call); lets a

@@ -50,6 +50,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cfloat>
+#include <mutex>
 #include "defs.h"
 #include "ptx.cuh"
 
@@ -58,6 +59,12 @@
 #endif
 #ifndef DSA_BF16_KV_STAGES
 #define DSA_BF16_KV_STAGES 6
+#endif
+#ifndef DSA_ROWSPLIT_FP8
+#define DSA_ROWSPLIT_FP8 0
+#endif
+#ifndef DSA_ROWSPLIT_BF16
+#define DSA_ROWSPLIT_BF16 1
 #endif
 #ifndef DSA_FP8_RAW_STAGES
 #define DSA_FP8_RAW_STAGES 4
@@ -100,15 +107,14 @@ constexpr int kKvBlockBytes = kTileRows * 128;            // 4096: one 64-column
 constexpr int kKvTileBytes = kMaxKBlocks * kKvBlockBytes; // 20480
 constexpr int kRawGroupBytes = 1024 + 640;                // 4 rows: 4 x 256 latent bytes | 4 x 144 tail (+pad)
 constexpr int kRawTileBytes = (kTileRows / 4) * kRawGroupBytes;   // 13312
-constexpr int kXRowBytes = kTileRows * 2 + 4;                     // a row's partial scores as 16-bit fixed point + its step (fp32)
-constexpr int kXInvOff = kHeadsPerBlock * kTileRows * 2;          // the steps follow the 4 chunks x 128 rows x 16 bytes
-constexpr int kXbufBytes = kHeadsPerBlock * kXRowBytes;           // 8704: one tile of partial scores
+constexpr int kXWarpBytes = 32 * (kTileRows * 2 + 4);             // 2176: per softmax warp, a tile row's 32 values as 16-bit words (partial
+                                                                  // scores in fixed point, or P in bf16) + one fp32 word per row
+constexpr int kXbufBytes = 4 * kXWarpBytes;                       // 8704: the four warps of a team
 constexpr float kQuantBias = 8421376.0f;                          // 2^23 + 2^15: adding it leaves round(x) + 32768 in the low mantissa bits
 constexpr int kMaskSlots = 16;
 constexpr int kGroups = 4;                                // softmax warpgroups sharing a tile's columns
 constexpr int kSoftmaxWarps = 4 * kGroups;
 constexpr int kMmaWarp = kSoftmaxWarps;                   // issues the score MMAs (and owns the TMEM allocation)
-constexpr int kPvWarp = kSoftmaxWarps + 1;                // issues the P V MMAs
 constexpr int kGatherWarp0 = kSoftmaxWarps + 2;           // fp8 cache: two gather issuers (idle for a bf16 cache) ...
 constexpr int kGatherWarps = 2;
 constexpr int kConvertWarp0 = kGatherWarp0 + kGatherWarps; // ... and eight converters (two warpgroups)
@@ -135,6 +141,9 @@ struct Cfg {
     // than one phase ahead of its barrier (with an odd ring the users alternate and a parity wait could
     // pass on the phase before last).
     static_assert(!kFp8 || kRawStages % 2 == 0, "even raw ring");
+    static_assert(kKvStages <= 8 && kRawStages <= 16, "kv_full/kv_empty hold 8 barriers, raw_full/raw_empty 16");
+    static_assert(kKvStages + kRawStages <= kScaleSlots && kKvStages + kRawStages <= kMaskSlots,
+                  "a tile's mask and scales stay in their slot from the gather to the softmax");
     static constexpr int kThreads = 32 * kWarps;
     static constexpr int kOffKv = kQSmemBytes;
     static constexpr int kOffRaw = kOffKv + kKvStages * kKvTileBytes;
@@ -145,7 +154,7 @@ struct Cfg {
 };
 
 struct Ctl {
-    float l_part[kGroups][kHeadsPerBlock];      // per-group row sums at the end of an item
+    float l_part[2][kGroups][kHeadsPerBlock];   // per-team row sums at the end of an item, by item parity
     float row_scale[kScaleSlots][2][kTileRows];  // fp8 cache: per tile buffer, the scales of this CTA's two groups for every tile row
     uint64_t q_full, q_empty, o_free;
     uint64_t kv_full[8], kv_empty[8];
@@ -153,6 +162,8 @@ struct Ctl {
     uint64_t raw_empty[16];  // ... and the four converter warps that read them are done
     uint64_t s_full[kGroups], s_empty[kGroups], p_full[kGroups], pv_done[kGroups];
     uint64_t l_bar;
+    uint64_t e_bar;    // every softmax warp has committed its last tile of the item (its P stores and reference-maximum steps)
+    uint64_t o_full;   // the item's last P V product has completed: O is final
     uint64_t m_bar[kGroups][4];        // [team][lane quadrant]: the tile's reference-maximum step is done
     // Exchange of partial scores with the peer CTA: one buffer per team, barriers per softmax warp.
     uint64_t x_full[kSoftmaxWarps];    // the peer's partial scores for this warp's rows have arrived (bytes)
@@ -308,6 +319,15 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #endif
     const int half = (int)cluster_ctarank();      // 0: columns [0,256); 1: columns [256,576)
     const int peer = half ^ 1;
+    // The two MMA issuers sit on the schedulers (warp number mod 4) whose softmax warps only export and import
+    // rows in this CTA - the light ones: quadrants 2, 3 in CTA 0 and 0, 1 in CTA 1; the gather issuers take the
+    // other two of warps 16-19.  (TMEM is allocated and released by warp 16 in both.)
+#ifndef DSA_ROLE_SWAP
+#define DSA_ROLE_SWAP 0
+#endif
+    const int mma_warp = (half || !DSA_ROLE_SWAP) ? kMmaWarp : kMmaWarp + 2;
+    const int pv_warp = mma_warp + 1;
+    const int gather_warp0 = (half || !DSA_ROLE_SWAP) ? kGatherWarp0 : kMmaWarp;
     const int nkb = half ? 5 : 4;                 // 64-column blocks of this CTA's slice
     const int col0 = half ? 256 : 0;              // first latent column of the slice
     const int w_begin = __ldg(p.list_indptr + list);
@@ -342,6 +362,8 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         mbar_init(smem_u32(&ctl->q_empty), 1);
         mbar_init(smem_u32(&ctl->o_free), kSoftmaxWarps);
         mbar_init(smem_u32(&ctl->l_bar), kSoftmaxWarps);
+        mbar_init(smem_u32(&ctl->e_bar), kSoftmaxWarps);
+        mbar_init(smem_u32(&ctl->o_full), 1);
         ctl->abort_flag = 0;
         fence_mbar_init();
     }
@@ -367,58 +389,72 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         // per warpgroup; each class of warpgroups executes one instruction at the top of its branch)
         setmaxnreg_inc<kRegsSoftmax>();
         // ============================================================ softmax + epilogue
-        // Four teams of four warps (one warp per TMEM lane quadrant) take the tiles round robin (team =
-        // tile number mod 4 = exchange buffer and barrier index), so four tiles are in flight through the
-        // long part of a step (TMEM load, exchange, mask, max, exp).  Thread = head row: it holds its row's
-        // 32 scores of the tile, so the row maximum and sum need no other thread.  Only the short commit
-        // of a tile is ordered after the commit of the tile before: there the shared reference maximum of
-        // the row is read, P (computed against the tile's own row maximum) is brought to it, O is
-        // rescaled in the rare case the reference moves (lazy threshold 8), P is stored and the tile is
-        // released to the MMA warp.
-        constexpr int G = kGroups, CPT = kTileRows, NP = CPT / 2, NCH = CPT / 4, OCOLS = kDvHalf / G;
+        // Four teams of four warps (one warp per TMEM lane quadrant) take the 32-slot tiles round robin (team =
+        // tile number mod 4), so four tiles are in flight.  Thread = head row: it holds its row's 32 scores of
+        // the tile, so the row maximum and sum need no other thread.  The two CTAs split the softmax by head
+        // rows: CTA c computes it for rows [64 c, 64 c + 64) ("own" rows, two of a team's four warps).  For the
+        // other 64 rows a warp only exports this CTA's partial scores to the peer and later imports the
+        // finished P of those rows from it.  Per tile and direction 4.3 KB of partial scores and 4.3 KB of P
+        // cross the SM-to-SM link (it carries ~11-17 bytes per clock): the partials as 16-bit fixed point with
+        // one power-of-two-ish step per row and tile (step = 2^-15 of the row's largest partial: <= 1.5e-4 in
+        // the exponent for scores up to 128), P as the bf16 the MMA consumes anyway.
+        // Only the short commit of a tile is ordered after the commit of the tile before: there the shared
+        // reference maximum of the row is read and moved when the tile's maximum exceeds it by more than the
+        // lazy margin of 8 (the reference's threshold); O is rescaled in that rare case, in both CTAs (the
+        // factor travels with P).
+        constexpr int G = kGroups, CPT = kTileRows, NP = CPT / 2, OCOLS = kDvHalf / G;
         static_assert(kGroups == 4 && kTileRows == 32, "four teams, one thread per row and tile");
         const int cg = warp >> 2;            // warpgroup
         const int team = cg;                 // tiles this warp works on: it % 4 == team
         const int quad = warp & 3;           // TMEM lane quadrant this warp may touch
         const int row = quad * 32 + lane;    // head row inside the block == TMEM lane
+        // kRowSplit: the pair splits the softmax by head rows as described above.  Otherwise (fp8 cache, where
+        // the single score buffer in TMEM and the four tile stages make the latency of a tile's chain the
+        // bound, not the work in it) both CTAs run the softmax of all 128 rows on the same numbers: every warp
+        // sends its partial scores and adds the peer's - both sides add the two *quantised* partials, so they
+        // hold the same scores bit for bit - and no P crosses the link.
+        constexpr bool kRowSplit = kFp8 ? (DSA_ROWSPLIT_FP8 != 0) : (DSA_ROWSPLIT_BF16 != 0);
+        const bool own = !kRowSplit || (quad >> 1) == half;   // this CTA computes the softmax of the warp's rows
         const uint32_t lane_base = tmem + (static_cast<uint32_t>(quad * 32) << 16);
-        // exchange buffer of a tile: [8 chunks of 4 columns][128 rows][16 bytes]
-        const uint32_t peer_sx = map_to_cta(smem_u32(sX), peer);
-        // the peer thread with the same (warp, lane) reads what this thread sends: one byte-counting
-        // barrier per warp for arrival, one per warp for the credit "the peer has read the last one"
+        // Incoming buffer of this warp, written by the peer CTA's warp of the same number (it handles the same
+        // rows): [4 chunks of 16 bytes][32 lanes] + one word per lane.  An own-row warp receives partial scores
+        // there and sends P; the other warps send partial scores and receive P.
+        const uint32_t xin = smem_u32(sX) + static_cast<uint32_t>(warp) * kXWarpBytes;
+        const uint8_t* xin_p = sX + warp * kXWarpBytes;
+        const uint32_t xout = map_to_cta(xin, peer);
+        // one byte-counting barrier per warp for arrival, one per warp for the credit "the peer has read the last one"
         const uint32_t my_xfull = smem_u32(&ctl->x_full[warp]);
         const uint32_t my_xfree = smem_u32(&ctl->x_free[warp]);
         const uint32_t peer_xfull = map_to_cta(my_xfull, peer);
         const uint32_t peer_xfree = map_to_cta(my_xfree, peer);
         const uint32_t peer_xsink = map_to_cta(smem_u32(&ctl->x_sink[warp]), peer);
         uint32_t it_base = 0;   // global tile counter at the start of the item
+        uint32_t n_sent = 0;    // tiles this warp has sent to the peer
         int item_n = 0;
 
-        // bf16 cache: this thread's share of an item's Q slice (its head row, a quarter of the slice's
-        // columns), read from global memory one item ahead and stored into TMEM when the item starts.
+        // this thread's share of an item's Q slice (its head row, a quarter of the slice's columns), read from
+        // global memory one item ahead and stored into TMEM when the item starts.
         constexpr int kQRegs = kFp8 ? 32 : 40;
         uint32_t qreg[kQRegs];
         const int q_ncol = (!kFp8 && half) ? 40 : 32;   // TMEM columns (bf16 pairs) per warp; fp8: latent columns only
         auto q_fetch = [&](const dsa_v32_work_info& wq) {
-            if (C::kQInTmem) {
-                const int head = wq.head_block * kHeadsPerBlock + row;
-                const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.q) + (size_t)wq.q_row * p.stride_q_row +
-                                           (size_t)head * p.stride_q_head + col0 + 2 * cg * q_ncol;
-                const bool live = head < p.H;
+            const int head = wq.head_block * kHeadsPerBlock + row;
+            const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.q) + (size_t)wq.q_row * p.stride_q_row +
+                                       (size_t)head * p.stride_q_head + col0 + 2 * cg * q_ncol;
+            const bool live = head < p.H;
 #pragma unroll
-                for (int j = 0; j < kQRegs / 4; ++j) {
-                    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                    if (live && 4 * j < q_ncol) v = __ldg(reinterpret_cast<const uint4*>(src) + j);
-                    qreg[4 * j + 0] = v.x;
-                    qreg[4 * j + 1] = v.y;
-                    qreg[4 * j + 2] = v.z;
-                    qreg[4 * j + 3] = v.w;
-                }
+            for (int j = 0; j < kQRegs / 4; ++j) {
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (live && 4 * j < q_ncol) v = __ldg(reinterpret_cast<const uint4*>(src) + j);
+                qreg[4 * j + 0] = v.x;
+                qreg[4 * j + 1] = v.y;
+                qreg[4 * j + 2] = v.z;
+                qreg[4 * j + 3] = v.w;
             }
         };
         auto q_prefetch_l2 = [&](const dsa_v32_work_info& wq) {
             const int head = wq.head_block * kHeadsPerBlock + row;
-            if (C::kQInTmem && head < p.H) {
+            if (head < p.H) {
                 const char* src = reinterpret_cast<const char*>(reinterpret_cast<const __nv_bfloat16*>(p.q) + (size_t)wq.q_row * p.stride_q_row +
                                                                (size_t)head * p.stride_q_head + col0 + 2 * cg * q_ncol);
                 asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
@@ -462,232 +498,304 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const uint32_t tb = buf_of<kFp8>(it);         // barrier index (= team) and phase of this tile
                 const uint32_t tph = phase_of<kFp8>(it);
                 const bool first = (it == it_base);
+                const uint32_t xph = (it / G) & 1u;           // the warp's own exchange barriers advance once per tile of its team
                 // The tile's values live in pairs (64-bit registers) so that the fp32 arithmetic on them uses the
                 // two-wide forms (fma/mul/add .f32x2): half the instructions of the scalar forms.
                 uint64_t tv2[NP];
-                // ---- own partial scores out of TMEM
-                // exchange buffer of the team; the warp's own barriers advance once per tile of its team
-                const uint32_t x_off = static_cast<uint32_t>(team) * kXbufBytes + static_cast<uint32_t>(row) * 16u;
-                const uint32_t xph = (it / G) & 1u;
-                if (lane == 0) mbar_arrive_expect_tx(my_xfull, 32 * kXRowBytes);
+                if (lane == 0) mbar_arrive_expect_tx(my_xfull, kXWarpBytes);
+                // ---- this CTA's partial scores of the warp's 32 rows, out of TMEM
                 if (kFp8)
                     if (!warp_wait(smem_u32(&ctl->kv_full[it % S]), (it / S) & 1, abort_flag)) goto done;
                 if (!warp_wait(smem_u32(&ctl->s_full[tb]), tph, abort_flag)) goto done;
                 tc_fence_after();
-                if (warp == 0 || warp == 4) PROF(2, it, 0);
+                if (warp == 0 || warp == 2) { if (own) PROF(2, it, 0); else PROF(3, it, 0); }
                 {
                     const uint32_t s0 = lane_base + s_col_of<kFp8>(it);
                     if (kFp8) {
-                        // 16 columns at a time: the accumulators of scale group a and scale group b, then (in the
-                        // CTA that has them) the rope columns.  The score buffer is single, so it is handed back
-                        // to the MMA warp the moment the last load has returned.
+                        // 16 columns at a time: the accumulators of scale group a, scale group b and (in the CTA
+                        // that has them) the rope columns, all loads of a round in flight together.  The score
+                        // buffer is single, so it is handed back to the MMA warp the moment the last load has returned.
 #pragma unroll
                         for (int hc = 0; hc < 2; ++hc) {
-                            uint32_t sr[16], sr2[16];
+                            uint32_t sr[16], sr2[16], sr3[16];
                             tmem_ld_n<16>(s0 + 16 * hc, sr);
                             tmem_ld_n<16>(s0 + 32 + 16 * hc, sr2);
+                            if (half) tmem_ld_n<16>(s0 + 64 + 16 * hc, sr3);
                             const float4* sa = reinterpret_cast<const float4*>(ctl->row_scale[it % kScaleSlots][0] + 16 * hc);
                             const float4* sb4 = reinterpret_cast<const float4*>(ctl->row_scale[it % kScaleSlots][1] + 16 * hc);
                             tmem_wait_ld();
+                            if (hc == 1) {
+                                tc_fence_before();
+                                __syncwarp();
+                                if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[tb]));
+                            }
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
                                 const float4 wa = sa[j], wb = sb4[j];
-                                tv2[8 * hc + 2 * j] = fma2(pack2(wb.x, wb.y), pack2u(sr2[4 * j], sr2[4 * j + 1]),
-                                                           mul2(pack2(wa.x, wa.y), pack2u(sr[4 * j], sr[4 * j + 1])));
-                                tv2[8 * hc + 2 * j + 1] = fma2(pack2(wb.z, wb.w), pack2u(sr2[4 * j + 2], sr2[4 * j + 3]),
-                                                               mul2(pack2(wa.z, wa.w), pack2u(sr[4 * j + 2], sr[4 * j + 3])));
+                                uint64_t r0 = mul2(pack2(wa.x, wa.y), pack2u(sr[4 * j], sr[4 * j + 1]));
+                                uint64_t r1 = mul2(pack2(wa.z, wa.w), pack2u(sr[4 * j + 2], sr[4 * j + 3]));
+                                if (half) {
+                                    r0 = add2(r0, pack2u(sr3[4 * j], sr3[4 * j + 1]));
+                                    r1 = add2(r1, pack2u(sr3[4 * j + 2], sr3[4 * j + 3]));
+                                }
+                                tv2[8 * hc + 2 * j] = fma2(pack2(wb.x, wb.y), pack2u(sr2[4 * j], sr2[4 * j + 1]), r0);
+                                tv2[8 * hc + 2 * j + 1] = fma2(pack2(wb.z, wb.w), pack2u(sr2[4 * j + 2], sr2[4 * j + 3]), r1);
                             }
-                        }
-                        if (half) {
-                            uint32_t sr3[32];
-                            tmem_ld_n<32>(s0 + 64, sr3);
-                            tmem_wait_ld();
-                            tc_fence_before();
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[tb]));
-#pragma unroll
-                            for (int j = 0; j < NP; ++j) tv2[j] = add2(tv2[j], pack2u(sr3[2 * j], sr3[2 * j + 1]));
-                        } else {
-                            tc_fence_before();
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[tb]));
                         }
                     } else {
                         uint32_t sr[CPT];
                         tmem_ld_n<CPT>(s0, sr);
                         tmem_wait_ld();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[tb]));   // the MMA warp may overwrite the scores
 #pragma unroll
                         for (int j = 0; j < NP; ++j) tv2[j] = pack2u(sr[2 * j], sr[2 * j + 1]);
                     }
-                    if (warp == 0 || warp == 4) PROF(4, it, 0);
+                    if ((warp == 0 || warp == 2) && own) PROF(4, it, 0);
                 }
-                if (!kFp8) {
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&ctl->s_empty[tb]));   // the MMA warp may overwrite the scores
-                }
-                // ---- exchange: the two CTAs' partial scores are summed through distributed shared memory.  The
-                // link between the two SMs carries only ~11-17 bytes per clock and direction, so the partials
-                // cross it as 16-bit fixed point with one power-of-two step per row and tile (step = 2^-15 of
-                // the row's largest partial: <= 3e-4 in the exponent for scores up to 128, against P rounded
-                // to bf16 afterwards), 68 bytes per row instead of 128.  Both CTAs add the two *quantised*
-                // partials, so they hold the same scores bit for bit.
-                uint32_t own_inv_bits;
-                {
-                    float amax = 0.0f;
-#pragma unroll
-                    for (int j = 0; j < NP; ++j) {
-                        float v0, v1;
-                        unpack2(tv2[j], v0, v1);
-                        amax = fmaxf(amax, fmaxf(fabsf(v0), fabsf(v1)));
-                    }
-                    // e = biased exponent of the largest partial (NaN/Inf -> the step becomes NaN and so do the scores)
-                    uint32_t e = __float_as_uint(amax) >> 23;
-                    e = e < 20u ? 20u : e;
-                    const float q_scale = __uint_as_float((268u - e) << 23) * 0.99996948f;   // largest partial -> < 32767.5
-                    own_inv_bits = e >= 255u ? 0x7FC00000u : __float_as_uint(__uint_as_float((e - 14u) << 23) * 1.0000305f);
-                    const uint64_t qs2 = pack2(q_scale, q_scale), qc2 = pack2(kQuantBias, kQuantBias);
-#pragma unroll
-                    for (int j = 0; j < NP; ++j) tv2[j] = fma2(tv2[j], qs2, qc2);   // 2^23 + 32768 + n: n in the low 16 bits
-                }
-                if (it >= G)   // the peer has read what this warp sent last (its credit has arrived)
-                    if (!warp_wait_cluster(my_xfree, xph ^ 1u, abort_flag)) goto done;
-                if (lane == 0) mbar_arrive_expect_tx(my_xfree, 4);   // the credit for this send
-                if (warp == 0 || warp == 4) PROF(7, it, 1);
-#pragma unroll
-                for (int c = 0; c < NCH / 2; ++c) {
-                    uint32_t w[4];
-#pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        w[k] = __byte_perm(static_cast<uint32_t>(tv2[4 * c + k]), static_cast<uint32_t>(tv2[4 * c + k] >> 32), 0x5410u);
-                    st_async_b32x4(peer_sx + x_off + c * (kHeadsPerBlock * 16), w[0], w[1], w[2], w[3], peer_xfull);
-                }
-                st_async_u32(peer_sx + static_cast<uint32_t>(team) * kXbufBytes + kXInvOff + static_cast<uint32_t>(row) * 4u, own_inv_bits,
-                             peer_xfull);
-                if (warp == 0 || warp == 4) PROF(2, it, 1);
-                {
-                    // own partials back from their quantised form while the peer's are on their way
-                    const float own_inv = __uint_as_float(own_inv_bits);
-                    const uint64_t oi2 = pack2(own_inv, own_inv), nb2 = pack2(-kQuantBias, -kQuantBias);
-#pragma unroll
-                    for (int j = 0; j < NP; ++j) tv2[j] = mul2(add2(tv2[j], nb2), oi2);
-                }
-                if (!warp_wait_cluster(my_xfull, xph, abort_flag)) goto done;
-                if (warp == 0 || warp == 4) PROF(2, it, 2);
-                {
-                    // credit: the peer may overwrite the buffer.  The credit word is computed from every lane's
-                    // loaded values, so it cannot leave before all of the warp's reads have returned.
-                    const uint4* src = reinterpret_cast<const uint4*>(sX + x_off);
-                    const float peer_inv = *reinterpret_cast<const float*>(sX + team * kXbufBytes + kXInvOff + row * 4);
-                    const uint64_t pi2 = pack2(peer_inv, peer_inv), nb2 = pack2(-kQuantBias, -kQuantBias);
-                    uint32_t dep = __float_as_uint(peer_inv);
-#pragma unroll
-                    for (int c = 0; c < NCH / 2; ++c) {
-                        const uint4 o = src[c * kHeadsPerBlock];
-                        const uint32_t w[4] = {o.x, o.y, o.z, o.w};
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            const uint64_t b2 = pack2u(__byte_perm(w[k], 0x4B00u, 0x5410u), __byte_perm(w[k], 0x4B00u, 0x5432u));
-                            tv2[4 * c + k] = fma2(add2(b2, nb2), pi2, tv2[4 * c + k]);
-                        }
-                        dep |= o.x;
-                    }
-                    dep = __reduce_or_sync(0xffffffffu, dep);
-                    if (lane == 0) st_async_u32(peer_xsink, dep, peer_xfree);
-                }
-                if (!kFp8)
-                    if (!warp_wait(smem_u32(&ctl->kv_full[it % S]), (it / S) & 1, abort_flag)) goto done;
-                // ---- mask (padding slots; the mask is the same for every row, so a full tile skips this)
-                const uint32_t mask = ctl->tile_mask[it % kMaskSlots];
-                if (mask != 0xFFFFFFFFu) {
-#pragma unroll
-                    for (int j = 0; j < NP; ++j) {
-                        float v0, v1;
-                        unpack2(tv2[j], v0, v1);
-                        if (!((mask >> (2 * j)) & 1u)) v0 = -INFINITY;
-                        if (!((mask >> (2 * j + 1)) & 1u)) v1 = -INFINITY;
-                        tv2[j] = pack2(v0, v1);
-                    }
-                }
-                // ---- row maximum over the tile's 32 columns, in the log2 domain; the scale is positive, so
-                // the maximum is taken on the raw scores and scaled once
-                float mt;
-                {
-                    float t[NP];
-#pragma unroll
-                    for (int j = 0; j < NP; ++j) {
-                        float v0, v1;
-                        unpack2(tv2[j], v0, v1);
-                        t[j] = fmaxf(v0, v1);
-                    }
-                    const float u0 = max3(t[0], t[1], t[2]), u1 = max3(t[3], t[4], t[5]), u2 = max3(t[6], t[7], t[8]);
-                    const float u3 = max3(t[9], t[10], t[11]), u4 = max3(t[12], t[13], t[14]);
-                    mt = fmaxf(max3(u0, u1, t[15]), max3(u2, u3, u4)) * p.scale_log2;
-                }
-                if (warp == 0 || warp == 4) PROF(7, it, 2);
-                // ---- the row's reference maximum, moved in tile order.  This is the only step that waits
-                // for the tile before (per lane quadrant: the warp of the previous team with the same rows),
-                // and it is a handful of instructions: read the reference, move it if the tile's maximum
-                // exceeds it by more than the lazy margin of 8, publish.
-                if (!first)
-                    if (!warp_wait(smem_u32(&ctl->m_bar[buf_of<kFp8>(it - 1)][quad]), phase_of<kFp8>(it - 1), abort_flag)) goto done;
-                const float m_cur = first ? -INFINITY : ctl->m_shared[row];
-                const bool raise = mt > m_cur + 8.0f;
-                const float m_fin = raise ? mt : m_cur;
-                if (raise || first) ctl->m_shared[row] = m_fin;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&ctl->m_bar[tb][quad]));
-                if (warp == 0 || warp == 4) PROF(7, it, 3);
-                // ---- P = 2^(score - reference): at most 2^8; a masked slot gives 0
-                const float m_fin_use = (m_fin == -INFINITY) ? 0.0f : m_fin;
-                float lsum;
-                {
-                    const uint64_t c2 = pack2(p.scale_log2, p.scale_log2), nm2 = pack2(-m_fin_use, -m_fin_use);
-                    uint64_t ls2 = pack2(0.0f, 0.0f);
-#pragma unroll
-                    for (int j = 0; j < NP; ++j) {
-                        float v0, v1;
-                        unpack2(fma2(tv2[j], c2, nm2), v0, v1);
-                        tv2[j] = pack2(ex2_approx(v0), ex2_approx(v1));
-                        ls2 = add2(ls2, tv2[j]);
-                    }
-                    float l0, l1;
-                    unpack2(ls2, l0, l1);
-                    lsum = l0 + l1;
-                }
-                if (l_part != 0.0f && l_ref != m_fin) l_part *= ex2_approx(l_ref - m_fin);
-                l_part += lsum;
-                l_ref = m_fin;
-                // P as the MMA wants it: bf16 pairs; fp8 cache: two copies, each pre-multiplied by one scale
-                // group's row scales
                 constexpr int kPVariants = kFp8 ? 2 : 1;
-                uint32_t pk[kPVariants][NP];
-                if (kFp8) {
+                uint32_t pk[kPVariants][NP];   // P as the MMA wants it: bf16 pairs; fp8 cache: one copy per scale group
+                float f2 = 1.0f;               // factor that brings O so far to this tile's reference maximum
+                if (!own) {
+                    // ================================ rows whose softmax the peer computes
+                    // ---- export this CTA's partial scores as 16-bit fixed point
+                    {
+                        float amax = 0.0f;
 #pragma unroll
-                    for (int v = 0; v < 2; ++v) {
-                        const float4* sc = reinterpret_cast<const float4*>(ctl->row_scale[it % kScaleSlots][v]);
+                        for (int j = 0; j < NP; ++j) {
+                            float v0, v1;
+                            unpack2(tv2[j], v0, v1);
+                            amax = fmaxf(amax, fmaxf(fabsf(v0), fabsf(v1)));
+                        }
+                        // e = biased exponent of the largest partial (NaN/Inf -> the step becomes NaN and so do the scores)
+                        uint32_t e = __float_as_uint(amax) >> 23;
+                        e = e < 20u ? 20u : e;
+                        const float q_scale = __uint_as_float((268u - e) << 23) * 0.99996948f;   // largest partial -> < 32767.5
+                        const uint32_t inv_bits = e >= 255u ? 0x7FC00000u : __float_as_uint(__uint_as_float((e - 14u) << 23) * 1.0000305f);
+                        const uint64_t qs2 = pack2(q_scale, q_scale), qc2 = pack2(kQuantBias, kQuantBias);
 #pragma unroll
-                        for (int j = 0; j < CPT / 4; ++j) {
-                            const float4 w4 = sc[j];
-                            pk[v][2 * j] = pack_bf16x2_from2(mul2(tv2[2 * j], pack2(w4.x, w4.y)));
-                            pk[v][2 * j + 1] = pack_bf16x2_from2(mul2(tv2[2 * j + 1], pack2(w4.z, w4.w)));
+                        for (int j = 0; j < NP; ++j) tv2[j] = fma2(tv2[j], qs2, qc2);   // 2^23 + 32768 + n: n in the low 16 bits
+                        if (n_sent > 0)   // the peer has read what this warp sent last (its credit has arrived)
+                            if (!warp_wait_cluster(my_xfree, (n_sent & 1u) ^ 1u, abort_flag)) goto done;
+                        if (lane == 0) mbar_arrive_expect_tx(my_xfree, 4);   // the credit for this send
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            uint32_t wq[4];
+#pragma unroll
+                            for (int k = 0; k < 4; ++k)
+                                wq[k] = __byte_perm(static_cast<uint32_t>(tv2[4 * c + k]), static_cast<uint32_t>(tv2[4 * c + k] >> 32), 0x5410u);
+                            st_async_b32x4(xout + c * 512 + lane * 16, wq[0], wq[1], wq[2], wq[3], peer_xfull);
+                        }
+                        st_async_u32(xout + 2048 + lane * 4, inv_bits, peer_xfull);
+                        ++n_sent;
+                    }
+                    if (warp == 0 || warp == 2) PROF(3, it, 1);
+                    // ---- import the finished P of these rows (bf16 pairs) and the rescale factor
+                    if (!warp_wait_cluster(my_xfull, xph, abort_flag)) goto done;
+                    if (warp == 0 || warp == 2) PROF(3, it, 2);
+                    {
+                        uint32_t pw[NP];
+                        uint32_t dep;
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const uint4 o = *reinterpret_cast<const uint4*>(xin_p + c * 512 + lane * 16);
+                            pw[4 * c + 0] = o.x;
+                            pw[4 * c + 1] = o.y;
+                            pw[4 * c + 2] = o.z;
+                            pw[4 * c + 3] = o.w;
+                        }
+                        f2 = *reinterpret_cast<const float*>(xin_p + 2048 + lane * 4);
+                        // credit: the peer may overwrite the buffer.  The credit word is computed from every lane's
+                        // loaded values, so it cannot leave before all of the warp's reads have returned.
+                        dep = pw[0] | pw[4] | pw[8] | pw[12] | __float_as_uint(f2);
+                        dep = __reduce_or_sync(0xffffffffu, dep);
+                        if (lane == 0) st_async_u32(peer_xsink, dep, peer_xfree);
+                        if (kFp8) {
+#pragma unroll
+                            for (int v = 0; v < kPVariants; ++v) {
+                                const float4* sc = reinterpret_cast<const float4*>(ctl->row_scale[it % kScaleSlots][v]);
+#pragma unroll
+                                for (int j = 0; j < CPT / 4; ++j) {
+                                    const float4 w4 = sc[j];
+                                    const uint64_t a2 = pack2u(pw[2 * j] << 16, pw[2 * j] & 0xFFFF0000u);
+                                    const uint64_t b2 = pack2u(pw[2 * j + 1] << 16, pw[2 * j + 1] & 0xFFFF0000u);
+                                    pk[v][2 * j] = pack_bf16x2_from2(mul2(a2, pack2(w4.x, w4.y)));
+                                    pk[v][2 * j + 1] = pack_bf16x2_from2(mul2(b2, pack2(w4.z, w4.w)));
+                                }
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < NP; ++j) pk[0][j] = pw[j];
                         }
                     }
                 } else {
+                    // ================================ rows whose softmax this CTA computes
+                    if (!kRowSplit) {
+                        // ---- both CTAs compute these rows: send this CTA's partial scores (16-bit fixed point) ...
+                        float amax = 0.0f;
 #pragma unroll
-                    for (int j = 0; j < NP; ++j) pk[0][j] = pack_bf16x2_from2(tv2[j]);
+                        for (int j = 0; j < NP; ++j) {
+                            float v0, v1;
+                            unpack2(tv2[j], v0, v1);
+                            amax = fmaxf(amax, fmaxf(fabsf(v0), fabsf(v1)));
+                        }
+                        uint32_t e = __float_as_uint(amax) >> 23;
+                        e = e < 20u ? 20u : e;
+                        const float q_scale = __uint_as_float((268u - e) << 23) * 0.99996948f;
+                        const uint32_t inv_bits = e >= 255u ? 0x7FC00000u : __float_as_uint(__uint_as_float((e - 14u) << 23) * 1.0000305f);
+                        const uint64_t qs2 = pack2(q_scale, q_scale), qc2 = pack2(kQuantBias, kQuantBias);
+#pragma unroll
+                        for (int j = 0; j < NP; ++j) tv2[j] = fma2(tv2[j], qs2, qc2);
+                        if (n_sent > 0)
+                            if (!warp_wait_cluster(my_xfree, (n_sent & 1u) ^ 1u, abort_flag)) goto done;
+                        if (lane == 0) mbar_arrive_expect_tx(my_xfree, 4);
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            uint32_t wq[4];
+#pragma unroll
+                            for (int k = 0; k < 4; ++k)
+                                wq[k] = __byte_perm(static_cast<uint32_t>(tv2[4 * c + k]), static_cast<uint32_t>(tv2[4 * c + k] >> 32), 0x5410u);
+                            st_async_b32x4(xout + c * 512 + lane * 16, wq[0], wq[1], wq[2], wq[3], peer_xfull);
+                        }
+                        st_async_u32(xout + 2048 + lane * 4, inv_bits, peer_xfull);
+                        ++n_sent;
+                        // ... and take them back from the quantised form while the peer's are on their way
+                        const float own_inv = __uint_as_float(inv_bits);
+                        const uint64_t oi2 = pack2(own_inv, own_inv), nb2 = pack2(-kQuantBias, -kQuantBias);
+#pragma unroll
+                        for (int j = 0; j < NP; ++j) tv2[j] = mul2(add2(tv2[j], nb2), oi2);
+                    }
+                    // ---- add the peer's partial scores
+                    if (!warp_wait_cluster(my_xfull, xph, abort_flag)) goto done;
+                    if (warp == 0 || warp == 2) PROF(2, it, 2);
+                    {
+                        const float peer_inv = *reinterpret_cast<const float*>(xin_p + 2048 + lane * 4);
+                        const uint64_t pi2 = pack2(peer_inv, peer_inv), nb2 = pack2(-kQuantBias, -kQuantBias);
+                        uint32_t dep = __float_as_uint(peer_inv);
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const uint4 o = *reinterpret_cast<const uint4*>(xin_p + c * 512 + lane * 16);
+                            const uint32_t wq[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const uint64_t b2 = pack2u(__byte_perm(wq[k], 0x4B00u, 0x5410u), __byte_perm(wq[k], 0x4B00u, 0x5432u));
+                                tv2[4 * c + k] = fma2(add2(b2, nb2), pi2, tv2[4 * c + k]);
+                            }
+                            dep |= o.x;
+                        }
+                        dep = __reduce_or_sync(0xffffffffu, dep);
+                        if (lane == 0) st_async_u32(peer_xsink, dep, peer_xfree);
+                    }
+                    if (!kFp8)
+                        if (!warp_wait(smem_u32(&ctl->kv_full[it % S]), (it / S) & 1, abort_flag)) goto done;
+                    // ---- mask (padding slots; the mask is the same for every row, so a full tile skips this)
+                    const uint32_t mask = ctl->tile_mask[it % kMaskSlots];
+                    if (mask != 0xFFFFFFFFu) {
+#pragma unroll
+                        for (int j = 0; j < NP; ++j) {
+                            float v0, v1;
+                            unpack2(tv2[j], v0, v1);
+                            if (!((mask >> (2 * j)) & 1u)) v0 = -INFINITY;
+                            if (!((mask >> (2 * j + 1)) & 1u)) v1 = -INFINITY;
+                            tv2[j] = pack2(v0, v1);
+                        }
+                    }
+                    // ---- row maximum over the tile's 32 columns, in the log2 domain; the scale is positive, so
+                    // the maximum is taken on the raw scores and scaled once
+                    float mt;
+                    {
+                        float t[NP];
+#pragma unroll
+                        for (int j = 0; j < NP; ++j) {
+                            float v0, v1;
+                            unpack2(tv2[j], v0, v1);
+                            t[j] = fmaxf(v0, v1);
+                        }
+                        const float u0 = max3(t[0], t[1], t[2]), u1 = max3(t[3], t[4], t[5]), u2 = max3(t[6], t[7], t[8]);
+                        const float u3 = max3(t[9], t[10], t[11]), u4 = max3(t[12], t[13], t[14]);
+                        mt = fmaxf(max3(u0, u1, t[15]), max3(u2, u3, u4)) * p.scale_log2;
+                    }
+                    if (warp == 0 || warp == 2) PROF(7, it, 2);
+                    // ---- the row's reference maximum, moved in tile order.  This is the only step that waits
+                    // for the tile before (per lane quadrant: the warp of the previous team with the same rows),
+                    // and it is a handful of instructions: read the reference, move it if the tile's maximum
+                    // exceeds it by more than the lazy margin of 8, publish.
+                    if (!first)
+                        if (!warp_wait(smem_u32(&ctl->m_bar[buf_of<kFp8>(it - 1)][quad]), phase_of<kFp8>(it - 1), abort_flag)) goto done;
+                    const float m_cur = first ? -INFINITY : ctl->m_shared[row];
+                    const bool raise = mt > m_cur + 8.0f;
+                    const float m_fin = raise ? mt : m_cur;
+                    if (raise || first) ctl->m_shared[row] = m_fin;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&ctl->m_bar[tb][quad]));
+                    if (warp == 0 || warp == 2) PROF(7, it, 3);
+                    if (raise && !first) f2 = (m_cur == -INFINITY) ? 0.0f : ex2_approx(m_cur - m_fin);
+                    // ---- P = 2^(score - reference): at most 2^8; a masked slot gives 0
+                    const float m_fin_use = (m_fin == -INFINITY) ? 0.0f : m_fin;
+                    float lsum;
+                    {
+                        const uint64_t c2 = pack2(p.scale_log2, p.scale_log2), nm2 = pack2(-m_fin_use, -m_fin_use);
+                        uint64_t ls2 = pack2(0.0f, 0.0f);
+#pragma unroll
+                        for (int j = 0; j < NP; ++j) {
+                            float v0, v1;
+                            unpack2(fma2(tv2[j], c2, nm2), v0, v1);
+                            tv2[j] = pack2(ex2_approx(v0), ex2_approx(v1));
+                            ls2 = add2(ls2, tv2[j]);
+                        }
+                        float l0, l1;
+                        unpack2(ls2, l0, l1);
+                        lsum = l0 + l1;
+                    }
+                    if (l_part != 0.0f && l_ref != m_fin) l_part *= ex2_approx(l_ref - m_fin);
+                    l_part += lsum;
+                    l_ref = m_fin;
+                    // ---- P to the peer (bf16 pairs) with the rescale factor, once it has read the last one
+                    {
+                        uint32_t ps[NP];
+#pragma unroll
+                        for (int j = 0; j < NP; ++j) ps[j] = pack_bf16x2_from2(tv2[j]);
+                        if (kRowSplit) {
+                            if (n_sent > 0)
+                                if (!warp_wait_cluster(my_xfree, (n_sent & 1u) ^ 1u, abort_flag)) goto done;
+                            if (lane == 0) mbar_arrive_expect_tx(my_xfree, 4);   // the credit for this send
+#pragma unroll
+                            for (int c = 0; c < 4; ++c)
+                                st_async_b32x4(xout + c * 512 + lane * 16, ps[4 * c], ps[4 * c + 1], ps[4 * c + 2], ps[4 * c + 3], peer_xfull);
+                            st_async_u32(xout + 2048 + lane * 4, __float_as_uint(f2), peer_xfull);
+                            ++n_sent;
+                        }
+                        if (warp == 0 || warp == 2) PROF(2, it, 1);
+                        if (!kFp8) {
+#pragma unroll
+                            for (int j = 0; j < NP; ++j) pk[0][j] = ps[j];
+                        }
+                    }
+                    if (kFp8) {
+                        // two copies, each pre-multiplied by one scale group's row scales
+#pragma unroll
+                        for (int v = 0; v < kPVariants; ++v) {
+                            const float4* sc = reinterpret_cast<const float4*>(ctl->row_scale[it % kScaleSlots][v]);
+#pragma unroll
+                            for (int j = 0; j < CPT / 4; ++j) {
+                                const float4 w4 = sc[j];
+                                pk[v][2 * j] = pack_bf16x2_from2(mul2(tv2[2 * j], pack2(w4.x, w4.y)));
+                                pk[v][2 * j + 1] = pack_bf16x2_from2(mul2(tv2[2 * j + 1], pack2(w4.z, w4.w)));
+                            }
+                        }
+                    }
+                    if (warp == 0 || warp == 2) PROF(4, it, 1);
                 }
-                if (warp == 0 || warp == 4) PROF(4, it, 1);
                 // ---- hand P to the MMA warp: after the P V product that last read this tile's P buffer
                 if (it >= kBufReuse<kFp8>)
                     if (!warp_wait(smem_u32(&ctl->pv_done[buf_of<kFp8>(it - kBufReuse<kFp8>)]), phase_of<kFp8>(it - kBufReuse<kFp8>), abort_flag))
                         goto done;
-                if (__any_sync(0xffffffffu, raise) && !first) {
+                if (__any_sync(0xffffffffu, f2 != 1.0f) && !first) {
                     // the reference moved: O so far (complete once the previous tile's P V product has finished)
                     // is brought to the new reference before this tile's product is added
                     if (!warp_wait(smem_u32(&ctl->pv_done[buf_of<kFp8>(it - 1)]), phase_of<kFp8>(it - 1), abort_flag)) goto done;
                     tc_fence_after();
-                    const float f2 = raise ? ((m_cur == -INFINITY) ? 0.0f : ex2_approx(m_cur - m_fin)) : 1.0f;
 #pragma unroll 1
                     for (int oc = 0; oc < kDvHalf; oc += 32) {
                         uint32_t o[32];
@@ -704,29 +812,43 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
                     for (int v = 0; v < kPVariants; ++v) tmem_st_n<NP>(p0col + 16 * v, pk[v]);
                 }
-                if (warp == 0 || warp == 4) PROF(4, it, 2);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&ctl->p_full[tb]));
-                if (warp == 0 || warp == 4) PROF(2, it, 3);
+                if (warp == 0 || warp == 2) { if (own) PROF(2, it, 3); else PROF(3, it, 3); }
             }
             // ---- epilogue of the item (all sixteen warps)
             {
-                const uint32_t it_last = it_end - 1;
-                // every tile of the item has been committed: the row's reference maximum is final
-                if (!warp_wait(smem_u32(&ctl->p_full[buf_of<kFp8>(it_last)]), phase_of<kFp8>(it_last), abort_flag)) goto done;
-                const float m_ref = ctl->m_shared[row];
-                ctl->l_part[cg][row] = (l_part != 0.0f && l_ref != m_ref) ? l_part * ex2_approx(l_ref - m_ref) : l_part;
+                const int lp = item_n & 1;   // the row sums are kept per item parity: the next item's may arrive early
+                // Every warp arrives when its own tiles of the item are committed; once all sixteen have, every
+                // row's reference maximum is final.  (A per-item barrier and not the last tile's p_full: a parity
+                // wait is only safe when the barrier's previous phase has already completed, which a warp that
+                // finished early cannot know of another team's barrier.)
                 __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&ctl->l_bar));
+                if (lane == 0) mbar_arrive(smem_u32(&ctl->e_bar));
+                if (!warp_wait(smem_u32(&ctl->e_bar), item_n & 1, abort_flag)) goto done;
+                float m_ref = 0.0f;
+                if (own) {
+                    // this team's share of the row sums, for this CTA and for the peer (it holds the other half of
+                    // the rows' output columns)
+                    m_ref = ctl->m_shared[row];
+                    const float lv = (l_part != 0.0f && l_ref != m_ref) ? l_part * ex2_approx(l_ref - m_ref) : l_part;
+                    ctl->l_part[lp][cg][row] = lv;
+                    if (kRowSplit) st_cluster_u32(map_to_cta(smem_u32(&ctl->l_part[lp][cg][row]), peer), __float_as_uint(lv));
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(smem_u32(&ctl->l_bar));
+                        if (kRowSplit) mbar_arrive_cluster(map_to_cta(smem_u32(&ctl->l_bar), peer));
+                    }
+                }
                 if (w + 1 < w_end)
                     if (!q_store(p.works[w + 1], item_n + 1)) goto done;
-                if (!warp_wait(smem_u32(&ctl->l_bar), item_n & 1, abort_flag)) goto done;
+                if (!warp_wait_cluster(smem_u32(&ctl->l_bar), item_n & 1, abort_flag)) goto done;
                 float l = 0.0f;
 #pragma unroll
-                for (int g = 0; g < G; ++g) l += ctl->l_part[g][row];
-                if (!warp_wait(smem_u32(&ctl->pv_done[buf_of<kFp8>(it_last)]), phase_of<kFp8>(it_last), abort_flag)) goto done;
+                for (int g = 0; g < G; ++g) l += ctl->l_part[lp][g][row];
+                if (!warp_wait(smem_u32(&ctl->o_full), item_n & 1, abort_flag)) goto done;
                 tc_fence_after();
                 const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
                 const int head = wi.head_block * kHeadsPerBlock + row;
@@ -753,7 +875,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                             }
                         }
                     }
-                    if (live && half == 0 && cg == 0 && p.lse != nullptr) p.lse[(size_t)wi.q_row * p.H + head] = lse_nat;
+                    if (live && (kRowSplit ? own : half == 0) && cg == 0 && p.lse != nullptr) p.lse[(size_t)wi.q_row * p.H + head] = lse_nat;
                 } else {
                     float* o_dst = p.o_accum + ((size_t)wi.partial_slot * kHeadsPerBlock + row) * kDV + half * kDvHalf;
 #pragma unroll 1
@@ -767,7 +889,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                             d4[v] = make_float4(__uint_as_float(o[4 * v + 0]) * inv, __uint_as_float(o[4 * v + 1]) * inv,
                                                 __uint_as_float(o[4 * v + 2]) * inv, __uint_as_float(o[4 * v + 3]) * inv);
                     }
-                    if (half == 0 && cg == 0)
+                    if ((kRowSplit ? own : half == 0) && cg == 0)
                         p.lse_accum[(size_t)wi.partial_slot * kHeadsPerBlock + row] = (l > 0.0f) ? lse_nat : -FLT_MAX;
                 }
                 tc_fence_before();
@@ -776,9 +898,12 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
             it_base = it_end;
         }
+        // nothing this warp sent may still be on its way when the CTA exits: wait for the credit of the last send
+        if (n_sent > 0)
+            if (!warp_wait_cluster(my_xfree, (n_sent & 1u) ^ 1u, abort_flag)) goto done;
     } else {
     setmaxnreg_dec<kRegsOther>();
-    if (warp == kMmaWarp) {
+    if (warp == mma_warp) {
         // ============================================================ score MMA issuer
         // The whole warp runs the loop converged (descriptors stay warp-uniform); one elected lane issues.
         // Scores and P V products are issued by two different warps, each blocking on its own inputs, so
@@ -813,7 +938,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 PROF(1, it, 1);
             }
         }
-    } else if (warp == kPvWarp) {
+    } else if (warp == pv_warp) {
         // ============================================================ P V MMA issuer
         const uint32_t el = elect_one() ? 1u : 0u;
         const uint64_t v_desc0 = make_smem_desc_sw128(smem_u32(sKV), kKvBlockBytes, 1024); // MN-major view
@@ -840,6 +965,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 tc_commit_el(smem_u32(&ctl->kv_empty[s]), el);
                 PROF(6, it, 1);
                 tc_commit_el(smem_u32(&ctl->pv_done[sb]), el);
+                if (t + 1 == n_tiles) tc_commit_el(smem_u32(&ctl->o_full), el);
                 PROF(1, it, 3);
             }
         }
@@ -924,7 +1050,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         // 32-bit elements so that a request may be wider than 256 bytes); every lane fetches its row's two
         // scales by cp.async straight into the scale table.  The issuers run ahead of the converters by the
         // raw ring (kRawStages tiles), across items.
-        const int iw = warp - kGatherWarp0;
+        const int iw = warp - gather_warp0;
         const int gl = lane & 7;
         const int oob_row = (int)p.num_kv_rows;
         const uint32_t row_bytes = half ? 400u : 256u;   // latent half (+ scales + rope)
@@ -1024,10 +1150,8 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if ((it & 1u) != static_cast<uint32_t>(grp)) continue;
                 const int rs = it % R, s = it % S;
                 if (!warp_wait(smem_u32(&ctl->raw_full[rs]), (it / R) & 1, abort_flag)) goto done;
-                if (cw == 0) PROF(3, it, 2);
                 if (cw == 4) PROF(5, it, 2);
                 if (!warp_wait(smem_u32(&ctl->kv_empty[s]), ((it / S) & 1) ^ 1, abort_flag)) goto done;
-                if (cw == 0) PROF(3, it, 0);
                 if (cw == 4) PROF(5, it, 0);
                 const uint8_t* row_raw = sRaw + rs * kRawTileBytes + (r >> 2) * kRawGroupBytes + (r & 3) * row_bytes;
                 const uint8_t* src = row_raw + qd * 64;
@@ -1057,14 +1181,12 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     *reinterpret_cast<uint4*>(d + (((2 * qd + 0) ^ (r & 7)) * 16)) = a;
                     *reinterpret_cast<uint4*>(d + (((2 * qd + 1) ^ (r & 7)) * 16)) = b;
                 }
-                if (cw == 0) PROF(3, it, 3);
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(smem_u32(&ctl->kv_full[s]));
                     mbar_arrive(smem_u32(&ctl->raw_empty[rs]));
                 }
-                if (cw == 0) PROF(3, it, 1);
                 if (cw == 4) PROF(5, it, 1);
             }
         }
@@ -1172,14 +1294,20 @@ __global__ void __launch_bounds__(256) pack_fp8_rows_kernel(const float* __restr
 }
 
 // ------------------------------------------------------------------ launch helpers (called from capi.cu)
+// The opt-in for more than 48 KB of dynamic shared memory is a per-device attribute of the kernel: it is
+// set once for every device this process launches on (the current device at the time of the call).
 template <bool kFp8>
 static cudaError_t configure() {
-    static bool done = false;
-    if (done) return cudaSuccess;
-    cudaError_t e = cudaFuncSetAttribute(sparse_mla_kernel<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg<kFp8>::kSmemBytes);
+    static std::mutex mu;
+    static bool done[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
-    done = true;
+    std::lock_guard<std::mutex> guard(mu);
+    if (dev >= 0 && dev < 64 && done[dev]) return cudaSuccess;
+    e = cudaFuncSetAttribute(sparse_mla_kernel<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<kFp8>::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) done[dev] = true;
     return cudaSuccess;
 }
 

@@ -61,26 +61,33 @@ def decode_fp8(B=64, H=128, kv_len=32768, topk=2048, page=64, pad_frac=0.05, n_b
                 page=page, n_valid=topk - n_pad, s_q=s_q)
 
 
-def prefill_bf16(T=4096, H=128, topk=2048, seed=2026, device="cuda", q_begin=0, q_end=None):
-    """Causal prefill of queries [q_begin, q_end) of a T-token sequence (the whole cache is built)."""
+def prefill_bf16(T=4096, H=128, topk=2048, seed=2026, device="cuda", q_begin=0, q_end=None, block=1024):
+    """Causal prefill of queries [q_begin, q_end) of a T-token sequence (the whole cache is built).
+    Queries and index lists are drawn per block of `block` absolute query positions from a generator
+    seeded by (seed, block number), so any query range is a slice of the same T-token problem."""
     q_end = T if q_end is None else q_end
-    g = _gen(seed, device)
-    kv = torch.randn(T, D_QK, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    kv = torch.randn(T, D_QK, generator=_gen(seed, device), device=device, dtype=torch.float32).to(torch.bfloat16)
     nq = q_end - q_begin
-    q = torch.randn(nq, H, D_QK, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    q = torch.empty(nq, H, D_QK, dtype=torch.bfloat16, device=device)
     idx = torch.full((nq, topk), -1, dtype=torch.int32, device=device)
-    t = torch.arange(q_begin, q_end, device=device)
-    chunk = 1024
-    for c0 in range(0, nq, chunk):
-        c1 = min(nq, c0 + chunk)
-        tt = t[c0:c1]
-        width = int(tt.max().item()) + 1
-        keys = torch.rand(c1 - c0, width, generator=g, device=device)
+    for b in range(q_begin // block, (q_end + block - 1) // block):
+        g = _gen(seed * 1000003 + 17 * b + 1, device)
+        t0, t1 = b * block, min(T, (b + 1) * block)
+        qb = torch.randn(t1 - t0, H, D_QK, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+        tt = torch.arange(t0, t1, device=device)
+        width = t1
+        keys = torch.rand(t1 - t0, width, generator=g, device=device)
         keys[torch.arange(width, device=device)[None, :] > tt[:, None]] = 2.0  # positions after t sort last
-        order = keys.argsort(dim=1)[:, :topk].to(torch.int32)
-        k = order.shape[1]
+        k = min(topk, width)
+        order = keys.topk(k, dim=1, largest=False).indices.to(torch.int32)
+        del keys
         valid = torch.arange(k, device=device)[None, :] <= tt[:, None]
-        idx[c0:c1, :k] = torch.where(valid, order, torch.full_like(order, -1))
+        ib = torch.full((t1 - t0, topk), -1, dtype=torch.int32, device=device)
+        ib[:, :k] = torch.where(valid, order, torch.full_like(order, -1))
+        lo, hi = max(t0, q_begin), min(t1, q_end)
+        q[lo - q_begin:hi - q_begin] = qb[lo - t0:hi - t0]
+        idx[lo - q_begin:hi - q_begin] = ib[lo - t0:hi - t0]
+    t = torch.arange(q_begin, q_end, device=device)
     valid_len = torch.minimum(t + 1, torch.tensor(topk, device=device)).to(torch.int32)
     return dict(q=q, kv=kv, indices=idx.contiguous(), valid_len=valid_len.cpu().numpy(), T=T, H=H, topk=topk,
                 n_pairs=int(valid_len.sum().item()))

@@ -4,17 +4,28 @@
     python bench.py --gpus N --steps K --warmup W            this library (one process per GPU)
     python bench.py --impl reference --steps K --warmup W    the reference's CPU path on the host cores
 
-A step is one pass of the decode pipeline (attention kernel + split merge; the plan is built once
-outside the loop, as the reference keeps its metadata kernel out of the timed loop) over one batch of
-the fp8 decode workload: batch 64, 128 heads, top-k 2048 (last 5 % of slots -1), kv_len 32768 in a
-paged fp8 cache of 64-token blocks with a permuted block table.  Successive steps use different
-batches (queries and index lists) so the rows gathered by consecutive steps exceed the L2.
-With N > 1 every rank runs its own batch of 64 sequences against its own cache (the path shards by
-sequence with no exchange), so scaling is weak and `value` is the sum over ranks.
+Headline (the JSON line's `value`): a step is one pass of the decode pipeline (attention kernel + split
+merge; the plan is built once outside the loop, as the reference keeps its metadata kernel out of the timed
+loop) over one batch of the fp8 decode workload: batch 64, 128 heads, top-k 2048 (last 5 % of slots -1),
+kv_len 32768 in a paged fp8 cache of 64-token blocks with a permuted block table.  Successive steps use
+different batches (queries and index lists) so the rows gathered by consecutive steps exceed the L2.
+With N > 1 every rank runs its own batch of 64 sequences against its own cache (replicas: the path shards
+by sequence with no exchange), so that number scales weakly and `value` is the sum over ranks.
 
-Prints one JSON line (rank 0).  `value` is TFLOP/s of algorithmic work, 2 * H * (576 + 512) * pairs,
-pairs = valid (query, position) slots, with inputs resident in HBM; `e2e` is the same through the
-host-buffer C-ABI call with pinned host queries / index lists in and outputs back every step.
+The same line carries, measured in the same run:
+  `prefill`  (N = 1)  the other half of the metric: the 4096-token causal bf16 prefill, with its own
+                      roofline and CPU baseline;
+  `sharded`  (every N) the configurations that are partitioned over the GPUs of the box, each over the
+                      same problem size at every N (strong scaling):
+        cfg4_tp     MTP fp8 decode, batch 128 x 2 query rows, 128 heads sharded 128 / N per GPU, cache
+                    replicated, NCCL all-gather of the outputs (timed with and without the gather)
+        cfg4_batch  the same problem sharded by sequence: 128 / N sequences per GPU, all 128 heads
+        cfg5        131072-token causal bf16 prefill, queries cut into contiguous chunks of equal work,
+                    latent cache replicated, no collective
+
+`value` is TFLOP/s of algorithmic work, 2 * H * (576 + 512) * pairs, pairs = valid (query, position)
+slots, with inputs resident in HBM; `e2e` is the same through the host-buffer C-ABI call with pinned host
+queries / index lists in and outputs back every step.
 """
 import argparse
 import ctypes as C
@@ -30,10 +41,10 @@ sys.path.insert(0, ROOT)
 
 D_QK, D_V = 576, 512
 CFG = dict(B=64, H=128, kv_len=32768, topk=2048, page=64, pad_frac=0.05, n_batches=4)
-FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)
-# dram bytes (read + write) of one attention-kernel launch on the workload above, from the ncu
-# capture summarised in profiles/ (null until a capture exists for the current kernel)
-NCU_TRAFFIC_BYTES_AT_BATCH16 = 28.46e6  # dram read + write of one launch captured at batch 16 (profiles/sparse_mla_fp8_decode_cluster_kernel.md)
+CFG4 = dict(B=128, s_q=2, H=128, kv_len=65536, topk=2048, page=64)
+CFG5_TOKENS = 131072
+FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
+SM_SCALE = 1.0 / math.sqrt(192.0)
 
 
 def peaks():
@@ -41,8 +52,21 @@ def peaks():
     if os.path.exists(path):
         with open(path) as f:
             d = json.load(f)
-        return dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]), source="measured")
+        return dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]),
+                    bf16_tflops_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), source="measured")
     return dict(FALLBACK_PEAKS, source="fallback")
+
+
+def measured_traffic(batch):
+    """DRAM bytes (read + write) of one attention launch of the headline workload, from the ncu capture
+    recorded beside its summary (taken at a smaller batch; traffic is proportional to the batch because
+    every sequence has its own cache pages).  None when no capture of the current kernel is recorded."""
+    path = os.path.join(ROOT, "profiles", "sparse_mla_fp8_decode_traffic.json")
+    if not os.path.exists(path):
+        return None
+    with open(path) as f:
+        d = json.load(f)
+    return float(d["dram_bytes_per_launch"]) * batch / float(d["batch"])
 
 
 class ClockSampler:
@@ -83,6 +107,7 @@ class ClockSampler:
 
     def start(self):
         if self.nv:
+            self._stop.clear()
             self._thread = threading.Thread(target=self._run, daemon=True)
             self._thread.start()
 
@@ -90,6 +115,7 @@ class ClockSampler:
         if self._thread:
             self._stop.set()
             self._thread.join()
+            self._thread = None
             try:
                 self._once()
             except Exception:
@@ -140,9 +166,41 @@ def reference_cpu(sample_queries, n_valid, H, repeats=1):
     from opfoundry_b200 import synth
     case = synth.make_decode_case(B, H, max(n_valid, 64), n_valid, fp8=True, seed=1)
     t0 = time.perf_counter()
-    O.sparse_mla(case["q"], case["kv"], case["indices"], 1 / math.sqrt(192), kv_is_fp8=True, kv_batch_stride_rows=case["kv_batch_stride_rows"],
+    O.sparse_mla(case["q"], case["kv"], case["indices"], SM_SCALE, kv_is_fp8=True, kv_batch_stride_rows=case["kv_batch_stride_rows"],
                  num_threads=cores)
     return time.perf_counter() - t0, cores, kind
+
+
+def reference_cpu_prefill(valid_lens, H, kv_rows):
+    """The reference's bf16 CPU function (host.cc:508-548) on a sample of prefill queries: every sampled
+    query is one 'batch' of its CSR page table with its own list of `valid_lens[i]` rows.  Returns
+    (seconds, cores, kind)."""
+    import numpy as np
+    from oracle import oracle as O
+    R = O.ref_lib()
+    cores = int(os.environ.get("MLA_DECODE_NUM_THREADS", os.cpu_count() or 1))
+    n = len(valid_lens)
+    rng = np.random.default_rng(1)
+    ip = np.concatenate([[0], np.cumsum(valid_lens)]).astype(np.int32)
+    ix = np.concatenate([rng.permutation(kv_rows)[:v] for v in valid_lens]).astype(np.int32)
+    if R is not None:
+        q = np.zeros((n, H, D_QK), np.uint16)
+        kv = np.zeros((kv_rows, D_QK), np.uint16)
+        R.ref_rand_bf16(O._p(q), q.size)
+        R.ref_rand_bf16(O._p(kv), kv.size)
+        out = np.zeros((n, H, D_V), np.uint16); lse = np.zeros((n, H), np.float32)
+        t0 = time.perf_counter()
+        R.ref_attention_bf16(O._p(q), O._p(kv), O._p(out), O._p(lse), O._p(ip), O._p(ix), n, H, 1)
+        return time.perf_counter() - t0, cores, "reference"
+    q = rng.integers(0x3c00, 0x4000, size=(n, H, D_QK)).astype(np.uint16)
+    kv = rng.integers(0x3c00, 0x4000, size=(kv_rows, D_QK)).astype(np.uint16)
+    topk = int(max(valid_lens))
+    idx = np.full((n, topk), -1, np.int32)
+    for i, v in enumerate(valid_lens):
+        idx[i, :v] = ix[ip[i]:ip[i + 1]]
+    t0 = time.perf_counter()
+    O.sparse_mla(q, kv, idx, SM_SCALE, s_q=n, num_threads=cores)
+    return time.perf_counter() - t0, cores, "port"
 
 
 def cpu_baseline_block(budget_s=15.0):
@@ -153,6 +211,26 @@ def cpu_baseline_block(budget_s=15.0):
     tf = flops_of(n * n_valid, H) / t / 1e12
     return dict(value=tf, unit="TFLOP/s", cores=cores, kind=kind, seconds=round(t, 3),
                 sample="%d of %d decode queries x %d heads x %d valid rows, reference fp8 CPU function" % (n, CFG["B"], H, n_valid))
+
+
+def cpu_baseline_prefill(T, topk, H, budget_s=10.0):
+    """A deterministic sample of the prefill's queries (short ones, the tile-boundary ones, then evenly
+    spaced ones) through the reference's bf16 CPU function; the rate is per (query-head, position) pair, so
+    the whole prefill's CPU time follows by the pair count."""
+    import numpy as np
+    probe = [min(T, topk)]
+    t1, cores, kind = reference_cpu_prefill(probe, H, T)
+    n = int(max(4, min(64, budget_s / max(t1, 1e-3))))
+    qs = sorted(set([0, 31, 32, 63, 64] + [int(x) for x in np.linspace(0, T - 1, n)]))
+    lens = [min(t + 1, topk) for t in qs]
+    t, cores, kind = reference_cpu_prefill(lens, H, T)
+    pairs = float(sum(lens))
+    tf = flops_of(pairs, H) / t / 1e12
+    total_pairs = float(np.minimum(np.arange(T) + 1, topk).sum())
+    return dict(value=tf, unit="TFLOP/s", cores=cores, kind=kind, seconds=round(t, 3),
+                sample="%d of %d prefill queries (%d of %d pairs) x %d heads, reference bf16 CPU function" % (
+                    len(qs), T, int(pairs), int(total_pairs), H),
+                extrapolated_seconds_whole_prefill=round(t * total_pairs / pairs, 1))
 
 
 def run_reference_arm(args, rank):
@@ -185,150 +263,208 @@ def workload_config():
                 valid_len_hint="given to the planner (the analogue of the reference's kv_indptr lengths)")
 
 
-def run_prefill(args, rank, world, local_rank, torch, dist, api, workloads):
-    """bf16 causal prefill: one sequence of T tokens, 128 heads, top-k 2048; a step = the whole prefill.
-    With N > 1 ranks the query tokens are cut into contiguous chunks of equal work, the latent cache is
-    replicated and nothing is exchanged (strong scaling of one sequence)."""
-    from opfoundry_b200 import shard
+# --------------------------------------------------------------------------- timing helper
+class Env:
+    """What every leg needs: rank facts, the library, and a timed loop that follows the timing rules
+    (warm-up, barrier + synchronize on both sides, CUDA events on the launching stream, max over ranks)."""
+
+    def __init__(self, rank, world, local_rank, torch, dist, api, workloads):
+        self.rank, self.world, self.local_rank = rank, world, local_rank
+        self.torch, self.dist, self.api, self.workloads = torch, dist, api, workloads
+        self.L = api.lib()
+        self.sampler = ClockSampler(local_rank)
+
+    def stream(self):
+        return C.c_void_p(self.torch.cuda.current_stream().cuda_stream)
+
+    def barrier(self):
+        self.torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier()
+            self.torch.cuda.synchronize()
+
+    def max_ms(self, ms):
+        t = self.torch.tensor([ms], dtype=self.torch.float64, device="cuda")
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(self, step, steps, warmup, status_args=None):
+        """ms per step, max over ranks."""
+        torch = self.torch
+        for i in range(max(3, warmup)):
+            step(i)
+        torch.cuda.synchronize()
+        if status_args is not None:
+            self.api._check(self.L.dsa_v32_device_status(C.byref(status_args), self.stream()), "device status after warm-up")
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self.barrier()
+        self.sampler.start()
+        e0.record()
+        for i in range(steps):
+            step(i)
+        e1.record()
+        self.barrier()
+        self.sampler.stop()
+        if status_args is not None:
+            self.api._check(self.L.dsa_v32_device_status(C.byref(status_args), self.stream()), "device status after the timed region")
+        return self.max_ms(e0.elapsed_time(e1)) / steps
+
+    def free(self):
+        import gc
+        gc.collect()
+        self.torch.cuda.empty_cache()
+
+
+def roofline_block(flops_per_gpu, bytes_per_gpu, ms, pk, kernel, sustained=False):
+    """The slower of the two bounds sets the roofline of one GPU's share of a step."""
+    peak_tf = pk["bf16_tflops_sustained"] if sustained else pk["bf16_tflops"]
+    t_flop = flops_per_gpu / (peak_tf * 1e12) * 1e6
+    t_mem = bytes_per_gpu / (pk["hbm_gbs"] * 1e9) * 1e6
+    bound = "tensor" if t_flop >= t_mem else "hbm"
+    t_us = ms * 1e3
+    if bound == "tensor":
+        achieved, peak, unit = flops_per_gpu / (t_us * 1e-6) / 1e12, peak_tf, "TFLOP/s"
+    else:
+        achieved, peak, unit = bytes_per_gpu / (t_us * 1e-6) / 1e9, pk["hbm_gbs"], "GB/s"
+    return dict(bound=bound, achieved=achieved, peak=peak, unit=unit, frac=achieved / peak, traffic=None,
+                peak_source=pk["source"] + (" (sustained)" if sustained else " (burst)"), kernel=kernel,
+                t_flop_us=t_flop, t_mem_us=t_mem, flops_per_gpu=flops_per_gpu, gathered_bytes_per_gpu=bytes_per_gpu)
+
+
+# --------------------------------------------------------------------------- prefill (config 3 / config 5)
+def prefill_leg(env, T, steps, warmup, label):
+    """bf16 causal prefill of one T-token sequence, 128 heads, top-k 2048; a step = the whole prefill.  With
+    N > 1 ranks the query tokens are cut into contiguous chunks of equal work, the latent cache is replicated
+    and nothing is exchanged (strong scaling of one sequence)."""
     import numpy as np
-    T, H, topk = args.tokens, CFG["H"], CFG["topk"]
+    from opfoundry_b200 import shard
+    torch, api = env.torch, env.api
+    H, topk = CFG["H"], CFG["topk"]
     valid_all = np.minimum(np.arange(T) + 1, topk)
-    bounds = shard.shard_queries_equal_work(valid_all, world)
-    q0, q1 = bounds[rank], bounds[rank + 1]
-    W = workloads.prefill_bf16(T=T, H=H, topk=topk, seed=2026, q_begin=q0, q_end=q1)
+    bounds = shard.shard_queries_equal_work(valid_all, env.world)
+    q0, q1 = bounds[env.rank], bounds[env.rank + 1]
+    W = env.workloads.prefill_bf16(T=T, H=H, topk=topk, seed=2026, q_begin=q0, q_end=q1)
     nq = q1 - q0
     plan = api.mla_decode_plan_create(nq, H, topk, nq, valid_len_hint=W["valid_len"])
     out = torch.empty(nq, H, D_V, dtype=torch.bfloat16, device="cuda")
     lse = torch.empty(nq, H, dtype=torch.float32, device="cuda")
-    a = api.make_args(W["q"], W["kv"], W["indices"], plan, 1.0 / math.sqrt(192.0), out=out, lse=lse)
-    L = api.lib()
-    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
-
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-
-    for _ in range(args.warmup):
-        api._check(L.dsa_v32_decode_pipeline(C.byref(a), 0, stream), "prefill")
-    torch.cuda.synchronize()
-    api._check(L.dsa_v32_device_status(C.byref(a), stream), "device status")
-    K = args.steps
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler = ClockSampler(local_rank)
-    barrier()
-    sampler.start()
-    e0.record()
-    for _ in range(K):
-        api._check(L.dsa_v32_decode_pipeline(C.byref(a), 0, stream), "prefill")
-    e1.record()
-    barrier()
-    sampler.stop()
-    ms = shard.max_over_ranks([e0.elapsed_time(e1)], "cuda")[0] / K
-    total_pairs = float(valid_all.sum())
-    if rank == 0:
-        pk = peaks()
-        flops = flops_of(total_pairs, H)
-        tf = flops / (ms * 1e-3) / 1e12
-        print(json.dumps(dict(
-            metric="sparse_mla_prefill_bf16_tflops", value=tf, unit="TFLOP/s", n_gpus=world, steps=K, warmup=args.warmup,
-            ms_per_step=ms, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="bf16 MMA, fp32 accumulate",
-            data="synthetic",
-            config=dict(workload="prefill_bf16_t%d_h128_topk2048_causal" % T, tokens=T, heads=H, topk=topk, pairs=total_pairs,
-                        sharding="contiguous query chunks of equal work, latent cache replicated, no exchange",
-                        l2="gathered rows per step %.1f GB from a %.1f MB cache (L2-resident by construction of the config)" % (
-                            total_pairs * 1152 / 1e9, T * 1152 / 1e6)),
-            roofline=dict(bound="tensor", achieved=tf, peak=pk["bf16_tflops"], unit="TFLOP/s", frac=tf / pk["bf16_tflops"],
-                          traffic=None, peak_source=pk["source"], kernel="sparse_mla_kernel<bf16>",
-                          flops_per_launch=flops, gathered_bytes_per_launch=total_pairs * 1152.0),
-            gpu_launches=K * (2 if plan.info.num_partials > 0 else 1), clocks=sampler.summary())), flush=True)
-
-
-def run_decode_tp(args, rank, world, local_rank, torch, dist, api, workloads):
-    """fp8 decode with one MTP token, head-sharded (the TP layout of a serving stack): batch 128, two
-    query rows per sequence (half of the sequences share one index list between their rows), 128 heads in
-    total of which every rank attends 128 / N, kv_len 65536 in 64-token pages, top-k 2048, the latent cache
-    replicated on every rank; a step = attention on the local heads + one NCCL all-gather of the outputs.
-    Strong scaling: the total work is fixed.  Note what the layout costs: the tensor-core tile has 128 rows
-    (heads), so a rank with 128 / N heads still pays for 128, while its gathered bytes stay the same."""
-    from opfoundry_b200 import shard
-    B, s_q, H_all, kv_len, topk, page = args.batch if args.batch != 64 else 128, 2, 128, 65536, 2048, 64
-    h0, h1 = shard.shard_heads(H_all, world, rank)
-    Hl = h1 - h0
-    W = workloads.decode_fp8(B=B, H=H_all, kv_len=kv_len, topk=topk, page=page, pad_frac=0.0, n_batches=2, seed=2026, s_q=s_q)
-    total_q = B * s_q
-    g = torch.Generator(device="cuda")
-    g.manual_seed(99)
-    share = torch.rand(B, generator=g, device="cuda") < 0.5          # sequences whose two rows share a list
-    steps = []
-    for q, idx in W["steps"]:
-        idx = idx.clone().view(B, s_q, topk)
-        idx[share, 1] = idx[share, 0]
-        steps.append((q[:, h0:h1].contiguous(), idx.view(total_q, topk).contiguous()))
-    plan = api.mla_decode_plan_create(total_q, Hl, topk, s_q)
-    out = torch.empty(total_q, Hl, D_V, dtype=torch.bfloat16, device="cuda")
-    lse = torch.empty(total_q, Hl, dtype=torch.float32, device="cuda")
-    gathered = torch.empty(world, total_q, Hl, D_V, dtype=torch.bfloat16, device="cuda")   # rank-major; heads of rank r = block r
-    arg_sets = [api.make_args(q, W["cache"], idx, plan, 1.0 / math.sqrt(192.0), out=out, lse=lse, block_table=W["block_table"],
-                              page_block_size=page) for q, idx in steps]
-    L = api.lib()
-    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    a = api.make_args(W["q"], W["kv"], W["indices"], plan, SM_SCALE, out=out, lse=lse)
 
     def step(i):
-        api._check(L.dsa_v32_decode_pipeline(C.byref(arg_sets[i % len(arg_sets)]), 0, stream), "decode step")
+        api._check(env.L.dsa_v32_decode_pipeline(C.byref(a), 0, env.stream()), "prefill")
+
+    ms = env.timed(step, steps, warmup, a)
+    total_pairs = float(valid_all.sum())
+    local_pairs = float(valid_all[q0:q1].sum())
+    pk = peaks()
+    flops = flops_of(total_pairs, H)
+    tf = flops / (ms * 1e-3) / 1e12
+    # the whole job's rate against N GPUs' tensor peak; a long prefill runs under the power cap, so the
+    # sustained peak is given beside the burst one
+    block = dict(workload="%s_prefill_bf16_t%d_h128_topk2048_causal" % (label, T), tokens=T, heads=H, topk=topk, n_gpus=env.world,
+                 ms_per_step=ms, tflops=tf, steps=steps, pairs=total_pairs, pairs_rank0=local_pairs,
+                 sharding="contiguous query chunks of equal work, latent cache replicated, no exchange",
+                 l2="gathered rows per step %.1f GB from a %.1f MB cache (the cache is L2-resident by construction of the config)" % (
+                     total_pairs * 1152 / 1e9, T * 1152 / 1e6),
+                 roofline=dict(bound="tensor", achieved=tf, peak=env.world * pk["bf16_tflops"], unit="TFLOP/s",
+                               frac=tf / (env.world * pk["bf16_tflops"]),
+                               frac_of_sustained=tf / (env.world * pk["bf16_tflops_sustained"]), traffic=None,
+                               peak_source=pk["source"], kernel="sparse_mla_kernel<bf16>", flops_per_step=flops,
+                               gathered_bytes_per_step=total_pairs * 1152.0,
+                               t_flop_us=flops / env.world / (pk["bf16_tflops"] * 1e12) * 1e6),
+                 gpu_launches=steps * (2 if plan.info.num_partials > 0 else 1), clocks=env.sampler.summary())
+    del W, plan, out, lse, a
+    env.free()
+    return block
+
+
+# --------------------------------------------------------------------------- config 4 (MTP fp8 decode)
+def cfg4_problem(env, seq_begin, seq_end, n_batches=2):
+    """Sequences [seq_begin, seq_end) of the config-4 problem: paged fp8 cache of those sequences, and for
+    each of `n_batches` steps the queries [seqs * 2, 128, 576] and their index lists (the two rows of a
+    sequence share one list for the sequences a seeded coin picks)."""
+    torch = env.torch
+    c = CFG4
+    n = seq_end - seq_begin
+    W = env.workloads.decode_fp8(B=n, H=c["H"], kv_len=c["kv_len"], topk=c["topk"], page=c["page"], pad_frac=0.0,
+                                 n_batches=n_batches, seed=4000 + seq_begin, s_q=c["s_q"])
+    g = torch.Generator(device="cuda")
+    g.manual_seed(99)
+    share = (torch.rand(c["B"], generator=g, device="cuda") < 0.5)[seq_begin:seq_end]
+    steps = []
+    for q, idx in W["steps"]:
+        idx = idx.clone().view(n, c["s_q"], c["topk"])
+        idx[share, 1] = idx[share, 0]
+        steps.append((q, idx.view(n * c["s_q"], c["topk"]).contiguous()))
+    W["steps"] = steps
+    W["share_frac"] = float(share.float().mean().item()) if n else 0.0
+    return W
+
+
+def cfg4_leg(env, mode, steps, warmup):
+    """mode "tp": every rank attends all 128 x 2 query rows with its 128 / N heads over the replicated cache;
+    mode "batch": every rank attends its 128 / N sequences with all 128 heads over its own sequences' cache.
+    Both end with one NCCL all-gather of the bf16 outputs (the only exchange the path has); the step is
+    timed with and without it."""
+    from opfoundry_b200 import shard
+    torch, api, dist = env.torch, env.api, env.dist
+    c = CFG4
+    world, rank = env.world, env.rank
+    if mode == "tp":
+        h0, h1 = shard.shard_heads(c["H"], world, rank)
+        s0, s1 = 0, c["B"]
+    else:
+        h0, h1 = 0, c["H"]
+        s0, s1 = shard.shard_batch(c["B"], world, rank)
+    Hl, nseq = h1 - h0, s1 - s0
+    W = cfg4_problem(env, s0, s1)
+    total_q = nseq * c["s_q"]
+    step_in = [(q[:, h0:h1].contiguous(), idx) for q, idx in W["steps"]]
+    plan = api.mla_decode_plan_create(total_q, Hl, c["topk"], c["s_q"])
+    out = torch.empty(total_q, Hl, D_V, dtype=torch.bfloat16, device="cuda")
+    lse = torch.empty(total_q, Hl, dtype=torch.float32, device="cuda")
+    gathered = torch.empty(world, total_q, Hl, D_V, dtype=torch.bfloat16, device="cuda") if world > 1 else None
+    arg_sets = [api.make_args(q, W["cache"], idx, plan, SM_SCALE, out=out, lse=lse, block_table=W["block_table"],
+                              page_block_size=c["page"]) for q, idx in step_in]
+
+    def attn(i):
+        api._check(env.L.dsa_v32_decode_pipeline(C.byref(arg_sets[i % len(arg_sets)]), 0, env.stream()), "decode step")
+
+    def attn_gather(i):
+        attn(i)
         if world > 1:
-            dist.all_gather_into_tensor(gathered, out)
+            dist.all_gather_into_tensor(gathered, out)   # rank-major: block r = rank r's heads (tp) or sequences (batch)
 
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-
-    for i in range(args.warmup):
-        step(i)
-    torch.cuda.synchronize()
-    api._check(L.dsa_v32_device_status(C.byref(arg_sets[0]), stream), "device status")
-    K = args.steps
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler = ClockSampler(local_rank)
-    barrier()
-    sampler.start()
-    e0.record()
-    for i in range(K):
-        step(i)
-    e1.record()
-    barrier()
-    sampler.stop()
-    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item()) / K
-    if rank == 0:
-        pk = peaks()
-        pairs = float(total_q * topk)
-        flops = flops_of(pairs, H_all)
-        tf = flops / (ms * 1e-3) / 1e12
-        launches = (2 if plan.info.num_partials > 0 else 1)
-        print(json.dumps(dict(
-            metric="sparse_mla_decode_fp8_mtp_tp_tflops", value=tf, unit="TFLOP/s", n_gpus=world, steps=K, warmup=args.warmup,
-            ms_per_step=ms, higher_is_better=True, scaling="strong", vs_baseline=None,
-            dtype="bf16 MMA, fp32 accumulate (fp8 e4m3 cache)", data="synthetic",
-            config=dict(workload="decode_fp8_mtp_b%d_sq2_h128_topk2048_kv65536_paged64_tp%d" % (B, world), batch=B, s_q=s_q,
-                        heads_total=H_all, heads_per_gpu=Hl, topk=topk, kv_len=kv_len,
-                        sharding="heads sharded %d per GPU, latent cache replicated, one NCCL all-gather of the outputs per step" % Hl,
-                        l2="every step gathers %.0f MB of rows > 126 MB L2" % (pairs * 656 / 1e6)),
-            roofline=dict(bound="tensor", achieved=tf, peak=world * pk["bf16_tflops"], unit="TFLOP/s",
-                          frac=tf / (world * pk["bf16_tflops"]), traffic=None, peak_source=pk["source"],
-                          kernel="sparse_mla_kernel<fp8> + all-gather", flops_per_launch=flops / world,
-                          gathered_bytes_per_launch=pairs * 656.0),
-            gpu_launches=K * launches, clocks=sampler.summary())), flush=True)
+    ms_attn = env.timed(attn, steps, warmup, arg_sets[0])
+    ms_full = env.timed(attn_gather, steps, warmup, arg_sets[0]) if world > 1 else ms_attn
+    clocks = env.sampler.summary()
+    pk = peaks()
+    pairs_total = float(c["B"] * c["s_q"] * c["topk"])
+    flops_total = flops_of(pairs_total, c["H"])
+    # per GPU: tp keeps every GPU's gathered bytes and divides the flops; batch divides both
+    pairs_gpu = float(total_q * c["topk"])
+    roof = roofline_block(flops_of(pairs_gpu, Hl), pairs_gpu * 656.0, ms_attn, pk, "sparse_mla_kernel<fp8>")
+    block = dict(workload="cfg4_%s_decode_fp8_mtp_b%d_sq2_h128_topk2048_kv65536_paged64" % (mode, c["B"]), n_gpus=world,
+                 heads_per_gpu=Hl, sequences_per_gpu=nseq, shared_list_fraction=W["share_frac"],
+                 ms_per_step=ms_full, ms_per_step_without_gather=ms_attn, all_gather_ms=ms_full - ms_attn,
+                 all_gather_bytes_per_gpu=(out.numel() * 2 if world > 1 else 0),
+                 tflops=flops_total / (ms_full * 1e-3) / 1e12, tflops_without_gather=flops_total / (ms_attn * 1e-3) / 1e12,
+                 steps=steps, pairs=pairs_total, roofline=roof,
+                 sharding=("heads sharded %d per GPU, latent cache replicated" % Hl if mode == "tp" else
+                           "sequences sharded %d per GPU with their cache, all 128 heads" % nseq) + ", one NCCL all-gather of the outputs per step",
+                 l2="every step gathers %.0f MB of rows per GPU > 126 MB L2" % (pairs_gpu * 656 / 1e6),
+                 gpu_launches=steps * (2 if plan.info.num_partials > 0 else 1), clocks=clocks)
+    del W, plan, out, lse, gathered, arg_sets, step_in
+    env.free()
+    return block
 
 
-def e2e_leg(api, torch, W, plan, sm_scale, out, lse, K, barrier):
+# --------------------------------------------------------------------------- host-buffer leg of the headline
+def e2e_leg(env, W, plan, out, lse, K):
     """K steps through the host-buffer C-ABI call: pinned host q / index lists in, out / lse back,
     the caller synchronising on every step's result."""
+    api, torch = env.api, env.torch
     B, H = W["B"], W["H"]
     q_host = [q.cpu().pin_memory() for (q, _) in W["steps"]]
     i_host = [idx.cpu().pin_memory() for (_, idx) in W["steps"]]
@@ -336,21 +472,106 @@ def e2e_leg(api, torch, W, plan, sm_scale, out, lse, K, barrier):
     lse_host = torch.empty(B, H, dtype=torch.float32).pin_memory()
     q_dev = torch.empty_like(W["steps"][0][0])
     i_dev = torch.empty_like(W["steps"][0][1])
-    a_e2e = api.make_args(q_dev, W["cache"], i_dev, plan, sm_scale, out=out, lse=lse, block_table=W["block_table"],
+    a_e2e = api.make_args(q_dev, W["cache"], i_dev, plan, SM_SCALE, out=out, lse=lse, block_table=W["block_table"],
                           page_block_size=W["page"])
     for i in range(3):
         api.mla_decode_step_host(a_e2e, q_host[i % len(q_host)], i_host[i % len(i_host)], out_host, lse_host)
     g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
+    env.barrier()
     g0.record()
     for i in range(K):
         api.mla_decode_step_host(a_e2e, q_host[i % len(q_host)], i_host[i % len(i_host)], out_host, lse_host)
         torch.cuda.current_stream().synchronize()   # the caller reads the step's result before the next step
     g1.record()
-    barrier()
+    env.barrier()
     h2d = q_host[0].numel() * 2 + i_host[0].numel() * 4
     d2h = out_host.numel() * 2 + lse_host.numel() * 4
     return g0.elapsed_time(g1), h2d, d2h
+
+
+# --------------------------------------------------------------------------- headline (config 2)
+def headline_leg(env, args):
+    torch, api = env.torch, env.api
+    W = env.workloads.decode_fp8(B=CFG["B"], H=CFG["H"], kv_len=CFG["kv_len"], topk=CFG["topk"], page=CFG["page"],
+                                 pad_frac=CFG["pad_frac"], n_batches=CFG["n_batches"], seed=2026 + env.rank)
+    B, H, topk, n_valid = W["B"], W["H"], W["topk"], W["n_valid"]
+    pairs = B * n_valid
+    step_flops = flops_of(pairs, H)
+    plan = api.mla_decode_plan_create(B, H, topk, 1, valid_len_hint=[n_valid] * B)
+    out = torch.empty(B, H, D_V, dtype=torch.bfloat16, device="cuda")
+    lse = torch.empty(B, H, dtype=torch.float32, device="cuda")
+    arg_sets = [api.make_args(q, W["cache"], idx, plan, SM_SCALE, out=out, lse=lse, block_table=W["block_table"],
+                              page_block_size=W["page"]) for (q, idx) in W["steps"]]
+    L = env.L
+
+    def step(i):
+        a = arg_sets[i % len(arg_sets)]
+        rc = L.dsa_v32_decode_fp8(C.byref(a), env.stream())
+        if rc == 0:
+            rc = L.dsa_v32_combine(C.byref(a), env.stream())
+        if rc:
+            raise api.DsaError(rc, "decode step")
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    api._check(L.dsa_v32_device_status(C.byref(arg_sets[0]), env.stream()), "device status after warm-up")
+
+    K = args.steps
+    ev_a = [torch.cuda.Event(enable_timing=True) for _ in range(K)]
+    ev_b = [torch.cuda.Event(enable_timing=True) for _ in range(K)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    stream = env.stream()
+    env.barrier()
+    env.sampler.start()
+    e0.record()
+    for i in range(K):
+        a = arg_sets[i % len(arg_sets)]
+        ev_a[i].record()
+        rc = L.dsa_v32_decode_fp8(C.byref(a), stream)
+        ev_b[i].record()
+        rc = rc or L.dsa_v32_combine(C.byref(a), stream)
+        if rc:
+            raise api.DsaError(rc, "decode step")
+    e1.record()
+    env.barrier()
+    env.sampler.stop()
+    total_ms = e0.elapsed_time(e1)
+    attn_ms = sum(a.elapsed_time(b) for a, b in zip(ev_a, ev_b)) / K
+    api._check(L.dsa_v32_device_status(C.byref(arg_sets[0]), env.stream()), "device status after the timed region")
+    clocks = env.sampler.summary()
+
+    e2e_ms, h2d, d2h = float("nan"), 0, 0
+    if not args.no_e2e:
+        e2e_ms, h2d, d2h = e2e_leg(env, W, plan, out, lse, K)
+
+    t = torch.tensor([total_ms, attn_ms, e2e_ms], dtype=torch.float64, device="cuda")
+    if env.world > 1:
+        env.dist.all_reduce(t, op=env.dist.ReduceOp.MAX)
+    total_ms, attn_ms, e2e_ms = (float(x) for x in t.tolist())
+    world = env.world
+    pk = peaks()
+    ms_per_step = total_ms / K
+    value = world * step_flops / (ms_per_step * 1e-3) / 1e12
+    attn_tf = step_flops / (attn_ms * 1e-3) / 1e12
+    gathered = pairs * 656.0
+    line = dict(metric="sparse_mla_decode_fp8_tflops", value=value, unit="TFLOP/s", n_gpus=world, steps=K,
+                warmup=args.warmup, ms_per_step=ms_per_step, us_per_step=ms_per_step * 1e3, higher_is_better=True,
+                scaling="weak", vs_baseline=None, dtype="bf16 MMA, fp32 accumulate (fp8 e4m3 cache)", data="synthetic",
+                config=workload_config(),
+                roofline=dict(bound="tensor", achieved=attn_tf, peak=pk["bf16_tflops"], unit="TFLOP/s",
+                              frac=attn_tf / pk["bf16_tflops"], traffic=measured_traffic(B),
+                              peak_source=pk["source"], kernel="sparse_mla_kernel<fp8>", kernel_us=attn_ms * 1e3,
+                              flops_per_launch=step_flops, gathered_bytes_per_launch=gathered,
+                              gathered_gbs=gathered / (attn_ms * 1e-3) / 1e9, hbm_peak_gbs=pk["hbm_gbs"],
+                              t_flop_us=step_flops / (pk["bf16_tflops"] * 1e12) * 1e6,
+                              t_mem_us=gathered / (pk["hbm_gbs"] * 1e9) * 1e6),
+                e2e=None if args.no_e2e else dict(value=world * step_flops / (e2e_ms / K * 1e-3) / 1e12, unit="TFLOP/s",
+                                                  ms_per_step=e2e_ms / K, h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
+                gpu_launches=K * (2 if plan.info.num_partials > 0 else 1), clocks=clocks)
+    del W, plan, out, lse, arg_sets
+    env.free()
+    return line
 
 
 # --------------------------------------------------------------------------- GPU arm
@@ -362,11 +583,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the `prefill` block")
+    ap.add_argument("--no-sharded", action="store_true", help="skip the `sharded` block")
     ap.add_argument("--batch", type=int, default=CFG["B"], help="sequences per GPU (smaller only for profiler captures)")
-    ap.add_argument("--workload", default="decode_fp8", choices=["decode_fp8", "prefill_bf16", "decode_fp8_tp"],
-                    help="decode_fp8: the headline; prefill_bf16: one causal prefill (second half of the metric; --tokens 131072 "
-                         "with --gpus 8 is the query-chunk-sharded long prefill); decode_fp8_tp: MTP decode with the heads "
-                         "sharded over the GPUs and an all-gather of the outputs")
+    ap.add_argument("--workload", default="all", choices=["all", "decode_fp8", "prefill_bf16", "decode_fp8_tp", "decode_fp8_batch"],
+                    help="all: the headline with the prefill and sharded blocks; the others run one leg alone and print "
+                         "its block (profiler captures, quick checks)")
     ap.add_argument("--tokens", type=int, default=4096, help="prefill_bf16: sequence length")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -392,110 +614,45 @@ def main():
         if world > 1:
             dist.barrier()
     api.lib()
+    env = Env(rank, world, local_rank, torch, dist, api, workloads)
+    short = max(5, min(args.steps, 20))
+
     if args.workload == "prefill_bf16":
-        run_prefill(args, rank, world, local_rank, torch, dist, api, workloads)
-        if world > 1:
-            dist.destroy_process_group()
-        return
-    if args.workload == "decode_fp8_tp":
-        run_decode_tp(args, rank, world, local_rank, torch, dist, api, workloads)
-        if world > 1:
-            dist.destroy_process_group()
-        return
-
-    W = workloads.decode_fp8(B=CFG["B"], H=CFG["H"], kv_len=CFG["kv_len"], topk=CFG["topk"], page=CFG["page"],
-                             pad_frac=CFG["pad_frac"], n_batches=CFG["n_batches"], seed=2026 + rank)
-    B, H, topk, n_valid = W["B"], W["H"], W["topk"], W["n_valid"]
-    pairs = B * n_valid
-    step_flops = flops_of(pairs, H)
-    plan = api.mla_decode_plan_create(B, H, topk, 1, valid_len_hint=[n_valid] * B)
-    out = torch.empty(B, H, D_V, dtype=torch.bfloat16, device="cuda")
-    lse = torch.empty(B, H, dtype=torch.float32, device="cuda")
-    sm_scale = 1.0 / math.sqrt(192.0)
-    arg_sets = [api.make_args(q, W["cache"], idx, plan, sm_scale, out=out, lse=lse, block_table=W["block_table"],
-                              page_block_size=W["page"]) for (q, idx) in W["steps"]]
-    L = api.lib()
-    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
-
-    def step(i):
-        a = arg_sets[i % len(arg_sets)]
-        rc = L.dsa_v32_decode_fp8(C.byref(a), stream)
-        if rc == 0:
-            rc = L.dsa_v32_combine(C.byref(a), stream)
-        if rc:
-            raise api.DsaError(rc, "decode step")
-
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-
-    for i in range(args.warmup):
-        step(i)
-    torch.cuda.synchronize()
-    st = L.dsa_v32_device_status(C.byref(arg_sets[0]), stream)
-    if st:
-        raise api.DsaError(st, "device status after warm-up")
-
-    K = args.steps
-    ev_a = [torch.cuda.Event(enable_timing=True) for _ in range(K)]
-    ev_b = [torch.cuda.Event(enable_timing=True) for _ in range(K)]
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler = ClockSampler(local_rank)
-    barrier()
-    sampler.start()
-    e0.record()
-    for i in range(K):
-        a = arg_sets[i % len(arg_sets)]
-        ev_a[i].record()
-        rc = L.dsa_v32_decode_fp8(C.byref(a), stream)
-        ev_b[i].record()
-        rc = rc or L.dsa_v32_combine(C.byref(a), stream)
-        if rc:
-            raise api.DsaError(rc, "decode step")
-    e1.record()
-    barrier()
-    sampler.stop()
-    total_ms = e0.elapsed_time(e1)
-    attn_ms = sum(a.elapsed_time(b) for a, b in zip(ev_a, ev_b)) / K
-    st = L.dsa_v32_device_status(C.byref(arg_sets[0]), stream)
-    if st:
-        raise api.DsaError(st, "device status after the timed region")
-
-    e2e_ms, h2d, d2h = float("nan"), 0, 0
-    if not args.no_e2e:
-        e2e_ms, h2d, d2h = e2e_leg(api, torch, W, plan, sm_scale, out, lse, K, barrier)
-
-    t = torch.tensor([total_ms, attn_ms, e2e_ms], dtype=torch.float64, device="cuda")
+        block = prefill_leg(env, args.tokens, args.steps, args.warmup, "single")
+        if rank == 0:
+            print(json.dumps(dict(metric="sparse_mla_prefill_bf16_tflops", value=block["tflops"], unit="TFLOP/s", n_gpus=world,
+                                  steps=args.steps, warmup=args.warmup, ms_per_step=block["ms_per_step"], higher_is_better=True,
+                                  scaling="strong", vs_baseline=None, dtype="bf16 MMA, fp32 accumulate", data="synthetic",
+                                  config=dict(workload=block["workload"]), roofline=block["roofline"],
+                                  gpu_launches=block["gpu_launches"], clocks=block["clocks"])), flush=True)
+    elif args.workload in ("decode_fp8_tp", "decode_fp8_batch"):
+        block = cfg4_leg(env, "tp" if args.workload == "decode_fp8_tp" else "batch", short, args.warmup)
+        if rank == 0:
+            print(json.dumps(dict(metric="sparse_mla_decode_fp8_mtp_tflops", value=block["tflops"], unit="TFLOP/s", n_gpus=world,
+                                  steps=short, warmup=args.warmup, ms_per_step=block["ms_per_step"], higher_is_better=True,
+                                  scaling="strong", vs_baseline=None, dtype="bf16 MMA, fp32 accumulate (fp8 e4m3 cache)",
+                                  data="synthetic", config=dict(workload=block["workload"]), block=block,
+                                  gpu_launches=block["gpu_launches"], clocks=block["clocks"])), flush=True)
+    else:
+        line = headline_leg(env, args)
+        if args.workload == "all":
+            if world == 1 and not args.no_prefill:
+                pre = prefill_leg(env, 4096, short, args.warmup, "cfg3")
+                if not args.no_cpu_baseline:
+                    pre["cpu_baseline"] = cpu_baseline_prefill(4096, CFG["topk"], CFG["H"])
+                line["prefill"] = pre
+            if not args.no_sharded:
+                sharded = dict(note="strong scaling: the same total problem at every N; ms are device-timed, max over ranks")
+                sharded["cfg4_tp"] = cfg4_leg(env, "tp", short, args.warmup)
+                sharded["cfg4_batch"] = cfg4_leg(env, "batch", short, args.warmup)
+                sharded["cfg5"] = prefill_leg(env, CFG5_TOKENS, 3, 3, "cfg5")
+                line["sharded"] = sharded
+        if rank == 0:
+            if world == 1 and not args.no_cpu_baseline:
+                line["cpu_baseline"] = cpu_baseline_block()
+            print(json.dumps(line), flush=True)
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, attn_ms, e2e_ms = (float(x) for x in t.tolist())
-    clocks = sampler.summary()
-    if rank == 0:
-        pk = peaks()
-        ms_per_step = total_ms / K
-        value = world * step_flops / (ms_per_step * 1e-3) / 1e12
-        attn_tf = step_flops / (attn_ms * 1e-3) / 1e12
-        gathered = pairs * 656.0
-        line = dict(metric="sparse_mla_decode_fp8_tflops", value=value, unit="TFLOP/s", n_gpus=world, steps=K,
-                    warmup=args.warmup, ms_per_step=ms_per_step, us_per_step=ms_per_step * 1e3, higher_is_better=True,
-                    scaling="weak", vs_baseline=None, dtype="bf16 MMA, fp32 accumulate (fp8 e4m3 cache)", data="synthetic",
-                    config=workload_config(),
-                    roofline=dict(bound="tensor", achieved=attn_tf, peak=pk["bf16_tflops"], unit="TFLOP/s",
-                                  frac=attn_tf / pk["bf16_tflops"], traffic=NCU_TRAFFIC_BYTES_AT_BATCH16 * B / 16.0,
-                                  peak_source=pk["source"], kernel="sparse_mla_kernel<fp8>", kernel_us=attn_ms * 1e3,
-                                  flops_per_launch=step_flops, gathered_bytes_per_launch=gathered,
-                                  gathered_gbs=gathered / (attn_ms * 1e-3) / 1e9, hbm_peak_gbs=pk["hbm_gbs"],
-                                  t_flop_us=step_flops / (pk["bf16_tflops"] * 1e12) * 1e6,
-                                  t_mem_us=gathered / (pk["hbm_gbs"] * 1e9) * 1e6),
-                    e2e=None if args.no_e2e else dict(value=world * step_flops / (e2e_ms / K * 1e-3) / 1e12, unit="TFLOP/s",
-                                                      ms_per_step=e2e_ms / K, h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
-                    gpu_launches=K * (2 if plan.info.num_partials > 0 else 1), clocks=clocks)
-        if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline_block()
-        print(json.dumps(line), flush=True)
-    if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 

@@ -71,6 +71,13 @@ typedef struct dsa_v32_work_info {
     int32_t _pad[2];
 } dsa_v32_work_info;
 
+/*
+ * Planner flag: limit the number of work lists a small problem is cut into, as the reference's metadata
+ * kernel does with auto_split (common/get_mla_metadata.hpp:8-13): at most
+ * round(1.2 * sqrt(total cost in tile steps * lists available)) lists are used.
+ */
+#define DSA_V32_PLAN_AUTO_SPLIT 1
+
 /* Problem shape the planner needs (no data pointers). */
 typedef struct dsa_v32_shape {
     int32_t total_q;   /* number of query rows = batches * s_q */
@@ -78,7 +85,7 @@ typedef struct dsa_v32_shape {
     int32_t topk;      /* slots per query row */
     int32_t s_q;       /* query rows per sequence (1 = plain decode, 2 = one MTP token, ...) */
     int32_t num_sms;   /* 0 = ask the device */
-    int32_t _pad;
+    int32_t flags;     /* DSA_V32_PLAN_* bits, 0 = defaults */
     const int32_t* valid_len_hint; /* optional host array [total_q]: slots >= this are known to be -1 */
 } dsa_v32_shape;
 
@@ -227,6 +234,16 @@ void* dsa_v32_static_scratch_address(void);
  * 0, or DSA_V32_ERR_DEVICE_WAIT when a bounded wait inside a kernel ran out.
  */
 int dsa_v32_device_status(const dsa_v32_attn_args* args, void* stream);
+
+/*
+ * Self-test of the bounded device-side wait: launches one warp that waits, for `budget_us` microseconds
+ * (1 .. 1000000), on an initialised barrier nothing arrives at.  The wait must run out, the kernel must
+ * record DSA_V32_ERR_DEVICE_WAIT in the status word of `workspace` (any planned workspace) and exit
+ * normally; result_dev[0] = 1 when the wait gave up, result_dev[1] = the abort flag it raised.  Afterwards
+ * dsa_v32_device_status reports and clears the code.  Nothing traps and nothing is left waiting, so the
+ * context stays usable.  No counterpart in the reference, whose kernels wait without a bound.
+ */
+int dsa_v32_selftest_wait_expiry(void* workspace, int32_t* result_dev, int64_t budget_us, void* stream);
 
 /*
  * Debug entry point for index parity: writes, for every (query row, slot), the physical KV row

@@ -28,7 +28,7 @@ class WorkInfo(C.Structure):
 
 class Shape(C.Structure):
     _fields_ = [("total_q", C.c_int32), ("H", C.c_int32), ("topk", C.c_int32), ("s_q", C.c_int32),
-                ("num_sms", C.c_int32), ("_pad", C.c_int32), ("valid_len_hint", C.c_void_p)]
+                ("num_sms", C.c_int32), ("flags", C.c_int32), ("valid_len_hint", C.c_void_p)]
 
 
 class PlanInfo(C.Structure):
@@ -55,7 +55,7 @@ EXPORTS = ["dsa_v32_abi_version", "dsa_v32_error_string", "dsa_v32_plan_info_get
            "dsa_v32_plan_host", "dsa_v32_plan_read", "dsa_v32_plan_release", "dsa_v32_decode_bf16", "dsa_v32_decode_fp8",
            "dsa_v32_prefill_bf16", "dsa_v32_combine", "dsa_v32_decode_pipeline", "dsa_v32_device_status",
            "dsa_v32_debug_rows", "dsa_v32_pack_fp8_rows", "dsa_v32_decode_pipeline_host",
-           "dsa_v32_decode_pipeline_static", "dsa_v32_static_scratch_address"]
+           "dsa_v32_decode_pipeline_static", "dsa_v32_static_scratch_address", "dsa_v32_selftest_wait_expiry"]
 
 _lib = None
 
@@ -82,6 +82,7 @@ def lib():
         L.dsa_v32_plan_host.argtypes = [C.POINTER(Shape), C.c_void_p, C.c_int64, C.POINTER(C.c_int64)]
         L.dsa_v32_plan_read.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]
         L.dsa_v32_plan_release.argtypes = [C.c_void_p]
+        L.dsa_v32_selftest_wait_expiry.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]
         for name in ("dsa_v32_decode_bf16", "dsa_v32_decode_fp8", "dsa_v32_prefill_bf16", "dsa_v32_combine",
                      "dsa_v32_device_status"):
             getattr(L, name).argtypes = [C.POINTER(AttnArgs), C.c_void_p]
@@ -127,8 +128,11 @@ class MlaDecodePlan:
         return list(works), list(indptr)
 
 
-def _shape(total_q, H, topk, s_q, num_sms, hint):
-    sh = Shape(total_q, H, topk, s_q, num_sms, 0, None)
+PLAN_AUTO_SPLIT = 1
+
+
+def _shape(total_q, H, topk, s_q, num_sms, hint, flags=0):
+    sh = Shape(total_q, H, topk, s_q, num_sms, flags, None)
     keep = None
     if hint is not None:
         keep = (C.c_int32 * total_q)(*[int(x) for x in hint])
@@ -136,9 +140,10 @@ def _shape(total_q, H, topk, s_q, num_sms, hint):
     return sh, keep
 
 
-def mla_decode_plan_create(total_q, H, topk, s_q=1, *, device="cuda", valid_len_hint=None, num_sms=0):
-    """Sizes the workspace, allocates it (torch owns it) and runs the metadata stage once."""
-    sh, keep = _shape(total_q, H, topk, s_q, num_sms, valid_len_hint)
+def mla_decode_plan_create(total_q, H, topk, s_q=1, *, device="cuda", valid_len_hint=None, num_sms=0, auto_split=False):
+    """Sizes the workspace, allocates it (torch owns it) and runs the metadata stage once.
+    auto_split: the reference scheduler's option of the same name (fewer work lists for small problems)."""
+    sh, keep = _shape(total_q, H, topk, s_q, num_sms, valid_len_hint, PLAN_AUTO_SPLIT if auto_split else 0)
     info = PlanInfo()
     _check(lib().dsa_v32_plan_info_get(C.byref(sh), C.byref(info)), "dsa_v32_plan_info_get")
     ws = torch.empty(int(info.workspace_bytes) + 256, dtype=torch.uint8, device=device)
@@ -148,9 +153,9 @@ def mla_decode_plan_create(total_q, H, topk, s_q=1, *, device="cuda", valid_len_
     return MlaDecodePlan(total_q, H, topk, s_q, info, ws, keep)
 
 
-def plan_host(total_q, H, topk, s_q=1, *, num_sms=148, valid_len_hint=None):
+def plan_host(total_q, H, topk, s_q=1, *, num_sms=148, valid_len_hint=None, auto_split=False):
     """Runs the planner on the host only and returns the raw metadata blob (bytes) - no GPU needed."""
-    sh, keep = _shape(total_q, H, topk, s_q, num_sms, valid_len_hint)
+    sh, keep = _shape(total_q, H, topk, s_q, num_sms, valid_len_hint, PLAN_AUTO_SPLIT if auto_split else 0)
     need = C.c_int64(0)
     _check(lib().dsa_v32_plan_host(C.byref(sh), None, 0, C.byref(need)), "dsa_v32_plan_host")
     buf = (C.c_uint8 * need.value)()

@@ -19,6 +19,7 @@ cudaError_t launch_combine(const float* o_accum, const float* lse_accum, const i
                            const int32_t* reduce_slots, const ReduceDst* reduce_dst, int num_reduce_rows, void* out, float* lse,
                            int64_t stride_o_row, int64_t stride_o_head, int H, cudaStream_t stream);
 cudaError_t launch_debug_rows(const AttnParams& p, int total_q, int32_t* rows_out, cudaStream_t stream);
+cudaError_t launch_wait_selftest(int32_t* status, int32_t* result, unsigned long long budget_ns, cudaStream_t stream);
 cudaError_t launch_pack_fp8(const float* latent, const void* rope, const int64_t* dst_rows, void* out, int64_t num_rows,
                             cudaStream_t stream);
 
@@ -511,6 +512,14 @@ int dsa_v32_device_status(const dsa_v32_attn_args* a, void* stream) {
         if (e != cudaSuccess) return (int)e;
     }
     return v;
+}
+
+int dsa_v32_selftest_wait_expiry(void* workspace, int32_t* result_dev, int64_t budget_us, void* stream) {
+    if (!workspace || !result_dev) return DSA_V32_ERR_NULL;
+    if (budget_us <= 0 || budget_us > 1000000) return DSA_V32_ERR_SHAPE;   // at most a second
+    int32_t* status = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(workspace) + offsetof(WorkspaceHeader, status));
+    cudaError_t e = launch_wait_selftest(status, result_dev, (unsigned long long)budget_us * 1000ull, (cudaStream_t)stream);
+    return e == cudaSuccess ? DSA_V32_OK : (int)e;
 }
 
 int dsa_v32_debug_rows(const dsa_v32_attn_args* a, int32_t* rows_out, void* stream) {

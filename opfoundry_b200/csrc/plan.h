@@ -13,6 +13,7 @@
 // index values, so it is computed on the host and uploaded once per shape.
 #pragma once
 #include <algorithm>
+#include <cmath>
 #include <cstring>
 #include <vector>
 #include "defs.h"
@@ -136,7 +137,14 @@ inline int build_plan_split(const dsa_v32_shape& sh, int num_sms, HostPlan& P) {
 
     // With little work only as many lists are used as can each get a minimum-length piece; the rest
     // stay empty (their CTA pairs exit at once).
-    const int L_used = int(std::max<int64_t>(1, std::min<int64_t>(L, tiles_left / kMinPieceTiles)));
+    int L_used = int(std::max<int64_t>(1, std::min<int64_t>(L, tiles_left / kMinPieceTiles)));
+    if (sh.flags & DSA_V32_PLAN_AUTO_SPLIT) {
+        // the reference's effective_splits (get_mla_metadata.hpp:8-13) with its coefficient 1.2 (defs.h:62):
+        // the cost it takes the root of is "blocks + overhead" summed over the units
+        const double work = double(std::max<int64_t>(1, tiles_left + n_units * kPieceOverheadTiles)) * double(L);
+        const long eff = std::lrint(1.2 * std::sqrt(work));
+        L_used = int(std::max<long>(1, std::min<long>(eff, L_used)));
+    }
     for (int list = 0; list < L; ++list) {
         if (list >= L_used) {
             P.list_indptr[list + 1] = int(P.works.size());

@@ -84,16 +84,19 @@ __device__ __forceinline__ uint64_t global_ns() {
 #ifndef DSA_WAIT_BUDGET_NS
 #define DSA_WAIT_BUDGET_NS 2000000000ull
 #endif
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_budget(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint64_t budget_ns) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_ns();
     for (uint32_t it = 0; it < DSA_WAIT_LIMIT; ++it) {
         if (mbar_try_wait_hint(bar, parity, DSA_WAIT_HINT_NS)) return true;
         if (*abort_flag) return false;
-        if (global_ns() - t0 > DSA_WAIT_BUDGET_NS) break;
+        if (global_ns() - t0 > budget_ns) break;
     }
     *abort_flag = 1;
     return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    return mbar_wait_budget(bar, parity, abort_flag, DSA_WAIT_BUDGET_NS);
 }
 
 // Warp-uniform forms for warps that run converged code (shuffles, tcgen05.ld/st) after a wait:

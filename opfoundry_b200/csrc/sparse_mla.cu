@@ -1293,6 +1293,29 @@ __global__ void __launch_bounds__(256) pack_fp8_rows_kernel(const float* __restr
     reinterpret_cast<uint32_t*>(row + kDV + 16)[lane] = reinterpret_cast<const uint32_t*>(rope + r * kDRope)[lane];
 }
 
+// ------------------------------------------------------------------ self-test of the bounded wait
+// One warp waits, with a short budget, on an initialised barrier that nothing ever arrives at: the wait
+// must give up, raise the CTA's abort flag and record DSA_V32_ERR_DEVICE_WAIT in the status word - the
+// path every wait of the attention kernel takes when its peer never answers - and the kernel must exit
+// normally.  result[0] = 1 when the wait returned false, result[1] = the abort flag it left.
+__global__ void __launch_bounds__(32) wait_expiry_selftest_kernel(int32_t* status, int32_t* result, unsigned long long budget_ns) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        fence_mbar_init();
+    }
+    __syncwarp();
+    const bool ok = __all_sync(0xffffffffu, mbar_wait_budget(smem_u32(&bar), 0, &abort_flag, budget_ns));
+    __syncwarp();
+    if (threadIdx.x == 0) {
+        if (abort_flag) atomicExch(status, DSA_V32_ERR_DEVICE_WAIT);
+        result[0] = ok ? 0 : 1;
+        result[1] = abort_flag;
+    }
+}
+
 // ------------------------------------------------------------------ launch helpers (called from capi.cu)
 // The opt-in for more than 48 KB of dynamic shared memory is a per-device attribute of the kernel: it is
 // set once for every device this process launches on (the current device at the time of the call).
@@ -1365,6 +1388,11 @@ cudaError_t launch_combine(const float* o_accum, const float* lse_accum, const i
     dim3 grid(num_reduce_rows, kHeadsPerBlock / 8);
     combine_kernel<<<grid, 256, 0, stream>>>(o_accum, lse_accum, reduce_indptr, reduce_slots, reduce_dst, out, lse,
                                              stride_o_row, stride_o_head, H);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_wait_selftest(int32_t* status, int32_t* result, unsigned long long budget_ns, cudaStream_t stream) {
+    wait_expiry_selftest_kernel<<<1, 32, 0, stream>>>(status, result, budget_ns);
     return cudaGetLastError();
 }
 

@@ -223,3 +223,24 @@ def test_repeated_launches_are_deterministic(oracle):
     a_out, a_lse, _ = run_gpu(case, SCALE)
     b_out, b_lse, _ = run_gpu(case, SCALE)
     assert np.array_equal(a_out, b_out) and np.array_equal(a_lse, b_lse)
+
+
+def test_bounded_wait_expires_and_reports(built_lib):
+    """A device-side wait that nothing satisfies runs out after its budget, the kernel exits normally,
+    the status word carries the code once, and the context keeps working."""
+    import ctypes as C
+    plan = api.mla_decode_plan_create(2, 16, 64, 1)
+    result = torch.zeros(2, dtype=torch.int32, device="cuda")
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert built_lib.dsa_v32_selftest_wait_expiry(plan.workspace.data_ptr(), result.data_ptr(), 200, st) == 0
+    a = api.AttnArgs()
+    a.workspace = plan.workspace.data_ptr()
+    assert built_lib.dsa_v32_device_status(C.byref(a), st) == 1001      # DSA_V32_ERR_DEVICE_WAIT, read and cleared
+    assert result.cpu().tolist() == [1, 1]                              # the wait returned false and raised the abort flag
+    assert built_lib.dsa_v32_device_status(C.byref(a), st) == 0
+    assert built_lib.dsa_v32_selftest_wait_expiry(plan.workspace.data_ptr(), result.data_ptr(), 0, st) == -2
+    # the context is intact: a normal launch on the same workspace still gives the right answer
+    from gpu_util import run_gpu
+    case = synth.make_decode_case(2, 16, 256, 64, fp8=False, seed=3)
+    out, lse, _ = run_gpu(case, SCALE)
+    assert np.all(np.isfinite(lse))

@@ -26,10 +26,10 @@ def parse(blob):
     return h, indptr, works, r_indptr, r_slots, r_dst
 
 
-def check_plan(total_q, H, topk, s_q=1, num_sms=148, hint=None):
+def check_plan(total_q, H, topk, s_q=1, num_sms=148, hint=None, auto_split=False):
     built = pytest.importorskip("opfoundry_b200.build")
     built.build()
-    blob = api.plan_host(total_q, H, topk, s_q, num_sms=num_sms, valid_len_hint=hint)
+    blob = api.plan_host(total_q, H, topk, s_q, num_sms=num_sms, valid_len_hint=hint, auto_split=auto_split)
     h, indptr, works, r_indptr, r_slots, r_dst = parse(blob)
     assert h["magic"] == 0x44534133 and h["num_lists"] == num_sms // 2
     assert indptr[0] == 0 and indptr[-1] == h["num_works"] and np.all(np.diff(indptr) >= 0)
@@ -104,3 +104,40 @@ def test_bad_shapes_rejected():
         with pytest.raises(api.DsaError) as e:
             api.plan_host(*args)
         assert e.value.status == -2
+
+
+def _used_lists(blob):
+    h, indptr, *_ = parse(blob)
+    return int((np.diff(indptr) > 0).sum())
+
+
+def test_varlen_and_auto_split_cover_exactly():
+    """Scheduler parity with the reference's metadata kernel in the sense that matters (integer-exact
+    coverage, not identical cuts): variable per-sequence lengths as its --varlen harness draws them
+    (common/host.cc:239-261: uniform in [min(5, s), s]) and its auto_split option
+    (common/get_mla_metadata.hpp:8-13) both leave every slot covered exactly once."""
+    rng = np.random.RandomState(1234)
+    for (B, s_q, topk, s) in [(3, 1, 2048, 4096), (16, 2, 2048, 1500), (64, 1, 512, 300), (5, 2, 96, 40)]:
+        lens = rng.randint(min(5, s), s + 1, size=B)
+        hint = np.repeat(np.minimum(lens, topk), s_q).astype(np.int32)
+        check_plan(B * s_q, 128, topk, s_q, hint=hint)
+        check_plan(B * s_q, 128, topk, s_q, hint=hint, auto_split=True)
+        check_plan(B * s_q, 16, topk, s_q, num_sms=20, hint=hint, auto_split=True)
+
+
+def test_auto_split_limits_the_lists_of_a_small_problem():
+    """effective lists = min(lists, round(1.2 * sqrt(cost * lists))), cost in tile steps + per-unit overhead."""
+    # 2 queries of 8 tiles each: cost = 16 + 2 * 6 = 28 steps, 74 lists -> round(1.2 * sqrt(28 * 74)) = 55 > 16 / 4 = 4 pieces
+    assert _used_lists(api.plan_host(2, 128, 256, 1, auto_split=True)) <= 4
+    # one query of 64 tiles: without the option it is cut into 16 pieces; with it into at most round(1.2 * sqrt(70 * 4)) = 20 -> unchanged,
+    # and on a 4-list device round(1.2 * sqrt(70 * 2)) = 14 -> at most 2
+    a = _used_lists(api.plan_host(1, 128, 2048, 1, num_sms=148))
+    b = _used_lists(api.plan_host(1, 128, 2048, 1, num_sms=148, auto_split=True))
+    assert b <= a
+    # a tiny problem on many lists: one tile step of work -> one list
+    assert _used_lists(api.plan_host(1, 16, 32, 1, auto_split=True)) == 1
+    import math
+    for (q, topk) in [(1, 64), (2, 128), (4, 2048)]:
+        tiles = q * ((topk + 31) // 32)
+        eff = max(1, min(74, int(round(1.2 * math.sqrt((tiles + q * 6) * 74)))))
+        assert _used_lists(api.plan_host(q, 128, topk, 1, auto_split=True)) <= eff

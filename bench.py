@@ -399,6 +399,7 @@ def cfg4_problem(env, seq_begin, seq_end, n_batches=2):
         steps.append((q, idx.view(n * c["s_q"], c["topk"]).contiguous()))
     W["steps"] = steps
     W["share_frac"] = float(share.float().mean().item()) if n else 0.0
+    W["mtp_shared"] = [bool(x) for x in share.cpu().tolist()]
     return W
 
 
@@ -421,7 +422,8 @@ def cfg4_leg(env, mode, steps, warmup):
     W = cfg4_problem(env, s0, s1)
     total_q = nseq * c["s_q"]
     step_in = [(q[:, h0:h1].contiguous(), idx) for q, idx in W["steps"]]
-    plan = api.mla_decode_plan_create(total_q, Hl, c["topk"], c["s_q"])
+    # rows of a sequence that share a list are gathered once when both fit one 128-row tile (128 / N heads <= 64)
+    plan = api.mla_decode_plan_create(total_q, Hl, c["topk"], c["s_q"], mtp_shared=W["mtp_shared"])
     out = torch.empty(total_q, Hl, D_V, dtype=torch.bfloat16, device="cuda")
     lse = torch.empty(total_q, Hl, dtype=torch.float32, device="cuda")
     gathered = torch.empty(world, total_q, Hl, D_V, dtype=torch.bfloat16, device="cuda") if world > 1 else None

@@ -68,7 +68,9 @@ typedef struct dsa_v32_work_info {
     int32_t k_end;
     int32_t head_block;
     int32_t reduce_row; /* index into the reduce tables, -1 when not split */
-    int32_t _pad[2];
+    int32_t stacked_rows; /* > 1: the item carries this many consecutive query rows of one sequence that share
+                             one index list (MTP), stacked along the heads: tile row r = query q_row + r / H, head r % H */
+    int32_t _pad;
 } dsa_v32_work_info;
 
 /*
@@ -87,6 +89,10 @@ typedef struct dsa_v32_shape {
     int32_t num_sms;   /* 0 = ask the device */
     int32_t flags;     /* DSA_V32_PLAN_* bits, 0 = defaults */
     const int32_t* valid_len_hint; /* optional host array [total_q]: slots >= this are known to be -1 */
+    const uint8_t* mtp_shared;     /* optional host array [total_q / s_q]: non-zero = the s_q query rows of the sequence
+                                      carry the same index list; when s_q * H <= 128 (and H is a multiple of 8) they are
+                                      planned as one item that gathers the rows once (the reference packs the s_q tokens
+                                      of a batch into one qo tile the same way: common/defs.h:186-190) */
 } dsa_v32_shape;
 
 /* What dsa_v32_plan_info reports; all byte counts refer to the caller's workspace. */

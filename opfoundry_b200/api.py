@@ -23,12 +23,12 @@ STATIC_SCRATCH_BYTES = 48 << 20
 
 class WorkInfo(C.Structure):
     _fields_ = [("q_row", C.c_int32), ("partial_slot", C.c_int32), ("k_begin", C.c_int32), ("k_end", C.c_int32),
-                ("head_block", C.c_int32), ("reduce_row", C.c_int32), ("_pad", C.c_int32 * 2)]
+                ("head_block", C.c_int32), ("reduce_row", C.c_int32), ("stacked_rows", C.c_int32), ("_pad", C.c_int32)]
 
 
 class Shape(C.Structure):
     _fields_ = [("total_q", C.c_int32), ("H", C.c_int32), ("topk", C.c_int32), ("s_q", C.c_int32),
-                ("num_sms", C.c_int32), ("flags", C.c_int32), ("valid_len_hint", C.c_void_p)]
+                ("num_sms", C.c_int32), ("flags", C.c_int32), ("valid_len_hint", C.c_void_p), ("mtp_shared", C.c_void_p)]
 
 
 class PlanInfo(C.Structure):
@@ -131,19 +131,27 @@ class MlaDecodePlan:
 PLAN_AUTO_SPLIT = 1
 
 
-def _shape(total_q, H, topk, s_q, num_sms, hint, flags=0):
-    sh = Shape(total_q, H, topk, s_q, num_sms, flags, None)
-    keep = None
+def _shape(total_q, H, topk, s_q, num_sms, hint, flags=0, mtp_shared=None):
+    sh = Shape(total_q, H, topk, s_q, num_sms, flags, None, None)
+    keep = []
     if hint is not None:
-        keep = (C.c_int32 * total_q)(*[int(x) for x in hint])
-        sh.valid_len_hint = C.cast(keep, C.c_void_p)
+        k = (C.c_int32 * total_q)(*[int(x) for x in hint])
+        sh.valid_len_hint = C.cast(k, C.c_void_p)
+        keep.append(k)
+    if mtp_shared is not None:
+        k = (C.c_uint8 * (total_q // s_q))(*[1 if x else 0 for x in mtp_shared])
+        sh.mtp_shared = C.cast(k, C.c_void_p)
+        keep.append(k)
     return sh, keep
 
 
-def mla_decode_plan_create(total_q, H, topk, s_q=1, *, device="cuda", valid_len_hint=None, num_sms=0, auto_split=False):
+def mla_decode_plan_create(total_q, H, topk, s_q=1, *, device="cuda", valid_len_hint=None, num_sms=0, auto_split=False,
+                           mtp_shared=None):
     """Sizes the workspace, allocates it (torch owns it) and runs the metadata stage once.
-    auto_split: the reference scheduler's option of the same name (fewer work lists for small problems)."""
-    sh, keep = _shape(total_q, H, topk, s_q, num_sms, valid_len_hint, PLAN_AUTO_SPLIT if auto_split else 0)
+    auto_split: the reference scheduler's option of the same name (fewer work lists for small problems).
+    mtp_shared: per sequence, whether its s_q query rows carry the same index list (then, when s_q * H <= 128,
+    they are planned as one item that gathers the rows once)."""
+    sh, keep = _shape(total_q, H, topk, s_q, num_sms, valid_len_hint, PLAN_AUTO_SPLIT if auto_split else 0, mtp_shared)
     info = PlanInfo()
     _check(lib().dsa_v32_plan_info_get(C.byref(sh), C.byref(info)), "dsa_v32_plan_info_get")
     ws = torch.empty(int(info.workspace_bytes) + 256, dtype=torch.uint8, device=device)
@@ -153,9 +161,9 @@ def mla_decode_plan_create(total_q, H, topk, s_q=1, *, device="cuda", valid_len_
     return MlaDecodePlan(total_q, H, topk, s_q, info, ws, keep)
 
 
-def plan_host(total_q, H, topk, s_q=1, *, num_sms=148, valid_len_hint=None, auto_split=False):
+def plan_host(total_q, H, topk, s_q=1, *, num_sms=148, valid_len_hint=None, auto_split=False, mtp_shared=None):
     """Runs the planner on the host only and returns the raw metadata blob (bytes) - no GPU needed."""
-    sh, keep = _shape(total_q, H, topk, s_q, num_sms, valid_len_hint, PLAN_AUTO_SPLIT if auto_split else 0)
+    sh, keep = _shape(total_q, H, topk, s_q, num_sms, valid_len_hint, PLAN_AUTO_SPLIT if auto_split else 0, mtp_shared)
     need = C.c_int64(0)
     _check(lib().dsa_v32_plan_host(C.byref(sh), None, 0, C.byref(need)), "dsa_v32_plan_host")
     buf = (C.c_uint8 * need.value)()

@@ -224,7 +224,7 @@ int launch_attention(const dsa_v32_attn_args* a, int want_dtype, cudaStream_t st
         {   // Q: the 64 rope columns of a head block, 128-byte swizzle (the latent columns go to TMEM by plain loads)
             const uint64_t dims[3] = {uint64_t(kDQK), uint64_t(a->H), uint64_t(a->total_q)};
             const uint64_t str[2] = {uint64_t(a->stride_q_head) * 2, uint64_t(a->stride_q_row) * 2};
-            const uint32_t box[3] = {64, uint32_t(kHeadsPerBlock), 1};
+            const uint32_t box[3] = {64, uint32_t(a->H < kHeadsPerBlock ? a->H : kHeadsPerBlock), 1};
             if (tmap_cache().get(&tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a->q, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
                 return DSA_V32_ERR_DRIVER;
         }

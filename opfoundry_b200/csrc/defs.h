@@ -31,7 +31,7 @@ static_assert(sizeof(WorkspaceHeader) <= 256, "header must fit its slot");
 // Where a merged row goes: query row and head block of a split unit.
 struct ReduceDst {
     int32_t q_row;
-    int32_t head_block;
+    int32_t head_block;   // >= 0: head block; < 0: minus the number of stacked query rows of the unit (head block 0)
 };
 
 // Kernel parameters (passed by value next to the tensor maps).

@@ -34,6 +34,29 @@ struct HostPlan {
 
 inline int64_t align256(int64_t x) { return (x + 255) & ~int64_t(255); }
 
+// One unit of work = one (query row, head block), or one sequence whose s_q query rows share an index
+// list and fit one 128-row tile together (stacked along the heads).
+struct PlanUnit {
+    int32_t q_row, head_block, stacked_rows, len;
+};
+inline void enumerate_units(const dsa_v32_shape& sh, std::vector<PlanUnit>& units) {
+    const int n_hb = (sh.H + kHeadsPerBlock - 1) / kHeadsPerBlock;
+    const bool can_stack = sh.mtp_shared != nullptr && sh.s_q > 1 && sh.s_q * sh.H <= kHeadsPerBlock && sh.H % 8 == 0;
+    auto row_len = [&](int q) { return sh.valid_len_hint ? std::max(0, std::min(sh.topk, sh.valid_len_hint[q])) : sh.topk; };
+    units.clear();
+    for (int seq = 0; seq < sh.total_q / sh.s_q; ++seq) {
+        const int q0 = seq * sh.s_q;
+        if (can_stack && sh.mtp_shared[seq]) {
+            int len = 0;
+            for (int t = 0; t < sh.s_q; ++t) len = std::max(len, row_len(q0 + t));
+            units.push_back(PlanUnit{q0, 0, sh.s_q, len});
+            continue;
+        }
+        for (int t = 0; t < sh.s_q; ++t)
+            for (int hb = 0; hb < n_hb; ++hb) units.push_back(PlanUnit{q0 + t, hb, 1, row_len(q0 + t)});
+    }
+}
+
 // Header and byte offsets of a plan whose tables are filled in.
 inline void finish_plan(const dsa_v32_shape& sh, int L, int n_hb, int next_slot, HostPlan& P) {
     WorkspaceHeader& h = P.hdr;
@@ -73,14 +96,11 @@ inline int build_plan_split(const dsa_v32_shape& sh, int num_sms, HostPlan& P) {
     if (num_sms < 2) return DSA_V32_ERR_SHAPE;
     const int L = num_sms / 2;
     const int n_hb = (sh.H + kHeadsPerBlock - 1) / kHeadsPerBlock;
-    const int64_t n_units = int64_t(sh.total_q) * n_hb;
+    std::vector<PlanUnit> units;
+    enumerate_units(sh, units);
+    const int64_t n_units = int64_t(units.size());
 
-    auto unit_len = [&](int64_t u) -> int {
-        const int q = int(u / n_hb);
-        int len = sh.topk;
-        if (sh.valid_len_hint) len = std::max(0, std::min(sh.topk, sh.valid_len_hint[q]));
-        return len;
-    };
+    auto unit_len = [&](int64_t u) -> int { return units[size_t(u)].len; };
     auto unit_tiles = [&](int64_t u) -> int { return std::max(1, (unit_len(u) + kTileRows - 1) / kTileRows); };
 
     // Cost of a piece = its tile steps + a fixed overhead.  Every list is given an equal share of
@@ -102,12 +122,13 @@ inline int build_plan_split(const dsa_v32_shape& sh, int num_sms, HostPlan& P) {
     std::vector<int> open_piece_ids;  // work indices of the pieces of the unit being split
 
     auto emit = [&](int tile_begin, int tile_end, bool last_piece) {
-        const int q = int(u / n_hb), hb = int(u % n_hb);
+        const int q = units[size_t(u)].q_row, hb = units[size_t(u)].head_block;
         const int len = std::max(unit_len(u), 1);
         dsa_v32_work_info w;
         std::memset(&w, 0, sizeof(w));
         w.q_row = q;
         w.head_block = hb;
+        w.stacked_rows = units[size_t(u)].stacked_rows;
         w.k_begin = tile_begin * kTileRows;
         w.k_end = last_piece ? std::min(std::max(len, w.k_begin + 1), sh.topk) : tile_end * kTileRows;
         w.partial_slot = -1;
@@ -124,7 +145,7 @@ inline int build_plan_split(const dsa_v32_shape& sh, int num_sms, HostPlan& P) {
                     P.reduce_slots.push_back(next_slot++);
                 }
                 P.reduce_indptr.push_back(int(P.reduce_slots.size()));
-                P.reduce_dst.push_back(ReduceDst{q, hb});
+                P.reduce_dst.push_back(ReduceDst{q, units[size_t(u)].stacked_rows > 1 ? -units[size_t(u)].stacked_rows : hb});
             }
             open_piece_ids.clear();
             pieces_of_unit = 0;
@@ -209,12 +230,10 @@ inline int build_plan_whole(const dsa_v32_shape& sh, int num_sms, HostPlan& P) {
     if (num_sms < 2) return DSA_V32_ERR_SHAPE;
     const int L = num_sms / 2;
     const int n_hb = (sh.H + kHeadsPerBlock - 1) / kHeadsPerBlock;
-    const int64_t n_units = int64_t(sh.total_q) * n_hb;
-    auto unit_len = [&](int64_t u) -> int {
-        int len = sh.topk;
-        if (sh.valid_len_hint) len = std::max(0, std::min(sh.topk, sh.valid_len_hint[u / n_hb]));
-        return len;
-    };
+    std::vector<PlanUnit> units;
+    enumerate_units(sh, units);
+    const int64_t n_units = int64_t(units.size());
+    auto unit_len = [&](int64_t u) -> int { return units[size_t(u)].len; };
     std::vector<int64_t> order(n_units);
     for (int64_t u = 0; u < n_units; ++u) order[u] = u;
     std::stable_sort(order.begin(), order.end(), [&](int64_t a, int64_t b) { return unit_len(a) > unit_len(b); });
@@ -231,8 +250,9 @@ inline int build_plan_whole(const dsa_v32_shape& sh, int num_sms, HostPlan& P) {
         auto& top = heap.back();
         dsa_v32_work_info w;
         std::memset(&w, 0, sizeof(w));
-        w.q_row = int(u / n_hb);
-        w.head_block = int(u % n_hb);
+        w.q_row = units[size_t(u)].q_row;
+        w.head_block = units[size_t(u)].head_block;
+        w.stacked_rows = units[size_t(u)].stacked_rows;
         w.k_begin = 0;
         w.k_end = std::min(len, sh.topk);
         w.partial_slot = -1;

@@ -232,6 +232,28 @@ __global__ void debug_rows_kernel(AttnParams p, int total_q, int32_t* rows_out) 
     }
 }
 
+// ------------------------------------------------------------------ tile row -> (query row, head)
+// Tile row r of a work item is head head_block * 128 + r of query row q_row, or, for an item that stacks
+// the query rows of one sequence that share an index list, head r % H of query row q_row + r / H.
+struct RowMap {
+    int q_row, head;
+    bool live;
+};
+__device__ __forceinline__ RowMap map_row(const dsa_v32_work_info& w, int row, int H) {
+    RowMap m;
+    if (w.stacked_rows > 1) {
+        const int sub = row / H;
+        m.q_row = w.q_row + sub;
+        m.head = row - sub * H;
+        m.live = sub < w.stacked_rows;
+    } else {
+        m.q_row = w.q_row;
+        m.head = w.head_block * kHeadsPerBlock + row;
+        m.live = m.head < H;
+    }
+    return m;
+}
+
 // ------------------------------------------------------------------ e4m3 -> bf16, exact, two at a time
 // Input: the two e4m3 bytes in the high byte of each 16-bit half.  Moving the 7 magnitude bits down
 // by 4 puts the 4 exponent bits and 3 mantissa bits where bf16 keeps them; read as bf16 that number
@@ -367,14 +389,18 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         ctl->abort_flag = 0;
         fence_mbar_init();
     }
+    if (kFp8 && p.H < kHeadsPerBlock) {   // rows of the rope block of Q that no load covers (heads >= H) must read as zero
+        for (int i = tid * 16; i < kQBlockBytes; i += C::kThreads * 16) *reinterpret_cast<uint4*>(sQ + i) = make_uint4(0u, 0u, 0u, 0u);
+        fence_proxy_async_smem();         // the MMAs read the block through the async proxy
+    }
     if (warp == kMmaWarp) {
         tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
         tmem_relinquish();
     }
-    if (warp == kLoaderWarp0 && lane == 0) {
+    if (kFp8 && warp == kLoaderWarp0 && lane == 0) {   // a bf16 cache is read with plain loads: its maps are unused
         prefetch_tensormap(&tm_q);
         prefetch_tensormap(&tm_kv);
-        if (kFp8) prefetch_tensormap(&tm_kv_tail);
+        prefetch_tensormap(&tm_kv_tail);
     }
     tc_fence_before();
     __syncthreads();
@@ -438,10 +464,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         uint32_t qreg[kQRegs];
         const int q_ncol = (!kFp8 && half) ? 40 : 32;   // TMEM columns (bf16 pairs) per warp; fp8: latent columns only
         auto q_fetch = [&](const dsa_v32_work_info& wq) {
-            const int head = wq.head_block * kHeadsPerBlock + row;
-            const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.q) + (size_t)wq.q_row * p.stride_q_row +
-                                       (size_t)head * p.stride_q_head + col0 + 2 * cg * q_ncol;
-            const bool live = head < p.H;
+            const RowMap rm = map_row(wq, row, p.H);
+            const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.q) + (size_t)rm.q_row * p.stride_q_row +
+                                       (size_t)rm.head * p.stride_q_head + col0 + 2 * cg * q_ncol;
+            const bool live = rm.live;
 #pragma unroll
             for (int j = 0; j < kQRegs / 4; ++j) {
                 uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -453,10 +479,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
         };
         auto q_prefetch_l2 = [&](const dsa_v32_work_info& wq) {
-            const int head = wq.head_block * kHeadsPerBlock + row;
-            if (head < p.H) {
-                const char* src = reinterpret_cast<const char*>(reinterpret_cast<const __nv_bfloat16*>(p.q) + (size_t)wq.q_row * p.stride_q_row +
-                                                               (size_t)head * p.stride_q_head + col0 + 2 * cg * q_ncol);
+            const RowMap rm = map_row(wq, row, p.H);
+            if (rm.live) {
+                const char* src = reinterpret_cast<const char*>(reinterpret_cast<const __nv_bfloat16*>(p.q) + (size_t)rm.q_row * p.stride_q_row +
+                                                               (size_t)rm.head * p.stride_q_head + col0 + 2 * cg * q_ncol);
                 asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
                 asm volatile("prefetch.global.L2 [%0];" ::"l"(src + 2 * q_ncol * 2 - 16));
             }
@@ -851,11 +877,12 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (!warp_wait(smem_u32(&ctl->o_full), item_n & 1, abort_flag)) goto done;
                 tc_fence_after();
                 const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
-                const int head = wi.head_block * kHeadsPerBlock + row;
-                const bool live = head < p.H;
+                const RowMap rm = map_row(wi, row, p.H);
+                const int head = rm.head;
+                const bool live = rm.live;
                 const float lse_nat = (l > 0.0f) ? (m_ref + __log2f(l)) * 0.69314718055994531f : INFINITY;
                 if (wi.partial_slot < 0) {
-                    __nv_bfloat16* o_dst = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)wi.q_row * p.stride_o_row +
+                    __nv_bfloat16* o_dst = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)rm.q_row * p.stride_o_row +
                                            (size_t)head * p.stride_o_head + half * kDvHalf;
 #pragma unroll 1
                     for (int oc = cg * OCOLS; oc < (cg + 1) * OCOLS; oc += 32) {
@@ -875,7 +902,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                             }
                         }
                     }
-                    if (live && (kRowSplit ? own : half == 0) && cg == 0 && p.lse != nullptr) p.lse[(size_t)wi.q_row * p.H + head] = lse_nat;
+                    if (live && (kRowSplit ? own : half == 0) && cg == 0 && p.lse != nullptr) p.lse[(size_t)rm.q_row * p.H + head] = lse_nat;
                 } else {
                     float* o_dst = p.o_accum + ((size_t)wi.partial_slot * kHeadsPerBlock + row) * kDV + half * kDvHalf;
 #pragma unroll 1
@@ -1141,9 +1168,15 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 // rope block of the item's Q (the latent part goes to TMEM through the softmax warps)
                 if (!warp_wait(smem_u32(&ctl->q_empty), (item_n & 1) ^ 1, abort_flag)) goto done;
                 if (lane == 0) {
+                    // the box holds min(H, 128) heads of one query row; a stacked item loads one box per query
+                    // row, H heads apart (rows of the block that no box covers were zeroed at kernel start)
                     const uint32_t bar = smem_u32(&ctl->q_full);
-                    mbar_arrive_expect_tx(bar, kQBlockBytes);
-                    tma_load_3d(smem_u32(sQ), &tm_q, bar, kDV, wi.head_block * kHeadsPerBlock, wi.q_row);
+                    const int hbox = p.H < kHeadsPerBlock ? p.H : kHeadsPerBlock;
+                    const int n_box = wi.stacked_rows > 1 ? wi.stacked_rows : 1;
+                    mbar_arrive_expect_tx(bar, static_cast<uint32_t>(n_box * hbox * 128));
+                    for (int b = 0; b < n_box; ++b)
+                        tma_load_3d(smem_u32(sQ) + static_cast<uint32_t>(b * hbox * 128), &tm_q, bar, kDV,
+                                    wi.head_block * kHeadsPerBlock, wi.q_row + b);
                 }
             }
             for (int t = 0; t < n_tiles; ++t, ++it) {
@@ -1224,7 +1257,13 @@ __global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int hrow = blockIdx.y * 8 + warp;  // head inside the 128-head block
     const ReduceDst dst = reduce_dst[rr];
-    const int head = dst.head_block * kHeadsPerBlock + hrow;
+    int head = dst.head_block * kHeadsPerBlock + hrow, q_row = dst.q_row;
+    if (dst.head_block < 0) {   // stacked unit: -head_block query rows of H heads each
+        const int sub = hrow / H;
+        if (sub >= -dst.head_block) return;
+        head = hrow - sub * H;
+        q_row += sub;
+    }
     if (head >= H) return;
     const int s0 = reduce_indptr[rr], ns = reduce_indptr[rr + 1] - s0;
     float m = -FLT_MAX;
@@ -1251,7 +1290,7 @@ __global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ 
         }
     }
     const float inv = denom > 0.0f ? 1.0f / denom : 0.0f;
-    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)dst.q_row * stride_o_row + (size_t)head * stride_o_head;
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)q_row * stride_o_row + (size_t)head * stride_o_head;
 #pragma unroll
     for (int v = 0; v < 4; ++v) {
         uint2 u;
@@ -1260,7 +1299,7 @@ __global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ 
         *reinterpret_cast<uint2*>(o + (v * 32 + lane) * 4) = u;
     }
     if (lane == 0 && lse != nullptr)
-        lse[(size_t)dst.q_row * H + head] = denom > 0.0f ? m + log2f(denom) * 0.69314718055994531f : INFINITY;
+        lse[(size_t)q_row * H + head] = denom > 0.0f ? m + log2f(denom) * 0.69314718055994531f : INFINITY;
 }
 
 // ------------------------------------------------------------------ cache write path

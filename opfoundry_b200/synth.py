@@ -137,7 +137,8 @@ def make_decode_case(B, H, kv_len, topk, *, s_q=1, fp8=False, paged=False, page_
                     row[topk - n_pad:] = -1
             indices[r] = row
     return dict(q=q, kv=kv, indices=indices, block_table=block_table, page_block_size=page_block_size,
-                kv_batch_stride_rows=stride_rows, s_q=s_q, fp8=fp8, H=H, topk=topk, kv_len=kv_len, B=B)
+                kv_batch_stride_rows=stride_rows, s_q=s_q, fp8=fp8, H=H, topk=topk, kv_len=kv_len, B=B,
+                mtp_shared=(coin != 0))
 
 
 def make_prefill_case(T, H, topk, *, seed=2026, q_rows=None):

@@ -17,10 +17,10 @@ def to_dev(case):
     return d
 
 
-def run_gpu(case, sm_scale, *, valid_len_hint=None, poison_out=True):
+def run_gpu(case, sm_scale, *, valid_len_hint=None, poison_out=True, mtp_shared=None):
     d = to_dev(case)
     total_q, H = d["q"].shape[0], d["q"].shape[1]
-    plan = api.mla_decode_plan_create(total_q, H, case["topk"], case["s_q"], valid_len_hint=valid_len_hint)
+    plan = api.mla_decode_plan_create(total_q, H, case["topk"], case["s_q"], valid_len_hint=valid_len_hint, mtp_shared=mtp_shared)
     out = torch.empty(total_q, H, 512, dtype=torch.bfloat16, device="cuda")
     lse = torch.empty(total_q, H, dtype=torch.float32, device="cuda")
     if poison_out:  # anything the kernels fail to write stays NaN

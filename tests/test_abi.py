@@ -28,7 +28,7 @@ def test_every_declared_symbol_is_exported(built_lib):
 
 def test_struct_sizes_match_header():
     assert C.sizeof(api.WorkInfo) == 32          # same size as the reference's work_info (defs.h:64-73,173)
-    assert C.sizeof(api.Shape) == 32
+    assert C.sizeof(api.Shape) == 40
     assert C.sizeof(api.PlanInfo) == 24
     assert C.sizeof(api.AttnArgs) == 7 * 8 + 7 * 8 + 8 * 4
 

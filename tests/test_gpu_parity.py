@@ -244,3 +244,22 @@ def test_bounded_wait_expires_and_reports(built_lib):
     case = synth.make_decode_case(2, 16, 256, 64, fp8=False, seed=3)
     out, lse, _ = run_gpu(case, SCALE)
     assert np.all(np.isfinite(lse))
+
+
+@pytest.mark.parametrize("fp8,H,s_q", [(True, 64, 2), (True, 16, 2), (False, 32, 4), (False, 64, 2)])
+def test_mtp_shared_lists_stacked_rows(oracle, fp8, H, s_q):
+    """Sequences whose MTP query rows share one index list run as one stacked item (rows gathered once);
+    the result must equal the oracle's, which knows nothing of the stacking.  Small and large plans (with
+    and without split items)."""
+    from gpu_util import run_gpu, run_oracle
+    for B, kv_len, topk in ((6, 1024, 512), (3, 4096, 2048)):
+        case = synth.make_decode_case(B, H, kv_len, topk, s_q=s_q, fp8=fp8, paged=fp8, share_mtp="coin", seed=7 * H + s_q + B)
+        if not case["mtp_shared"].any():
+            case["mtp_shared"][0] = True
+            case["indices"][1:s_q] = case["indices"][0]
+        g_out, g_lse, plan = run_gpu(case, SCALE, mtp_shared=case["mtp_shared"])
+        stacked = [w.stacked_rows for w in plan.read_works()[0]]
+        assert max(stacked) == s_q
+        r_out, r_lse = run_oracle(oracle, case, SCALE)
+        check_out(g_out, r_out, **(TOL_FP8 if fp8 else TOL_BF16))
+        check_lse(g_lse, r_lse)

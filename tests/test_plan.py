@@ -141,3 +141,33 @@ def test_auto_split_limits_the_lists_of_a_small_problem():
         tiles = q * ((topk + 31) // 32)
         eff = max(1, min(74, int(round(1.2 * math.sqrt((tiles + q * 6) * 74)))))
         assert _used_lists(api.plan_host(q, 128, topk, 1, auto_split=True)) <= eff
+
+
+def test_mtp_rows_that_share_a_list_are_planned_as_one_stacked_item():
+    """With s_q * H <= 128 the query rows of a sequence flagged as sharing one index list become one
+    work item (stacked_rows = s_q, gathered once); other sequences keep one item per row; every slot
+    of every query row is still covered exactly once."""
+    B, s_q, H, topk = 12, 2, 64, 512
+    shared = [b % 3 != 0 for b in range(B)]
+    for num_sms in (148, 8):
+        blob = api.plan_host(B * s_q, H, topk, s_q, num_sms=num_sms, mtp_shared=shared)
+        h, indptr, works, r_indptr, r_slots, r_dst = parse(blob)
+        cover = {}
+        for w in works:
+            q, slot, kb, ke, hb, rr, stacked = (int(x) for x in w[:7])
+            rows = stacked if stacked > 1 else 1
+            assert (stacked == s_q) == shared[q // s_q] and hb == 0
+            if stacked > 1:
+                assert q % s_q == 0
+            for t in range(rows):
+                cover.setdefault(q + t, []).append((kb, ke))
+            if rr >= 0:
+                assert int(r_dst[rr][0]) == q and int(r_dst[rr][1]) == (-stacked if stacked > 1 else 0)
+        assert sorted(cover) == list(range(B * s_q))
+        for q, pieces in cover.items():
+            pieces.sort()
+            assert pieces[0][0] == 0 and pieces[-1][1] == topk and all(a[1] == b[0] for a, b in zip(pieces, pieces[1:]))
+    # stacking needs s_q * H <= 128: at H = 128 the flags change nothing
+    a = api.plan_host(B * s_q, 128, topk, s_q, mtp_shared=shared)
+    b = api.plan_host(B * s_q, 128, topk, s_q)
+    assert a == b

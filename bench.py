@@ -406,8 +406,9 @@ def cfg4_problem(env, seq_begin, seq_end, n_batches=2):
 def cfg4_leg(env, mode, steps, warmup):
     """mode "tp": every rank attends all 128 x 2 query rows with its 128 / N heads over the replicated cache;
     mode "batch": every rank attends its 128 / N sequences with all 128 heads over its own sequences' cache.
-    Both end with one NCCL all-gather of the bf16 outputs (the only exchange the path has); the step is
-    timed with and without it."""
+    Both end with the all-gather of the bf16 outputs (the only exchange the path has): the step is timed
+    without it, with the gather fused into the kernels (peer stores + flags; the block's `ms_per_step`) and
+    with an NCCL all-gather after the kernels (the cross-check; both must give the same bytes)."""
     from opfoundry_b200 import shard
     torch, api, dist = env.torch, env.api, env.dist
     c = CFG4
@@ -440,8 +441,44 @@ def cfg4_leg(env, mode, steps, warmup):
 
     ms_attn = env.timed(attn, steps, warmup, arg_sets[0])
     ms_full = env.timed(attn_gather, steps, warmup, arg_sets[0]) if world > 1 else ms_attn
+    # the same step with the gather fused into the kernels: finished rows are stored straight into every
+    # peer's gathered buffer (peer-mapped pointers, plain stores), then one flag round
+    ms_fused, fused_ok = None, None
+    if world > 1:
+        pg = shard.PeerGather(c["B"] * c["s_q"], c["H"])
+        row0 = s0 * c["s_q"]
+        fused_args = []
+        for q, idx in step_in:
+            a = api.make_args(q, W["cache"], idx, plan, SM_SCALE, out=out, lse=lse, block_table=W["block_table"], page_block_size=c["page"])
+            a.stride_o_row, a.stride_o_head = pg.out.stride(0), pg.out.stride(1)
+            fused_args.append(a)
+
+        def fused(i):
+            po = pg.targets(row0, h0)
+            api._check(env.L.dsa_v32_decode_pipeline_allgather(C.byref(fused_args[i % len(fused_args)]), C.byref(po), env.stream()),
+                       "fused decode step")
+
+        ms_fused = env.timed(fused, steps, warmup, arg_sets[0])
+        # same numbers as the NCCL path: one more step of each on the same inputs
+        attn_gather(0)
+        fused(0)
+        torch.cuda.synchronize()
+        dist.barrier()
+        if mode == "tp":
+            ref = gathered.permute(1, 0, 2, 3).reshape(total_q, c["H"], D_V)          # [q, rank, heads, d] -> [q, H, d]
+        else:
+            ref = gathered.reshape(c["B"] * c["s_q"], c["H"], D_V)
+        fused_ok = bool(torch.equal(ref.view(torch.int16), pg.out.view(torch.int16)))
+        t = torch.tensor([1.0 if fused_ok else 0.0], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        fused_ok = bool(t.item() > 0.5)
+        dist.barrier()
+        pg.close()
+        dist.barrier()
+        del pg, fused_args
     clocks = env.sampler.summary()
     pk = peaks()
+    ms_step = ms_fused if ms_fused is not None else ms_full
     pairs_total = float(c["B"] * c["s_q"] * c["topk"])
     flops_total = flops_of(pairs_total, c["H"])
     # per GPU: tp keeps every GPU's gathered bytes and divides the flops; batch divides both
@@ -449,9 +486,13 @@ def cfg4_leg(env, mode, steps, warmup):
     roof = roofline_block(flops_of(pairs_gpu, Hl), pairs_gpu * 656.0, ms_attn, pk, "sparse_mla_kernel<fp8>")
     block = dict(workload="cfg4_%s_decode_fp8_mtp_b%d_sq2_h128_topk2048_kv65536_paged64" % (mode, c["B"]), n_gpus=world,
                  heads_per_gpu=Hl, sequences_per_gpu=nseq, shared_list_fraction=W["share_frac"],
-                 ms_per_step=ms_full, ms_per_step_without_gather=ms_attn, all_gather_ms=ms_full - ms_attn,
+                 ms_per_step=ms_step, ms_per_step_without_gather=ms_attn, ms_per_step_nccl_gather=ms_full,
+                 ms_per_step_fused_gather=ms_fused, nccl_all_gather_ms=ms_full - ms_attn, fused_equals_nccl=fused_ok,
+                 gather="stores into the peers' gathered buffers from the attention kernels + one flag round (the NCCL all-gather "
+                        "is timed beside it as the cross-check)" if world > 1 else "none (one GPU)",
                  all_gather_bytes_per_gpu=(out.numel() * 2 if world > 1 else 0),
-                 tflops=flops_total / (ms_full * 1e-3) / 1e12, tflops_without_gather=flops_total / (ms_attn * 1e-3) / 1e12,
+                 tflops=flops_total / (ms_step * 1e-3) / 1e12, tflops_without_gather=flops_total / (ms_attn * 1e-3) / 1e12,
+                 tflops_nccl_gather=flops_total / (ms_full * 1e-3) / 1e12,
                  steps=steps, pairs=pairs_total, roofline=roof,
                  sharding=("heads sharded %d per GPU, latent cache replicated" % Hl if mode == "tp" else
                            "sequences sharded %d per GPU with their cache, all 128 heads" % nseq) + ", one NCCL all-gather of the outputs per step",

@@ -194,6 +194,44 @@ int dsa_v32_combine(const dsa_v32_attn_args* args, void* stream);
 int dsa_v32_decode_pipeline(const dsa_v32_attn_args* args, int run_plan, void* stream);
 
 /*
+ * The pipeline fused with the all-gather that follows it when the heads or the sequences are sharded over
+ * the GPUs of one box: instead of args->out / args->lse the kernels store every finished output row
+ * straight into the gathered buffers of all peers (this GPU's own among them) through peer-mapped
+ * pointers - plain global stores over NVLink that overlap the rest of the attention - and a one-warp kernel
+ * then publishes "rank my_rank has written step `step`" in every peer's flag array and waits (bounded, one
+ * second) until all peers have published the same step here.  When the call's work on `stream` is complete,
+ * this GPU's gathered buffer holds every rank's slice.  The caller maps the buffers once (CUDA IPC or any
+ * peer mapping; no multicast object is involved) and passes, for every peer r:
+ *   out[r], lse[r]  where THIS rank's slice starts inside peer r's gathered out / lse buffer; the element
+ *                   strides are args->stride_o_row / stride_o_head and lse_stride_row for all peers,
+ *   flags[r]        peer r's array of DSA_V32_MAX_PEERS uint32 arrival flags (zero before the first step).
+ * `step` must grow by one with every call.  No counterpart in the reference, which is single-GPU; the
+ * collective it replaces is the NCCL all-gather of the head-sharded decode configuration.
+ */
+#define DSA_V32_MAX_PEERS 8
+typedef struct dsa_v32_peer_outputs {
+    int32_t num_peers; /* 1 .. DSA_V32_MAX_PEERS, this GPU included */
+    int32_t my_rank;   /* index of this GPU among the peers */
+    void* out[DSA_V32_MAX_PEERS];
+    float* lse[DSA_V32_MAX_PEERS]; /* all NULL: lse is not produced */
+    uint32_t* flags[DSA_V32_MAX_PEERS];
+    int64_t lse_stride_row; /* elements between query rows of the gathered lse */
+    uint32_t step;
+    uint32_t _pad;
+} dsa_v32_peer_outputs;
+int dsa_v32_decode_pipeline_allgather(const dsa_v32_attn_args* args, const dsa_v32_peer_outputs* peers, void* stream);
+/*
+ * Helpers for the mapping: export the 64-byte CUDA IPC handle of the cudaMalloc allocation a device pointer
+ * lies in, with the pointer's byte offset inside it; open such a handle exported by another process of the
+ * box FOR THE CURRENT DEVICE, enabling peer access to the exporting GPU on the way
+ * (kernels on this GPU may then store through the returned base address), and close it again.  A handle
+ * names a whole allocation: open it once per process and add the buffer's offset inside it.
+ */
+int dsa_v32_ipc_export(const void* dev_ptr, void* handle64_out, int64_t* offset_out);
+int dsa_v32_ipc_open(const void* handle64, void** base_out);
+int dsa_v32_ipc_close(void* base);
+
+/*
  * Host-buffer form of the pipeline, the call a serving loop makes once per step: copies this
  * step's queries and top-k lists from (pinned) host memory into args->q / args->indices, runs
  * attention + merge, and copies out / lse back to host memory, all asynchronously on `stream`.

@@ -36,6 +36,14 @@ class PlanInfo(C.Structure):
                 ("num_partials", C.c_int32), ("num_reduce_rows", C.c_int32)]
 
 
+MAX_PEERS = 8
+
+
+class PeerOutputs(C.Structure):
+    _fields_ = [("num_peers", C.c_int32), ("my_rank", C.c_int32), ("out", C.c_void_p * MAX_PEERS), ("lse", C.c_void_p * MAX_PEERS),
+                ("flags", C.c_void_p * MAX_PEERS), ("lse_stride_row", C.c_int64), ("step", C.c_uint32), ("_pad", C.c_uint32)]
+
+
 class AttnArgs(C.Structure):
     _fields_ = [("q", C.c_void_p), ("kv", C.c_void_p), ("out", C.c_void_p), ("lse", C.c_void_p),
                 ("indices", C.c_void_p), ("block_table", C.c_void_p), ("workspace", C.c_void_p),
@@ -55,7 +63,7 @@ EXPORTS = ["dsa_v32_abi_version", "dsa_v32_error_string", "dsa_v32_plan_info_get
            "dsa_v32_plan_host", "dsa_v32_plan_read", "dsa_v32_plan_release", "dsa_v32_decode_bf16", "dsa_v32_decode_fp8",
            "dsa_v32_prefill_bf16", "dsa_v32_combine", "dsa_v32_decode_pipeline", "dsa_v32_device_status",
            "dsa_v32_debug_rows", "dsa_v32_pack_fp8_rows", "dsa_v32_decode_pipeline_host",
-           "dsa_v32_decode_pipeline_static", "dsa_v32_static_scratch_address", "dsa_v32_selftest_wait_expiry"]
+           "dsa_v32_decode_pipeline_static", "dsa_v32_static_scratch_address", "dsa_v32_selftest_wait_expiry", "dsa_v32_decode_pipeline_allgather", "dsa_v32_ipc_export", "dsa_v32_ipc_open", "dsa_v32_ipc_close"]
 
 _lib = None
 
@@ -89,6 +97,10 @@ def lib():
         L.dsa_v32_decode_pipeline.argtypes = [C.POINTER(AttnArgs), C.c_int, C.c_void_p]
         L.dsa_v32_decode_pipeline_host.argtypes = [C.POINTER(AttnArgs), C.POINTER(HostIO), C.c_void_p]
         L.dsa_v32_decode_pipeline_static.argtypes = [C.POINTER(AttnArgs), C.c_void_p]
+        L.dsa_v32_decode_pipeline_allgather.argtypes = [C.POINTER(AttnArgs), C.POINTER(PeerOutputs), C.c_void_p]
+        L.dsa_v32_ipc_export.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_int64)]
+        L.dsa_v32_ipc_open.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
+        L.dsa_v32_ipc_close.argtypes = [C.c_void_p]
         L.dsa_v32_static_scratch_address.restype = C.c_void_p
         L.dsa_v32_static_scratch_address.argtypes = []
         L.dsa_v32_debug_rows.argtypes = [C.POINTER(AttnArgs), C.c_void_p, C.c_void_p]

@@ -16,8 +16,9 @@ int max_resident_pairs(bool fp8, int* out);
 cudaError_t launch_attn(bool fp8, int num_lists, const CUtensorMap& tq, const CUtensorMap& tkv, const CUtensorMap& ttail,
                         const AttnParams& p, cudaStream_t stream);
 cudaError_t launch_combine(const float* o_accum, const float* lse_accum, const int32_t* reduce_indptr,
-                           const int32_t* reduce_slots, const ReduceDst* reduce_dst, int num_reduce_rows, void* out, float* lse,
+                           const int32_t* reduce_slots, const ReduceDst* reduce_dst, int num_reduce_rows, const OutTargets& tgt,
                            int64_t stride_o_row, int64_t stride_o_head, int H, cudaStream_t stream);
+cudaError_t launch_peer_sync(const PeerSync& s, cudaStream_t stream);
 cudaError_t launch_debug_rows(const AttnParams& p, int total_q, int32_t* rows_out, cudaStream_t stream);
 cudaError_t launch_wait_selftest(int32_t* status, int32_t* result, unsigned long long budget_ns, cudaStream_t stream);
 cudaError_t launch_pack_fp8(const float* latent, const void* rope, const int64_t* dst_rows, void* out, int64_t num_rows,
@@ -156,6 +157,23 @@ void fill_params(const dsa_v32_attn_args* a, const WorkspaceHeader& h, AttnParam
     p->block_table_stride = a->block_table_stride;
     set_page(p, a->page_block_size);
     p->scale_log2 = a->sm_scale * 1.4426950408889634f;
+    p->n_peers = 0;
+    p->lse_stride_row = a->H;
+    for (int i = 0; i < DSA_V32_MAX_PEERS; ++i) {
+        p->out_peers[i] = nullptr;
+        p->lse_peers[i] = nullptr;
+    }
+}
+
+int check_peers(const dsa_v32_peer_outputs* pe) {
+    if (!pe) return DSA_V32_ERR_NULL;
+    if (pe->num_peers < 1 || pe->num_peers > DSA_V32_MAX_PEERS || pe->my_rank < 0 || pe->my_rank >= pe->num_peers) return DSA_V32_ERR_SHAPE;
+    if (pe->lse_stride_row <= 0) return DSA_V32_ERR_SHAPE;
+    for (int i = 0; i < pe->num_peers; ++i) {
+        if (!pe->out[i] || !pe->flags[i]) return DSA_V32_ERR_NULL;
+        if (!aligned16(pe->out[i])) return DSA_V32_ERR_ALIGN;
+    }
+    return DSA_V32_OK;
 }
 
 // Encoded tensor maps depend only on (base pointer, extents, strides): a serving loop passes the same
@@ -208,12 +226,21 @@ TmapCache& tmap_cache() {
     return c;
 }
 
-int launch_attention(const dsa_v32_attn_args* a, int want_dtype, cudaStream_t stream, const WorkspaceHeader* known = nullptr) {
+int launch_attention(const dsa_v32_attn_args* a, int want_dtype, cudaStream_t stream, const WorkspaceHeader* known = nullptr,
+                     const dsa_v32_peer_outputs* peers = nullptr) {
     WorkspaceHeader h;
     int rc = check_args(a, want_dtype, &h, known);
     if (rc) return rc;
     AttnParams p;
     fill_params(a, h, &p);
+    if (peers) {
+        p.n_peers = peers->num_peers;
+        p.lse_stride_row = peers->lse_stride_row;
+        for (int i = 0; i < peers->num_peers; ++i) {
+            p.out_peers[i] = peers->out[i];
+            p.lse_peers[i] = peers->lse[i];
+        }
+    }
     // bf16 cache: the kernel reads Q and the cache rows with plain loads and takes no tensor map
     CUtensorMap tq, tkv, ttail;
     std::memset(&tq, 0, sizeof(tq));
@@ -244,17 +271,33 @@ int launch_attention(const dsa_v32_attn_args* a, int want_dtype, cudaStream_t st
     return e == cudaSuccess ? DSA_V32_OK : (int)e;
 }
 
-int launch_merge(const dsa_v32_attn_args* a, cudaStream_t stream, const WorkspaceHeader* known = nullptr) {
+int launch_merge(const dsa_v32_attn_args* a, cudaStream_t stream, const WorkspaceHeader* known = nullptr,
+                 const dsa_v32_peer_outputs* peers = nullptr) {
     WorkspaceHeader h;
     if (!a) return DSA_V32_ERR_NULL;
     int rc = check_args(a, a->kv_dtype, &h, known);
     if (rc) return rc;
+    OutTargets tgt;
+    std::memset(&tgt, 0, sizeof(tgt));
+    if (peers) {
+        tgt.n_peers = peers->num_peers;
+        tgt.lse_stride_row = peers->lse_stride_row;
+        for (int i = 0; i < peers->num_peers; ++i) {
+            tgt.out[i] = peers->out[i];
+            tgt.lse[i] = peers->lse[i];
+        }
+    } else {
+        tgt.n_peers = 1;
+        tgt.lse_stride_row = a->H;
+        tgt.out[0] = a->out;
+        tgt.lse[0] = a->lse;
+    }
     uint8_t* ws = reinterpret_cast<uint8_t*>(a->workspace);
     cudaError_t e = launch_combine(reinterpret_cast<const float*>(ws + h.off_o_accum),
                                    reinterpret_cast<const float*>(ws + h.off_lse_accum),
                                    reinterpret_cast<const int32_t*>(ws + h.off_reduce_indptr),
                                    reinterpret_cast<const int32_t*>(ws + h.off_reduce_slots),
-                                   reinterpret_cast<const ReduceDst*>(ws + h.off_reduce_dst), h.num_reduce_rows, a->out, a->lse,
+                                   reinterpret_cast<const ReduceDst*>(ws + h.off_reduce_dst), h.num_reduce_rows, tgt,
                                    a->stride_o_row, a->stride_o_head, a->H, stream);
     return e == cudaSuccess ? DSA_V32_OK : (int)e;
 }
@@ -389,6 +432,68 @@ int dsa_v32_decode_pipeline(const dsa_v32_attn_args* a, int run_plan, void* stre
     int rc = launch_attention(a, a->kv_dtype, (cudaStream_t)stream);
     if (rc) return rc;
     return dsa_v32_combine(a, stream);
+}
+
+int dsa_v32_decode_pipeline_allgather(const dsa_v32_attn_args* a, const dsa_v32_peer_outputs* peers, void* stream) {
+    if (!a) return DSA_V32_ERR_NULL;
+    int rc = check_peers(peers);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    rc = launch_attention(a, a->kv_dtype, st, nullptr, peers);
+    if (rc) return rc;
+    rc = launch_merge(a, st, nullptr, peers);
+    if (rc) return rc;
+    PeerSync s;
+    std::memset(&s, 0, sizeof(s));
+    s.n_peers = peers->num_peers;
+    s.my_rank = peers->my_rank;
+    s.step = peers->step;
+    for (int i = 0; i < peers->num_peers; ++i) s.flags[i] = peers->flags[i];
+    s.status = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(a->workspace) + offsetof(WorkspaceHeader, status));
+    cudaError_t e = launch_peer_sync(s, st);
+    return e == cudaSuccess ? DSA_V32_OK : (int)e;
+}
+
+int dsa_v32_ipc_export(const void* dev_ptr, void* handle64_out, int64_t* offset_out) {
+    if (!dev_ptr || !handle64_out || !offset_out) return DSA_V32_ERR_NULL;
+    // the handle names the whole allocation the pointer lies in: find its base
+    typedef CUresult (*range_fn)(CUdeviceptr*, size_t*, CUdeviceptr);
+    static range_fn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            return DSA_V32_ERR_DRIVER;
+        fn = reinterpret_cast<range_fn>(p);
+    }
+    CUdeviceptr base = 0;
+    size_t size = 0;
+    if (fn(&base, &size, reinterpret_cast<CUdeviceptr>(dev_ptr)) != CUDA_SUCCESS) return DSA_V32_ERR_DRIVER;
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base));
+    if (e != cudaSuccess) return (int)e;
+    std::memcpy(handle64_out, &h, sizeof(h));
+    *offset_out = static_cast<int64_t>(reinterpret_cast<CUdeviceptr>(dev_ptr) - base);
+    return DSA_V32_OK;
+}
+
+int dsa_v32_ipc_open(const void* handle64, void** base_out) {
+    if (!handle64 || !base_out) return DSA_V32_ERR_NULL;
+    cudaIpcMemHandle_t h;
+    static_assert(sizeof(h) == 64, "CUDA IPC handles are 64 bytes");
+    std::memcpy(&h, handle64, sizeof(h));
+    void* ptr = nullptr;
+    // mapped for the CURRENT device, with peer access to the exporting GPU enabled as part of the call
+    cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return (int)e;
+    *base_out = ptr;
+    return DSA_V32_OK;
+}
+
+int dsa_v32_ipc_close(void* base) {
+    if (!base) return DSA_V32_ERR_NULL;
+    cudaError_t e = cudaIpcCloseMemHandle(base);
+    return e == cudaSuccess ? DSA_V32_OK : (int)e;
 }
 
 int dsa_v32_decode_pipeline_host(const dsa_v32_attn_args* a, const dsa_v32_host_io* io, void* stream) {

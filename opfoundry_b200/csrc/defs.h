@@ -54,6 +54,27 @@ struct AttnParams {
     int32_t H, topk, s_q, block_table_stride, page_block_size;
     int32_t page_shift;  // log2(page_block_size) when that is a power of two, else -1
     float scale_log2;  // sm_scale * log2(e)
+    // fused all-gather: when n_peers > 0 finished rows go to every peer's gathered buffer instead of out / lse
+    int32_t n_peers;
+    int64_t lse_stride_row;   // elements between query rows of lse (H without peers)
+    void* out_peers[DSA_V32_MAX_PEERS];
+    float* lse_peers[DSA_V32_MAX_PEERS];
+};
+
+// Destinations of the merge kernel (same convention as AttnParams).
+struct OutTargets {
+    int32_t n_peers;
+    int64_t lse_stride_row;
+    void* out[DSA_V32_MAX_PEERS];
+    float* lse[DSA_V32_MAX_PEERS];
+};
+
+// Arrival flags of the fused all-gather: flags[r] = peer r's array, one word per sending rank.
+struct PeerSync {
+    int32_t n_peers, my_rank;
+    uint32_t step;
+    uint32_t* flags[DSA_V32_MAX_PEERS];
+    int32_t* status;
 };
 
 }  // namespace dsa

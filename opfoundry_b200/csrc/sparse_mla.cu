@@ -882,27 +882,42 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const bool live = rm.live;
                 const float lse_nat = (l > 0.0f) ? (m_ref + __log2f(l)) * 0.69314718055994531f : INFINITY;
                 if (wi.partial_slot < 0) {
-                    __nv_bfloat16* o_dst = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)rm.q_row * p.stride_o_row +
-                                           (size_t)head * p.stride_o_head + half * kDvHalf;
+                    // element offset of the row's 256 columns of this CTA; the same in out and in every peer's
+                    // gathered buffer (fused all-gather: plain stores through the peer-mapped pointers)
+                    const size_t o_off = (size_t)rm.q_row * p.stride_o_row + (size_t)head * p.stride_o_head + half * kDvHalf;
+                    const int n_dst = p.n_peers > 0 ? p.n_peers : 1;
 #pragma unroll 1
                     for (int oc = cg * OCOLS; oc < (cg + 1) * OCOLS; oc += 32) {
                         uint32_t o[32];
                         tmem_ld32(lane_base + kColO + oc, o);
                         tmem_wait_ld();
                         if (live) {
-                            uint4* d4 = reinterpret_cast<uint4*>(o_dst + oc);
+                            uint4 u[4];
 #pragma unroll
                             for (int v = 0; v < 4; ++v) {
-                                uint4 u;
-                                u.x = pack_bf16x2(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
-                                u.y = pack_bf16x2(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
-                                u.z = pack_bf16x2(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
-                                u.w = pack_bf16x2(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
-                                d4[v] = u;
+                                u[v].x = pack_bf16x2(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
+                                u[v].y = pack_bf16x2(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
+                                u[v].z = pack_bf16x2(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
+                                u[v].w = pack_bf16x2(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
+                            }
+#pragma unroll 1
+                            for (int d = 0; d < n_dst; ++d) {
+                                __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.n_peers > 0 ? p.out_peers[d] : p.out);
+                                uint4* d4 = reinterpret_cast<uint4*>(base + o_off + oc);
+#pragma unroll
+                                for (int v = 0; v < 4; ++v) d4[v] = u[v];
                             }
                         }
                     }
-                    if (live && (kRowSplit ? own : half == 0) && cg == 0 && p.lse != nullptr) p.lse[(size_t)rm.q_row * p.H + head] = lse_nat;
+                    if (live && (kRowSplit ? own : half == 0) && cg == 0) {
+                        const size_t l_off = (size_t)rm.q_row * p.lse_stride_row + head;
+                        if (p.n_peers > 0) {
+                            for (int d = 0; d < p.n_peers; ++d)
+                                if (p.lse_peers[d] != nullptr) p.lse_peers[d][l_off] = lse_nat;
+                        } else if (p.lse != nullptr) {
+                            p.lse[l_off] = lse_nat;
+                        }
+                    }
                 } else {
                     float* o_dst = p.o_accum + ((size_t)wi.partial_slot * kHeadsPerBlock + row) * kDV + half * kDvHalf;
 #pragma unroll 1
@@ -1251,7 +1266,7 @@ done:
 __global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ o_accum, const float* __restrict__ lse_accum,
                                                       const int32_t* __restrict__ reduce_indptr,
                                                       const int32_t* __restrict__ reduce_slots,
-                                                      const ReduceDst* __restrict__ reduce_dst, void* out, float* lse,
+                                                      const ReduceDst* __restrict__ reduce_dst, const OutTargets tgt,
                                                       int64_t stride_o_row, int64_t stride_o_head, int H) {
     const int rr = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1290,16 +1305,45 @@ __global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ 
         }
     }
     const float inv = denom > 0.0f ? 1.0f / denom : 0.0f;
-    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)q_row * stride_o_row + (size_t)head * stride_o_head;
+    const float lse_val = denom > 0.0f ? m + log2f(denom) * 0.69314718055994531f : INFINITY;
+    for (int d = 0; d < tgt.n_peers; ++d) {   // one destination, or every peer's gathered buffer
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(tgt.out[d]) + (size_t)q_row * stride_o_row + (size_t)head * stride_o_head;
 #pragma unroll
-    for (int v = 0; v < 4; ++v) {
-        uint2 u;
-        u.x = pack_bf16x2(acc[4 * v + 0] * inv, acc[4 * v + 1] * inv);
-        u.y = pack_bf16x2(acc[4 * v + 2] * inv, acc[4 * v + 3] * inv);
-        *reinterpret_cast<uint2*>(o + (v * 32 + lane) * 4) = u;
+        for (int v = 0; v < 4; ++v) {
+            uint2 u;
+            u.x = pack_bf16x2(acc[4 * v + 0] * inv, acc[4 * v + 1] * inv);
+            u.y = pack_bf16x2(acc[4 * v + 2] * inv, acc[4 * v + 3] * inv);
+            *reinterpret_cast<uint2*>(o + (v * 32 + lane) * 4) = u;
+        }
+        if (lane == 0 && tgt.lse[d] != nullptr) tgt.lse[d][(size_t)q_row * tgt.lse_stride_row + head] = lse_val;
     }
-    if (lane == 0 && lse != nullptr)
-        lse[(size_t)q_row * H + head] = denom > 0.0f ? m + log2f(denom) * 0.69314718055994531f : INFINITY;
+}
+
+// ------------------------------------------------------------------ arrival flags of the fused all-gather
+// After the kernels that stored this rank's rows into the peers' buffers: publish the step in every peer's
+// flag array (system-scope release after a system-scope fence, so the rows are visible before the flag),
+// then wait until every peer has published the same step here.  The wait is bounded (one second); on expiry
+// the status word gets DSA_V32_ERR_DEVICE_WAIT and the kernel returns.
+__global__ void __launch_bounds__(32) peer_signal_wait_kernel(const PeerSync s) {
+    const int lane = threadIdx.x;
+    __threadfence_system();
+    if (lane < s.n_peers) {
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(s.flags[lane] + s.my_rank), "r"(s.step) : "memory");
+        const uint32_t* mine = s.flags[s.my_rank] + lane;
+        const uint64_t t0 = global_ns();
+        bool ok = false;
+        for (uint32_t it = 0; it < DSA_WAIT_LIMIT; ++it) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+            if (static_cast<int32_t>(v - s.step) >= 0) {
+                ok = true;
+                break;
+            }
+            if (global_ns() - t0 > 1000000000ull) break;
+            __nanosleep(200);
+        }
+        if (!ok) atomicExch(s.status, DSA_V32_ERR_DEVICE_WAIT);
+    }
 }
 
 // ------------------------------------------------------------------ cache write path
@@ -1421,12 +1465,17 @@ cudaError_t launch_attn(bool fp8, int num_lists, const CUtensorMap& tq, const CU
 }
 
 cudaError_t launch_combine(const float* o_accum, const float* lse_accum, const int32_t* reduce_indptr,
-                           const int32_t* reduce_slots, const ReduceDst* reduce_dst, int num_reduce_rows, void* out, float* lse,
+                           const int32_t* reduce_slots, const ReduceDst* reduce_dst, int num_reduce_rows, const OutTargets& tgt,
                            int64_t stride_o_row, int64_t stride_o_head, int H, cudaStream_t stream) {
     if (num_reduce_rows <= 0) return cudaSuccess;
     dim3 grid(num_reduce_rows, kHeadsPerBlock / 8);
-    combine_kernel<<<grid, 256, 0, stream>>>(o_accum, lse_accum, reduce_indptr, reduce_slots, reduce_dst, out, lse,
-                                             stride_o_row, stride_o_head, H);
+    combine_kernel<<<grid, 256, 0, stream>>>(o_accum, lse_accum, reduce_indptr, reduce_slots, reduce_dst, tgt, stride_o_row,
+                                             stride_o_head, H);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_peer_sync(const PeerSync& s, cudaStream_t stream) {
+    peer_signal_wait_kernel<<<1, 32, 0, stream>>>(s);
     return cudaGetLastError();
 }
 

@@ -60,3 +60,78 @@ def all_gather_heads(local_out, world):
     parts = [torch.empty_like(local_out) for _ in range(world)]
     dist.all_gather(parts, local_out.contiguous())
     return torch.cat(parts, dim=1)
+
+
+class PeerGather:
+    """The gathered output of a sharded decode step, written by the attention kernels themselves.
+
+    Every rank owns a full [total_q, H_all, 512] bf16 buffer (+ lse [total_q, H_all] and eight arrival
+    flags) and maps every peer's through CUDA IPC (plain peer mappings; no multicast object).  `targets`
+    builds the argument of dsa_v32_decode_pipeline_allgather for this rank's slice - rows [row0, ...) and
+    heads [head0, ...) of the full layout - so the kernels store finished rows into all buffers directly
+    and the NCCL all-gather after the step disappears.
+    """
+
+    def __init__(self, total_q, H_all, device="cuda"):
+        from . import api
+        self.api = api
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        if self.world > api.MAX_PEERS:
+            raise ValueError("at most %d peers" % api.MAX_PEERS)
+        self.total_q, self.H_all = total_q, H_all
+        self.out = torch.zeros(total_q, H_all, 512, dtype=torch.bfloat16, device=device)
+        self.lse = torch.zeros(total_q, H_all, dtype=torch.float32, device=device)
+        self.flags = torch.zeros(api.MAX_PEERS, dtype=torch.int32, device=device)
+        self.step = 0
+        torch.cuda.synchronize()
+        # export: (64-byte handle of the allocation, byte offset of the tensor inside it); the tensors keep it alive
+        import ctypes as C
+        mine = []
+        for t in (self.out, self.lse, self.flags):
+            hb = C.create_string_buffer(64)
+            off = C.c_int64(0)
+            api._check(api.lib().dsa_v32_ipc_export(t.data_ptr(), hb, C.byref(off)), "dsa_v32_ipc_export")
+            mine.append((hb.raw, int(off.value)))
+        everyone = [None] * self.world
+        if self.world > 1:
+            dist.all_gather_object(everyone, mine)
+        else:
+            everyone[0] = mine
+        # import: every distinct allocation is opened once, for THIS device (peer access is enabled by the open)
+        self._opened = {}
+        self.ptrs = []          # per peer: (out, lse, flags) device addresses usable from this GPU
+        for r in range(self.world):
+            if r == self.rank:
+                self.ptrs.append((self.out.data_ptr(), self.lse.data_ptr(), self.flags.data_ptr()))
+                continue
+            addrs = []
+            for handle, offset in everyone[r]:
+                if handle not in self._opened:
+                    base = C.c_void_p()
+                    api._check(api.lib().dsa_v32_ipc_open(handle, C.byref(base)), "dsa_v32_ipc_open")
+                    self._opened[handle] = base.value
+                addrs.append(self._opened[handle] + offset)
+            self.ptrs.append(tuple(addrs))
+        if self.world > 1:
+            dist.barrier()      # nobody stores into a peer before every mapping exists
+
+    def close(self):
+        """Unmaps the peers' buffers (call on every rank, after a barrier, before the buffers are freed)."""
+        for base in self._opened.values():
+            self.api.lib().dsa_v32_ipc_close(base)
+        self._opened = {}
+
+    def targets(self, row0, head0):
+        """PeerOutputs for the next step of this rank's slice starting at (row0, head0) of the full layout.
+        The matching strides for the attention arguments are out.stride(0), out.stride(1)."""
+        po = self.api.PeerOutputs()
+        po.num_peers, po.my_rank = self.world, self.rank
+        o_off = (row0 * self.out.stride(0) + head0 * self.out.stride(1)) * 2
+        l_off = (row0 * self.H_all + head0) * 4
+        for r, (o, l, f) in enumerate(self.ptrs):
+            po.out[r], po.lse[r], po.flags[r] = o + o_off, l + l_off, f
+        po.lse_stride_row = self.H_all
+        self.step += 1
+        po.step = self.step
+        return po

@@ -14,9 +14,16 @@
 // Each CTA loads only its columns of Q, gathers only its columns of every selected row, computes
 // the partial scores Q_c K_c^T over its columns and owns the 256 output columns that are the
 // first 256 of its slice (V is a prefix of K), so no byte of the cache is fetched or converted
-// twice.  The partial scores are summed across the pair through distributed shared memory (each
-// softmax thread stores its row of partials into the peer's exchange buffer and arrives on the
-// peer's mbarrier); both CTAs then run the same softmax on the same numbers.
+// twice.  The partial scores have to be summed across the pair through distributed shared memory,
+// and the link between two SMs is narrow (measured: 17-20 bytes per clock one way, 11-16 each way
+// when both send), so what crosses it is kept small: partial scores as 16-bit fixed point with a
+// per-row step instead of fp32, and
+//   bf16 cache: the softmax itself is split by head rows - CTA c computes it for rows [64 c, 64 c + 64),
+//              receives the peer's partial scores for those rows and sends the finished P (bf16) and the
+//              rare rescale factor back: 8.7 KB per 32-row tile and direction, half the exponentials;
+//   fp8 cache:  both CTAs run the softmax of all 128 rows on the same (quantised) sums - the single score
+//              buffer in TMEM and the four tile stages make the latency of a tile's chain the bound
+//              there, and the row split would add a second hop to it.
 //
 // Warp roles inside a CTA (28 warps = seven warpgroups; after the role split setmaxnreg gives the four
 // softmax warpgroups 88 registers per thread and the others 48):
@@ -26,27 +33,34 @@
 //              step - the row's reference maximum in shared memory is read and moved when the tile's
 //              maximum exceeds it by more than the lazy margin (the reference's threshold of 8:
 //              ..16mx4_64nx1_template.hpp:700-725); P = 2^(s - reference) -> bf16 -> tcgen05.st.
-//              Epilogue: O / l -> bf16, or the fp32 partial + lse of a split item; during its waits the
-//              next item's Q slice is stored into TMEM (A operand of the score MMAs).
+//              Epilogue: O / l -> bf16 (to out, or to every peer GPU's gathered buffer when the all-gather
+//              is fused), or the fp32 partial + lse of a split item; during its waits the next item's Q
+//              slice is stored into TMEM (A operand of the score MMAs).
 //   warp 16    score MMA issuer: S_c = Q_c K_c^T (tcgen05.mma M=128, N=32, K=16, A = the Q slice in TMEM,
 //              accumulator in TMEM; fp8 cache: the 64 rope columns of Q stay in shared memory)
 //   warp 17    P V MMA issuer: O_c += P V_c (A = P in TMEM, B = the same gathered tile described
 //              MN-major).  Two issuers so that neither stream waits behind the other's barriers.
 //   bf16 cache: warps 20-27 loaders, two groups of four on alternate tiles, 8 rows of the tile per warp:
-//              top-k slots -> block table -> TMA tile::gather4 straight into the 128-byte swizzled MMA
-//              tile (one warp can start a gather4 only every ~70 cycles, so the issue is spread over warps)
-//   fp8 cache: warps 18-19 gather issuers on alternate tiles (lane = row; one gather4 per four rows, the
-//              row's two scales by cp.async), warps 20-27 converters, two groups of four on alternate
-//              tiles: e4m3 -> bf16 exactly (e4m3 has 4 significant bits) into the swizzled MMA tile (the
-//              reference's LDS round trip: ..mxfp8_16mx8_32nx1_template.hpp:852-864).  The per-128 fp32
-//              scales never touch the operands: Q K^T keeps one fp32 accumulator per scale group (plus one
-//              for rope) and the softmax warps form sum_g scale_g S_g in fp32 before the exchange; for P V
-//              they store one copy of P per scale group, pre-multiplied by that group's scale, and each
-//              copy multiplies its own 128 output columns.
+//              top-k slots -> block table -> the row's bytes of this CTA's slice as 16-byte cp.async copies
+//              straight into the 128-byte swizzled MMA tile (a TMA tile::gather4 moves one 128-byte block
+//              of four rows per request, 40 requests per tile, and the issue rate of those requests was
+//              the period of the whole pipeline)
+//   fp8 cache: warps 18-19 gather issuers on alternate tiles (lane = row; one TMA tile::gather4 per four
+//              rows, the row's two scales by cp.async), warps 20-27 converters, two groups of four on
+//              alternate tiles: e4m3 -> bf16 exactly (e4m3 has 4 significant bits) into the swizzled MMA
+//              tile (the reference's LDS round trip: ..mxfp8_16mx8_32nx1_template.hpp:852-864).  The
+//              per-128 fp32 scales never touch the operands: Q K^T keeps one fp32 accumulator per scale
+//              group (plus one for rope) and the softmax warps form sum_g scale_g S_g in fp32 before the
+//              exchange; for P V they store one copy of P per scale group, pre-multiplied by that group's
+//              scale, and each copy multiplies its own 128 output columns.
+//
+// A work item may stack the query rows of one sequence that share an index list (MTP) along the heads
+// when they fit the 128-row tile together: tile row r = query row q_row + r / H, head r % H.
 //
 // Every mbarrier wait is bounded; on expiry the CTA raises its own and its peer's abort flag,
 // records DSA_V32_ERR_DEVICE_WAIT in the workspace status word and both drain to the normal exit
-// (cluster barrier, TMEM release).
+// (cluster barrier, TMEM release).  A parity wait is only issued on a barrier whose previous phase the
+// waiting warp knows to be complete (rings it takes part in, or per-item barriers).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cfloat>
@@ -73,32 +87,6 @@
 namespace dsa {
 
 
-#ifdef DSA_PROFILE
-// Working aid (never compiled into the shipped library): per-role time stamps of the first tiles of
-// cluster 0, to see which stage of the pipeline the others wait for.
-__device__ long long* g_prof = nullptr;
-__device__ int g_prof_list = 0;
-__device__ __forceinline__ long long prof_now() {   // SM-local cycle counter (cheap to read)
-    return clock64();
-}
-// Stamps go to a shared-memory table (a clock read and one store, no global traffic on the path being
-// measured) that the CTA copies out when it exits: tiles [kProfTile0, kProfTile0 + 12) of the list,
-// 32-bit cycle counts, in the unused tail of the control block.
-#ifndef DSA_PROF_TILE0
-#define DSA_PROF_TILE0 6
-#endif
-constexpr int kProfTiles = 12, kProfTile0 = DSA_PROF_TILE0;
-#define PROF(role, tile, slot)                                                                      \
-    do {                                                                                            \
-        const uint32_t pt_ = static_cast<uint32_t>(tile) - kProfTile0;                              \
-        if (prof_on && pt_ < kProfTiles && lane == 0)                                               \
-            s_prof[((role) * kProfTiles + pt_) * 4 + (slot)] = static_cast<uint32_t>(prof_now());   \
-    } while (0)
-extern "C" int dsa_v32_set_prof(long long* buf) { return (int)cudaMemcpyToSymbol(g_prof, &buf, sizeof(buf)); }
-extern "C" int dsa_v32_set_prof_list(int list) { return (int)cudaMemcpyToSymbol(g_prof_list, &list, sizeof(list)); }
-#else
-#define PROF(role, tile, slot) do { } while (0)
-#endif
 
 // ------------------------------------------------------------------ shared-memory map
 constexpr int kMaxKBlocks = 5;                            // 64-column blocks per CTA: 4 (CTA 0) or 5 (CTA 1)
@@ -174,7 +162,7 @@ struct Ctl {
     uint32_t tmem_base;
     int abort_flag;
 };
-static_assert(sizeof(Ctl) <= 10752, "control block (the rest of its 12 KB holds the profile table of profile builds)");
+static_assert(sizeof(Ctl) <= 12288 - 256, "control block");
 
 // TMEM columns (512 allocated).
 //   bf16 cache: O [0,256) | Q slice [256,416) (packed bf16 pairs, 128 or 160 used) | S 2 x 32 | P 2 x 16
@@ -332,13 +320,6 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int warp = tid >> 5;
     const int lane = tid & 31;
     const int list = blockIdx.x >> 1;
-#ifdef DSA_PROFILE
-    static_assert(sizeof(Ctl) + 8 * kProfTiles * 4 * 4 <= C::kCtlBytes, "profile table");
-    uint32_t* s_prof = reinterpret_cast<uint32_t*>(smem + C::kOffCtl + C::kCtlBytes - 8 * kProfTiles * 4 * 4);
-    const bool prof_on = g_prof != nullptr && list == g_prof_list;
-    if (prof_on)
-        for (int i = tid; i < 8 * kProfTiles * 4; i += blockDim.x) s_prof[i] = 0;
-#endif
     const int half = (int)cluster_ctarank();      // 0: columns [0,256); 1: columns [256,576)
     const int peer = half ^ 1;
     // The two MMA issuers sit on the schedulers (warp number mod 4) whose softmax warps only export and import
@@ -355,7 +336,6 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int w_begin = __ldg(p.list_indptr + list);
     const int w_end = __ldg(p.list_indptr + list + 1);
 
-    if (tid == 0) PROF(5, kProfTile0 + 10, 0);
     // Barrier initialisation, spread over threads (about 120 barriers; one thread doing them all took
     // 2 000 cycles of every launch): thread i < 16 takes the i-th barrier of every 16-element family,
     // threads 32-39 the tile barriers, 64-67 the per-team ones, 96 the singles.
@@ -407,7 +387,6 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     cluster_sync_all();   // the peer's barriers exist before anything is sent to it
     tc_fence_after();
     const uint32_t tmem = ctl->tmem_base;
-    if (tid == 0) PROF(5, kProfTile0 + 10, 1);
     const uint32_t peer_abort = map_to_cta(smem_u32(&ctl->abort_flag), peer);
 
     if (warp < kSoftmaxWarps) {
@@ -534,7 +513,6 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     if (!warp_wait(smem_u32(&ctl->kv_full[it % S]), (it / S) & 1, abort_flag)) goto done;
                 if (!warp_wait(smem_u32(&ctl->s_full[tb]), tph, abort_flag)) goto done;
                 tc_fence_after();
-                if (warp == 0 || warp == 2) { if (own) PROF(2, it, 0); else PROF(3, it, 0); }
                 {
                     const uint32_t s0 = lane_base + s_col_of<kFp8>(it);
                     if (kFp8) {
@@ -578,7 +556,6 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
                         for (int j = 0; j < NP; ++j) tv2[j] = pack2u(sr[2 * j], sr[2 * j + 1]);
                     }
-                    if ((warp == 0 || warp == 2) && own) PROF(4, it, 0);
                 }
                 constexpr int kPVariants = kFp8 ? 2 : 1;
                 uint32_t pk[kPVariants][NP];   // P as the MMA wants it: bf16 pairs; fp8 cache: one copy per scale group
@@ -616,10 +593,8 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         st_async_u32(xout + 2048 + lane * 4, inv_bits, peer_xfull);
                         ++n_sent;
                     }
-                    if (warp == 0 || warp == 2) PROF(3, it, 1);
                     // ---- import the finished P of these rows (bf16 pairs) and the rescale factor
                     if (!warp_wait_cluster(my_xfull, xph, abort_flag)) goto done;
-                    if (warp == 0 || warp == 2) PROF(3, it, 2);
                     {
                         uint32_t pw[NP];
                         uint32_t dep;
@@ -694,7 +669,6 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     }
                     // ---- add the peer's partial scores
                     if (!warp_wait_cluster(my_xfull, xph, abort_flag)) goto done;
-                    if (warp == 0 || warp == 2) PROF(2, it, 2);
                     {
                         const float peer_inv = *reinterpret_cast<const float*>(xin_p + 2048 + lane * 4);
                         const uint64_t pi2 = pack2(peer_inv, peer_inv), nb2 = pack2(-kQuantBias, -kQuantBias);
@@ -742,7 +716,6 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         const float u3 = max3(t[9], t[10], t[11]), u4 = max3(t[12], t[13], t[14]);
                         mt = fmaxf(max3(u0, u1, t[15]), max3(u2, u3, u4)) * p.scale_log2;
                     }
-                    if (warp == 0 || warp == 2) PROF(7, it, 2);
                     // ---- the row's reference maximum, moved in tile order.  This is the only step that waits
                     // for the tile before (per lane quadrant: the warp of the previous team with the same rows),
                     // and it is a handful of instructions: read the reference, move it if the tile's maximum
@@ -755,7 +728,6 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     if (raise || first) ctl->m_shared[row] = m_fin;
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&ctl->m_bar[tb][quad]));
-                    if (warp == 0 || warp == 2) PROF(7, it, 3);
                     if (raise && !first) f2 = (m_cur == -INFINITY) ? 0.0f : ex2_approx(m_cur - m_fin);
                     // ---- P = 2^(score - reference): at most 2^8; a masked slot gives 0
                     const float m_fin_use = (m_fin == -INFINITY) ? 0.0f : m_fin;
@@ -792,7 +764,6 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                             st_async_u32(xout + 2048 + lane * 4, __float_as_uint(f2), peer_xfull);
                             ++n_sent;
                         }
-                        if (warp == 0 || warp == 2) PROF(2, it, 1);
                         if (!kFp8) {
 #pragma unroll
                             for (int j = 0; j < NP; ++j) pk[0][j] = ps[j];
@@ -811,7 +782,6 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                             }
                         }
                     }
-                    if (warp == 0 || warp == 2) PROF(4, it, 1);
                 }
                 // ---- hand P to the MMA warp: after the P V product that last read this tile's P buffer
                 if (it >= kBufReuse<kFp8>)
@@ -842,7 +812,6 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&ctl->p_full[tb]));
-                if (warp == 0 || warp == 2) { if (own) PROF(2, it, 3); else PROF(3, it, 3); }
             }
             // ---- epilogue of the item (all sixteen warps)
             {
@@ -969,15 +938,12 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     if (!warp_wait(smem_u32(&ctl->s_empty[buf_of<kFp8>(it - kBufReuse<kFp8>)]), phase_of<kFp8>(it - kBufReuse<kFp8>), abort_flag))
                         goto done;
                 tc_fence_after();
-                PROF(1, it, 0);
                 const uint64_t k_desc = k_desc0 + static_cast<uint64_t>((s * kKvTileBytes) >> 4);
                 const uint32_t d0 = tmem + s_col_of<kFp8>(it);
                 if (half) issue_qk_mmas<kFp8, 5>(d0, q_desc, tmem + kColQ, k_desc, el);
                 else issue_qk_mmas<kFp8, 4>(d0, q_desc, tmem + kColQ, k_desc, el);
-                PROF(7, it, 0);
                 tc_commit_el(smem_u32(&ctl->s_full[sb]), el);
                 if (t + 1 == n_tiles) tc_commit_el(smem_u32(&ctl->q_empty), el);
-                PROF(1, it, 1);
             }
         }
     } else if (warp == pv_warp) {
@@ -1000,15 +966,11 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (t == 0 && item_n > 0)   // the previous item's O has been read out
                     if (!warp_wait(smem_u32(&ctl->o_free), (item_n - 1) & 1, abort_flag)) goto done;
                 tc_fence_after();
-                PROF(1, it, 2);
                 issue_pv_mmas<kFp8>(tmem + kColO, tmem + p_col_of<kFp8>(it),
                                     v_desc0 + static_cast<uint64_t>((s * kKvTileBytes) >> 4), t == 0, el);
-                PROF(6, it, 0);
                 tc_commit_el(smem_u32(&ctl->kv_empty[s]), el);
-                PROF(6, it, 1);
                 tc_commit_el(smem_u32(&ctl->pv_done[sb]), el);
                 if (t + 1 == n_tiles) tc_commit_el(smem_u32(&ctl->o_full), el);
-                PROF(1, it, 3);
             }
         }
     } else if (!kFp8) {
@@ -1062,9 +1024,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     const int row_of_lane8 = __shfl_sync(0xffffffffu, row, (lane & 7) * 4);
                     const uint32_t mask8 = __ballot_sync(0xffffffffu, row_of_lane8 >= 0) & 0xFFu;
                     const int s = it % S;
-                    if (lw == 0) PROF(0, it, 1);
                     if (!warp_wait(smem_u32(&ctl->kv_empty[s]), ((it / S) & 1) ^ 1, abort_flag)) goto done;
-                    if (lw == 0) PROF(0, it, 2);
                     const uint32_t bar = smem_u32(&ctl->kv_full[s]);
                     if (lane == 0) mask_bytes[(it % kMaskSlots) * 4 + l4] = static_cast<uint8_t>(mask8);
                     // padding / out-of-range rows: nothing is read, the row is filled with zeros
@@ -1078,7 +1038,6 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                             cp_async_16(dst_row + (cc >> 3) * kKvBlockBytes + (((cc & 7) ^ (r & 7)) << 4), src + cc * 16, nbytes);
                     }
                     cp_async_mbar_arrive_noinc(bar);
-                    if (lw == 0) PROF(0, it, 0);
                 }
                 it_base += n_tiles;
             }
@@ -1118,7 +1077,6 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             for (int u = u0; u < n_tiles; u += 2) {
                 const uint32_t it = it_base + u;
                 const int k0 = wi.k_begin + u * kTileRows;
-                if (iw == 0) PROF(0, it, 1);
                 const int row = row_of(idx_a, phys_a, seq, p);
                 {
                     const int phys_n = block_of(idx_c, seq, p);
@@ -1135,7 +1093,6 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const int r3 = __shfl_sync(0xffffffffu, coord, 4 * gl + 3);
                 const int rs = it % R;
                 if (!warp_wait(smem_u32(&ctl->raw_empty[rs]), ((it / R) & 1) ^ 1, abort_flag)) goto done;
-                if (iw == 0) PROF(0, it, 2);
                 const uint32_t bar = smem_u32(&ctl->raw_full[rs]);
                 if (lane == 0) {
                     ctl->tile_mask[it % kMaskSlots] = mask;
@@ -1155,8 +1112,6 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     const uint32_t dst = smem_u32(sRaw + rs * kRawTileBytes + lane * kRawGroupBytes);
                     tma_gather4(dst, tmap, bar, tcol, r0, r1, r2, r3);
                 }
-                if (iw == 0) PROF(0, it, 0);
-                if (iw == 1) PROF(5, it, 3);
             }
             it_base += n_tiles;
         }
@@ -1198,9 +1153,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if ((it & 1u) != static_cast<uint32_t>(grp)) continue;
                 const int rs = it % R, s = it % S;
                 if (!warp_wait(smem_u32(&ctl->raw_full[rs]), (it / R) & 1, abort_flag)) goto done;
-                if (cw == 4) PROF(5, it, 2);
                 if (!warp_wait(smem_u32(&ctl->kv_empty[s]), ((it / S) & 1) ^ 1, abort_flag)) goto done;
-                if (cw == 4) PROF(5, it, 0);
                 const uint8_t* row_raw = sRaw + rs * kRawTileBytes + (r >> 2) * kRawGroupBytes + (r & 3) * row_bytes;
                 const uint8_t* src = row_raw + qd * 64;
                 uint8_t* dst_row = sKV + s * kKvTileBytes + qd * kKvBlockBytes + r * 128;
@@ -1235,7 +1188,6 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     mbar_arrive(smem_u32(&ctl->kv_full[s]));
                     mbar_arrive(smem_u32(&ctl->raw_empty[rs]));
                 }
-                if (cw == 4) PROF(5, it, 1);
             }
         }
     }
@@ -1246,13 +1198,7 @@ done:
     tc_fence_before();
     __syncthreads();
     if (tid == 0 && ctl->abort_flag) atomicExch(p.status, DSA_V32_ERR_DEVICE_WAIT);
-    if (tid == 0) PROF(5, kProfTile0 + 10, 2);
-#ifdef DSA_PROFILE
-    if (prof_on)
-        for (int i = tid; i < 8 * kProfTiles * 4; i += blockDim.x) g_prof[(blockIdx.x & 1) * 8 * kProfTiles * 4 + i] = s_prof[i];
-#endif
     cluster_sync_all();
-    if (tid == 0) PROF(5, kProfTile0 + 10, 3);   // nobody leaves while the peer may still store into this CTA's shared memory
     if (warp == kMmaWarp) {
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);

@@ -1,4 +1,6 @@
-"""Partitioning and cross-rank reduction logic, run as two CPU ranks over gloo."""
+"""Partitioning and cross-rank reduction logic, run as two CPU ranks over gloo: index arithmetic, the
+maximum over ranks, the gather layout, and - with the CPU oracle standing in for the kernels - that head,
+sequence and query-chunk shards computed on separate ranks reassemble to the single-rank result."""
 import os
 import socket
 
@@ -50,7 +52,46 @@ def _worker(rank, world, port, ret):
         full = torch.arange(rows * H * D, dtype=torch.float32).view(rows, H, D)
         h0, h1 = shard.shard_heads(H, world, rank)
         gathered = shard.all_gather_heads(full[:, h0:h1].clone(), world)
-        ret[rank] = (mx, bool(torch.equal(gathered, full)))
+        # the three partitions of the path on a tiny problem: every rank runs the oracle on its shard only,
+        # the shards are exchanged, and the reassembled result must equal the oracle's on the whole problem
+        from oracle import build as obuild
+        obuild.build_oracle()
+        from oracle import oracle as O
+        from opfoundry_b200 import synth
+        scale = 0.07
+        case = synth.make_decode_case(4, 8, 64, 16, s_q=2, seed=5)          # 8 query rows, 8 heads, bf16 cache
+        run = lambda q, idx, s_q=2: O.sparse_mla(q, case["kv"], idx, scale, s_q=s_q, kv_batch_stride_rows=case["kv_batch_stride_rows"],
+                                                 num_threads=1)
+        want_out, want_lse = run(case["q"], case["indices"])
+
+        def gather_np(a, dim):
+            t = torch.from_numpy(np.ascontiguousarray(a).astype(np.float32))
+            parts = [torch.empty_like(t) for _ in range(world)]
+            dist.all_gather(parts, t)
+            return torch.cat(parts, dim=dim).numpy()
+
+        # heads: rank r computes heads [h0, h1) of every row
+        h0, h1 = shard.shard_heads(8, world, rank)
+        o, l = run(np.ascontiguousarray(case["q"][:, h0:h1]), case["indices"])
+        ok_heads = np.array_equal(gather_np(o, 1), want_out.astype(np.float32)) and np.array_equal(gather_np(l, 1), want_lse)
+        # sequences: rank r computes its sequences (both query rows of each)
+        b0, b1 = shard.shard_batch(4, world, rank)
+        sel = np.zeros((8, 16), np.int32) - 1
+        sel[2 * b0:2 * b1] = case["indices"][2 * b0:2 * b1]                 # rows of other ranks: empty lists, ignored below
+        o, l = run(case["q"], sel)
+        ok_batch = np.array_equal(gather_np(o[2 * b0:2 * b1], 0), want_out.astype(np.float32)) and \
+            np.array_equal(gather_np(l[2 * b0:2 * b1], 0), want_lse)
+        # query chunks of a causal prefill: contiguous ranges of equal work
+        pre = synth.make_prefill_case(24, 8, 8, seed=3)
+        p_out, p_lse = O.sparse_mla(pre["q"], pre["kv"], pre["indices"], scale, s_q=24, num_threads=1)
+        bounds = shard.shard_queries_equal_work(pre["valid_len"], world)
+        sub = np.arange(bounds[rank], bounds[rank + 1], dtype=np.int32)
+        c_out, c_lse = O.sparse_mla(pre["q"], pre["kv"], pre["indices"], scale, s_q=24, subset=sub, num_threads=1)
+        mine = torch.zeros(24, 8, 512)
+        mine[sub] = torch.from_numpy(c_out[sub].astype(np.float32))
+        dist.all_reduce(mine)                                               # disjoint rows: the sum is the concatenation
+        ok_chunks = np.array_equal(mine.numpy(), p_out.astype(np.float32)) and sum(bounds[i + 1] - bounds[i] for i in range(world)) == 24
+        ret[rank] = (mx, bool(torch.equal(gathered, full)), bool(ok_heads), bool(ok_batch), bool(ok_chunks))
     finally:
         dist.destroy_process_group()
 
@@ -63,3 +104,7 @@ def test_two_ranks_gloo():
     mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
     assert ret[0][0] == [11.0, 5.0] and ret[1][0] == [11.0, 5.0]
     assert ret[0][1] and ret[1][1]
+    for r in range(world):
+        assert ret[r][2], "head shards do not reassemble to the oracle's result"
+        assert ret[r][3], "sequence shards do not reassemble to the oracle's result"
+        assert ret[r][4], "query chunks do not reassemble to the oracle's result"

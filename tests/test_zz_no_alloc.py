@@ -31,7 +31,7 @@ def test_static_scratch_matches_regular_pipeline_twice(built_lib, fp8):
     tol = TOL_FP8 if fp8 else TOL_BF16
     # two different problems of the same shape, run back to back through the shared array
     cases = [synth.make_decode_case(6, 128, 2048, 700, fp8=fp8, paged=True, pad_frac=0.1, seed=900 + i) for i in range(2)]
-    for case in cases:
+    for n_call, case in enumerate(cases):
         d = to_dev(case)
         plan = api.mla_decode_plan_create(6, 128, 700, 1)
         assert plan.info.num_partials > 0          # the shape really uses split scratch
@@ -39,9 +39,15 @@ def test_static_scratch_matches_regular_pipeline_twice(built_lib, fp8):
                                                           block_table=d["block_table"], page_block_size=64)
         out = torch.full((6, 128, 512), float("nan"), dtype=torch.bfloat16, device="cuda")
         lse = torch.full((6, 128), float("nan"), dtype=torch.float32, device="cuda")
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         api.mla_decode_launch_pipeline_static(d["q"], d["kv"], d["indices"], SCALE, block_table=d["block_table"],
                                               page_block_size=64, out=out, lse=lse)
         torch.cuda.synchronize()
+        if n_call > 0:
+            # the property in the entry point's name: with the outputs handed in, a call leaves the device's free
+            # memory where it was (the first call on a device may still load the library's image with its array)
+            assert torch.cuda.mem_get_info()[0] == free_before
         check_out(_bits(out), _bits(ref_out), **tol)
         check_lse(lse.cpu().numpy(), ref_lse.cpu().numpy())
 

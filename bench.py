@@ -403,6 +403,46 @@ def cfg4_problem(env, seq_begin, seq_end, n_batches=2):
     return W
 
 
+def fused_gather_leg(env, mode, W, plan, step_in, out, lse, gathered, attn_gather, steps, warmup, status_args, s0, h0, total_q):
+    """The config-4 step with the gather fused into the kernels: finished rows are stored straight into every
+    peer's gathered buffer (peer-mapped pointers, plain stores), then one flag round.  Returns (ms per step,
+    whether one more step of it equals attention + NCCL all-gather bit for bit on every rank)."""
+    from opfoundry_b200 import shard
+    torch, api, dist = env.torch, env.api, env.dist
+    c = CFG4
+    pg = shard.PeerGather(c["B"] * c["s_q"], c["H"])
+    try:
+        row0 = s0 * c["s_q"]
+        fused_args = []
+        for q, idx in step_in:
+            a = api.make_args(q, W["cache"], idx, plan, SM_SCALE, out=out, lse=lse, block_table=W["block_table"], page_block_size=c["page"])
+            a.stride_o_row, a.stride_o_head = pg.out.stride(0), pg.out.stride(1)
+            fused_args.append(a)
+
+        def fused(i):
+            po = pg.targets(row0, h0)
+            api._check(env.L.dsa_v32_decode_pipeline_allgather(C.byref(fused_args[i % len(fused_args)]), C.byref(po), env.stream()),
+                       "fused decode step")
+
+        ms_fused = env.timed(fused, steps, warmup, status_args)
+        # same numbers as the NCCL path: one more step of each on the same inputs
+        attn_gather(0)
+        fused(0)
+        torch.cuda.synchronize()
+        dist.barrier()
+        if mode == "tp":
+            ref = gathered.permute(1, 0, 2, 3).reshape(total_q, c["H"], D_V)          # [rank, q, heads, d] -> [q, H, d]
+        else:
+            ref = gathered.reshape(c["B"] * c["s_q"], c["H"], D_V)
+        same = bool(torch.equal(ref.view(torch.int16), pg.out.view(torch.int16)))
+        t = torch.tensor([1.0 if same else 0.0], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return ms_fused, bool(t.item() > 0.5)
+    finally:
+        torch.cuda.synchronize()
+        pg.close()
+
+
 def cfg4_leg(env, mode, steps, warmup):
     """mode "tp": every rank attends all 128 x 2 query rows with its 128 / N heads over the replicated cache;
     mode "batch": every rank attends its 128 / N sequences with all 128 heads over its own sequences' cache.
@@ -443,41 +483,17 @@ def cfg4_leg(env, mode, steps, warmup):
     ms_full = env.timed(attn_gather, steps, warmup, arg_sets[0]) if world > 1 else ms_attn
     # the same step with the gather fused into the kernels: finished rows are stored straight into every
     # peer's gathered buffer (peer-mapped pointers, plain stores), then one flag round
-    ms_fused, fused_ok = None, None
+    ms_fused, fused_ok, fused_note = None, None, None
     if world > 1:
-        pg = shard.PeerGather(c["B"] * c["s_q"], c["H"])
-        row0 = s0 * c["s_q"]
-        fused_args = []
-        for q, idx in step_in:
-            a = api.make_args(q, W["cache"], idx, plan, SM_SCALE, out=out, lse=lse, block_table=W["block_table"], page_block_size=c["page"])
-            a.stride_o_row, a.stride_o_head = pg.out.stride(0), pg.out.stride(1)
-            fused_args.append(a)
-
-        def fused(i):
-            po = pg.targets(row0, h0)
-            api._check(env.L.dsa_v32_decode_pipeline_allgather(C.byref(fused_args[i % len(fused_args)]), C.byref(po), env.stream()),
-                       "fused decode step")
-
-        ms_fused = env.timed(fused, steps, warmup, arg_sets[0])
-        # same numbers as the NCCL path: one more step of each on the same inputs
-        attn_gather(0)
-        fused(0)
-        torch.cuda.synchronize()
-        dist.barrier()
-        if mode == "tp":
-            ref = gathered.permute(1, 0, 2, 3).reshape(total_q, c["H"], D_V)          # [q, rank, heads, d] -> [q, H, d]
-        else:
-            ref = gathered.reshape(c["B"] * c["s_q"], c["H"], D_V)
-        fused_ok = bool(torch.equal(ref.view(torch.int16), pg.out.view(torch.int16)))
-        t = torch.tensor([1.0 if fused_ok else 0.0], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MIN)
-        fused_ok = bool(t.item() > 0.5)
-        dist.barrier()
-        pg.close()
-        dist.barrier()
-        del pg, fused_args
-    clocks = env.sampler.summary()
-    pk = peaks()
+        try:
+            ms_fused, fused_ok = fused_gather_leg(env, mode, W, plan, step_in, out, lse, gathered, attn_gather, steps, warmup,
+                                                  arg_sets[0], s0, h0, total_q)
+        except Exception as ex:          # the NCCL number stands on its own; say why the fused one is missing
+            ms_fused, fused_ok, fused_note = None, False, "%s: %s" % (type(ex).__name__, ex)
+        ok = torch.tensor([0.0 if ms_fused is None else 1.0], device="cuda")
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() < 0.5:
+            ms_fused = None
     ms_step = ms_fused if ms_fused is not None else ms_full
     pairs_total = float(c["B"] * c["s_q"] * c["topk"])
     flops_total = flops_of(pairs_total, c["H"])
@@ -488,6 +504,7 @@ def cfg4_leg(env, mode, steps, warmup):
                  heads_per_gpu=Hl, sequences_per_gpu=nseq, shared_list_fraction=W["share_frac"],
                  ms_per_step=ms_step, ms_per_step_without_gather=ms_attn, ms_per_step_nccl_gather=ms_full,
                  ms_per_step_fused_gather=ms_fused, nccl_all_gather_ms=ms_full - ms_attn, fused_equals_nccl=fused_ok,
+                 fused_gather_note=fused_note,
                  gather="stores into the peers' gathered buffers from the attention kernels + one flag round (the NCCL all-gather "
                         "is timed beside it as the cross-check)" if world > 1 else "none (one GPU)",
                  all_gather_bytes_per_gpu=(out.numel() * 2 if world > 1 else 0),
@@ -504,11 +521,13 @@ def cfg4_leg(env, mode, steps, warmup):
 
 
 # --------------------------------------------------------------------------- host-buffer leg of the headline
-def e2e_leg(env, W, plan, out, lse, K):
-    """K steps through the host-buffer C-ABI call: pinned host q / index lists in, out / lse back,
-    the caller synchronising on every step's result."""
+def e2e_leg(env, W, out, lse, K, num_chunks):
+    """K steps through the host-buffer C-ABI call: pinned host q / index lists in, out / lse back, the caller
+    synchronising on every step's result.  num_chunks > 1: the call that cuts the batch into groups of
+    sequences whose PCIe copies overlap the other groups' kernels (its plan is for one group's shape)."""
     api, torch = env.api, env.torch
     B, H = W["B"], W["H"]
+    plan = api.mla_decode_plan_create(B // num_chunks, H, W["topk"], 1, valid_len_hint=[W["n_valid"]] * (B // num_chunks))
     q_host = [q.cpu().pin_memory() for (q, _) in W["steps"]]
     i_host = [idx.cpu().pin_memory() for (_, idx) in W["steps"]]
     out_host = torch.empty(B, H, D_V, dtype=torch.bfloat16).pin_memory()
@@ -518,12 +537,14 @@ def e2e_leg(env, W, plan, out, lse, K):
     a_e2e = api.make_args(q_dev, W["cache"], i_dev, plan, SM_SCALE, out=out, lse=lse, block_table=W["block_table"],
                           page_block_size=W["page"])
     for i in range(3):
-        api.mla_decode_step_host(a_e2e, q_host[i % len(q_host)], i_host[i % len(i_host)], out_host, lse_host)
+        api.mla_decode_step_host(a_e2e, q_host[i % len(q_host)], i_host[i % len(i_host)], out_host, lse_host, num_chunks)
+    torch.cuda.synchronize()
+    api._check(env.L.dsa_v32_device_status(C.byref(a_e2e), env.stream()), "device status (host-buffer leg)")
     g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     env.barrier()
     g0.record()
     for i in range(K):
-        api.mla_decode_step_host(a_e2e, q_host[i % len(q_host)], i_host[i % len(i_host)], out_host, lse_host)
+        api.mla_decode_step_host(a_e2e, q_host[i % len(q_host)], i_host[i % len(i_host)], out_host, lse_host, num_chunks)
         torch.cuda.current_stream().synchronize()   # the caller reads the step's result before the next step
     g1.record()
     env.barrier()
@@ -584,14 +605,16 @@ def headline_leg(env, args):
     api._check(L.dsa_v32_device_status(C.byref(arg_sets[0]), env.stream()), "device status after the timed region")
     clocks = env.sampler.summary()
 
-    e2e_ms, h2d, d2h = float("nan"), 0, 0
+    e2e_ms, e2e1_ms, h2d, d2h = float("nan"), float("nan"), 0, 0
+    e2e_chunks = 4 if B % 4 == 0 and B >= 16 else 1
     if not args.no_e2e:
-        e2e_ms, h2d, d2h = e2e_leg(env, W, plan, out, lse, K)
+        e2e1_ms, h2d, d2h = e2e_leg(env, W, out, lse, K, 1)
+        e2e_ms = e2e_leg(env, W, out, lse, K, e2e_chunks)[0] if e2e_chunks > 1 else e2e1_ms
 
-    t = torch.tensor([total_ms, attn_ms, e2e_ms], dtype=torch.float64, device="cuda")
+    t = torch.tensor([total_ms, attn_ms, e2e_ms, e2e1_ms], dtype=torch.float64, device="cuda")
     if env.world > 1:
         env.dist.all_reduce(t, op=env.dist.ReduceOp.MAX)
-    total_ms, attn_ms, e2e_ms = (float(x) for x in t.tolist())
+    total_ms, attn_ms, e2e_ms, e2e1_ms = (float(x) for x in t.tolist())
     world = env.world
     pk = peaks()
     ms_per_step = total_ms / K
@@ -610,7 +633,10 @@ def headline_leg(env, args):
                               t_flop_us=step_flops / (pk["bf16_tflops"] * 1e12) * 1e6,
                               t_mem_us=gathered / (pk["hbm_gbs"] * 1e9) * 1e6),
                 e2e=None if args.no_e2e else dict(value=world * step_flops / (e2e_ms / K * 1e-3) / 1e12, unit="TFLOP/s",
-                                                  ms_per_step=e2e_ms / K, h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
+                                                  ms_per_step=e2e_ms / K, h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
+                                                  call="dsa_v32_decode_pipeline_host_chunked, %d groups of sequences "
+                                                       "(copies overlap the other groups' kernels)" % e2e_chunks,
+                                                  ms_per_step_unchunked=e2e1_ms / K),
                 gpu_launches=K * (2 if plan.info.num_partials > 0 else 1), clocks=clocks)
     del W, plan, out, lse, arg_sets
     env.free()
@@ -650,7 +676,9 @@ def main():
     torch.cuda.set_device(local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        import datetime
+        # a short collective timeout: a rank that fails must not hold the others for the default ten minutes
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=90))
     if not os.path.exists(api.LIB_PATH):
         if rank == 0:
             build.build()

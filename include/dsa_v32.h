@@ -248,6 +248,18 @@ typedef struct dsa_v32_host_io {
     int64_t out_bytes;
 } dsa_v32_host_io;
 int dsa_v32_decode_pipeline_host(const dsa_v32_attn_args* args, const dsa_v32_host_io* io, void* stream);
+/*
+ * The same step cut into `num_chunks` equal groups of sequences so that the PCIe copies overlap the
+ * kernels: chunk c's queries and lists come in on an internal copy stream while chunk c-1 computes on
+ * `stream`, and its outputs leave on a second copy stream while chunk c+1 computes.  `args` describes the
+ * whole batch; `args->workspace` must be planned for ONE CHUNK's shape (total_q / num_chunks rows; the
+ * chunks run one after the other on `stream` and share it).  total_q must be a multiple of num_chunks * s_q;
+ * q / out / lse rows are taken as dense (row stride = stride_q_row / stride_o_row elements, lse [total_q, H]).
+ * The host buffers must stay valid, and `stream` complete, before the results are read.  The copy streams
+ * and events are created on the first call on a device and kept.
+ */
+int dsa_v32_decode_pipeline_host_chunked(const dsa_v32_attn_args* args, const dsa_v32_host_io* io, int32_t num_chunks,
+                                         void* stream);
 
 /*
  * The same pipeline for callers that cannot allocate device memory at all: code running where

@@ -63,7 +63,7 @@ EXPORTS = ["dsa_v32_abi_version", "dsa_v32_error_string", "dsa_v32_plan_info_get
            "dsa_v32_plan_host", "dsa_v32_plan_read", "dsa_v32_plan_release", "dsa_v32_decode_bf16", "dsa_v32_decode_fp8",
            "dsa_v32_prefill_bf16", "dsa_v32_combine", "dsa_v32_decode_pipeline", "dsa_v32_device_status",
            "dsa_v32_debug_rows", "dsa_v32_pack_fp8_rows", "dsa_v32_decode_pipeline_host",
-           "dsa_v32_decode_pipeline_static", "dsa_v32_static_scratch_address", "dsa_v32_selftest_wait_expiry", "dsa_v32_decode_pipeline_allgather", "dsa_v32_ipc_export", "dsa_v32_ipc_open", "dsa_v32_ipc_close"]
+           "dsa_v32_decode_pipeline_static", "dsa_v32_static_scratch_address", "dsa_v32_selftest_wait_expiry", "dsa_v32_decode_pipeline_allgather", "dsa_v32_ipc_export", "dsa_v32_ipc_open", "dsa_v32_ipc_close", "dsa_v32_decode_pipeline_host_chunked"]
 
 _lib = None
 
@@ -97,6 +97,7 @@ def lib():
         L.dsa_v32_decode_pipeline.argtypes = [C.POINTER(AttnArgs), C.c_int, C.c_void_p]
         L.dsa_v32_decode_pipeline_host.argtypes = [C.POINTER(AttnArgs), C.POINTER(HostIO), C.c_void_p]
         L.dsa_v32_decode_pipeline_static.argtypes = [C.POINTER(AttnArgs), C.c_void_p]
+        L.dsa_v32_decode_pipeline_host_chunked.argtypes = [C.POINTER(AttnArgs), C.POINTER(HostIO), C.c_int32, C.c_void_p]
         L.dsa_v32_decode_pipeline_allgather.argtypes = [C.POINTER(AttnArgs), C.POINTER(PeerOutputs), C.c_void_p]
         L.dsa_v32_ipc_export.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_int64)]
         L.dsa_v32_ipc_open.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
@@ -276,10 +277,12 @@ def pack_fp8_rows(latent, rope, out=None, dst_rows=None):
     return out
 
 
-def mla_decode_step_host(args, q_host, indices_host, out_host, lse_host):
+def mla_decode_step_host(args, q_host, indices_host, out_host, lse_host, num_chunks=1):
     """One serving step with pinned HOST tensors: H2D of q / indices, attention + merge, D2H of
     out / lse, all on the current stream (asynchronous; synchronise the stream to read results).
-    `args` comes from make_args and names the resident device buffers."""
+    `args` comes from make_args and names the resident device buffers.  num_chunks > 1 cuts the batch
+    into that many groups of sequences whose copies overlap the other groups' kernels; the plan in
+    `args` must then be for one group's shape (total_q / num_chunks rows)."""
     io = HostIO()
     io.q_host = q_host.data_ptr()
     io.indices_host = indices_host.data_ptr()
@@ -287,6 +290,10 @@ def mla_decode_step_host(args, q_host, indices_host, out_host, lse_host):
     io.lse_host = lse_host.data_ptr()
     io.q_bytes = q_host.numel() * q_host.element_size()
     io.out_bytes = out_host.numel() * out_host.element_size()
+    if num_chunks > 1:
+        _check(lib().dsa_v32_decode_pipeline_host_chunked(C.byref(args), C.byref(io), num_chunks, _stream()),
+               "dsa_v32_decode_pipeline_host_chunked")
+        return
     _check(lib().dsa_v32_decode_pipeline_host(C.byref(args), C.byref(io), _stream()), "dsa_v32_decode_pipeline_host")
 
 

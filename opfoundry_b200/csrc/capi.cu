@@ -524,6 +524,93 @@ int dsa_v32_decode_pipeline_host(const dsa_v32_attn_args* a, const dsa_v32_host_
     return DSA_V32_OK;
 }
 
+// ------------------------------------------------------------------ host-buffer pipeline in chunks
+// Copy streams and events of the chunked host-buffer call, created once per device and kept.
+namespace {
+struct ChunkStreams {
+    cudaStream_t in = nullptr, out = nullptr;
+    std::vector<cudaEvent_t> ev;   // start, done, then (copied-in, computed) per chunk
+    cudaError_t ensure(size_t n_events) {
+        cudaError_t e;
+        if (!in && (e = cudaStreamCreateWithFlags(&in, cudaStreamNonBlocking)) != cudaSuccess) return e;
+        if (!out && (e = cudaStreamCreateWithFlags(&out, cudaStreamNonBlocking)) != cudaSuccess) return e;
+        while (ev.size() < n_events) {
+            cudaEvent_t x;
+            if ((e = cudaEventCreateWithFlags(&x, cudaEventDisableTiming)) != cudaSuccess) return e;
+            ev.push_back(x);
+        }
+        return cudaSuccess;
+    }
+};
+std::mutex g_chunk_mu;
+ChunkStreams g_chunk_streams[64];
+}  // namespace
+
+int dsa_v32_decode_pipeline_host_chunked(const dsa_v32_attn_args* a, const dsa_v32_host_io* io, int32_t num_chunks, void* stream) {
+    if (!a || !io) return DSA_V32_ERR_NULL;
+    if (num_chunks <= 1) return dsa_v32_decode_pipeline_host(a, io, stream);
+    if (num_chunks > 64 || a->s_q <= 0 || a->total_q % (num_chunks * a->s_q) != 0) return DSA_V32_ERR_SHAPE;
+    if (!io->q_host || !io->indices_host || !io->out_host) return DSA_V32_ERR_NULL;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return DSA_V32_ERR_SHAPE;
+    std::lock_guard<std::mutex> guard(g_chunk_mu);
+    ChunkStreams& cs = g_chunk_streams[dev];
+    e = cs.ensure(2 + 2 * size_t(num_chunks));
+    if (e != cudaSuccess) return (int)e;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int rows = a->total_q / num_chunks;          // query rows per chunk
+    const int seqs = rows / a->s_q;
+    const size_t q_row_bytes = size_t(a->stride_q_row) * 2, o_row_bytes = size_t(a->stride_o_row) * 2;
+    // everything queued on `stream` before this call precedes the first copy
+    if ((e = cudaEventRecord(cs.ev[0], st)) != cudaSuccess) return (int)e;
+    if ((e = cudaStreamWaitEvent(cs.in, cs.ev[0], 0)) != cudaSuccess) return (int)e;
+    if ((e = cudaStreamWaitEvent(cs.out, cs.ev[0], 0)) != cudaSuccess) return (int)e;
+    for (int c = 0; c < num_chunks; ++c) {
+        const size_t r0 = size_t(c) * rows;
+        dsa_v32_attn_args b = *a;
+        b.total_q = rows;
+        b.q = reinterpret_cast<const uint8_t*>(a->q) + r0 * q_row_bytes;
+        b.out = reinterpret_cast<uint8_t*>(a->out) + r0 * o_row_bytes;
+        b.lse = a->lse ? a->lse + r0 * a->H : nullptr;
+        b.indices = a->indices + r0 * a->topk;
+        if (a->block_table) {
+            b.block_table = a->block_table + size_t(c) * seqs * a->block_table_stride;
+        } else {   // contiguous cache: the chunk's sequences start kv_batch_stride_rows * seqs rows further on
+            const size_t row_bytes = a->kv_dtype == DSA_V32_KV_FP8 ? size_t(DSA_V32_FP8_ROW_BYTES) : size_t(DSA_V32_BF16_ROW_BYTES);
+            const int64_t skip = int64_t(c) * seqs * a->kv_batch_stride_rows;
+            b.kv = reinterpret_cast<const uint8_t*>(a->kv) + size_t(skip) * row_bytes;
+            b.num_kv_rows = a->num_kv_rows - skip;
+        }
+        // this chunk's queries and lists come in on the copy stream while the chunk before computes
+        e = cudaMemcpyAsync(const_cast<void*>(b.q), reinterpret_cast<const uint8_t*>(io->q_host) + r0 * q_row_bytes,
+                            size_t(rows) * q_row_bytes, cudaMemcpyHostToDevice, cs.in);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaMemcpyAsync(const_cast<int32_t*>(b.indices), io->indices_host + r0 * a->topk, size_t(rows) * a->topk * 4,
+                            cudaMemcpyHostToDevice, cs.in);
+        if (e != cudaSuccess) return (int)e;
+        if ((e = cudaEventRecord(cs.ev[2 + 2 * c], cs.in)) != cudaSuccess) return (int)e;
+        if ((e = cudaStreamWaitEvent(st, cs.ev[2 + 2 * c], 0)) != cudaSuccess) return (int)e;
+        int rc = dsa_v32_decode_pipeline(&b, 0, stream);
+        if (rc) return rc;
+        // ... and its outputs leave on the other copy stream while the next chunk computes
+        if ((e = cudaEventRecord(cs.ev[3 + 2 * c], st)) != cudaSuccess) return (int)e;
+        if ((e = cudaStreamWaitEvent(cs.out, cs.ev[3 + 2 * c], 0)) != cudaSuccess) return (int)e;
+        e = cudaMemcpyAsync(reinterpret_cast<uint8_t*>(io->out_host) + r0 * o_row_bytes, b.out, size_t(rows) * o_row_bytes,
+                            cudaMemcpyDeviceToHost, cs.out);
+        if (e != cudaSuccess) return (int)e;
+        if (io->lse_host && b.lse) {
+            e = cudaMemcpyAsync(io->lse_host + r0 * a->H, b.lse, size_t(rows) * a->H * 4, cudaMemcpyDeviceToHost, cs.out);
+            if (e != cudaSuccess) return (int)e;
+        }
+    }
+    // the call's work is complete when `stream` is: it waits for the last copy out
+    if ((e = cudaEventRecord(cs.ev[1], cs.out)) != cudaSuccess) return (int)e;
+    if ((e = cudaStreamWaitEvent(st, cs.ev[1], 0)) != cudaSuccess) return (int)e;
+    return DSA_V32_OK;
+}
+
 // ------------------------------------------------------------------ no-allocation variant
 // Scratch for callers that may not allocate: lives in the library's device image.  In host code the
 // name below is only a handle for the runtime; the device address comes from cudaGetSymbolAddress.

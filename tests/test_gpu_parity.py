@@ -263,3 +263,28 @@ def test_mtp_shared_lists_stacked_rows(oracle, fp8, H, s_q):
         r_out, r_lse = run_oracle(oracle, case, SCALE)
         check_out(g_out, r_out, **(TOL_FP8 if fp8 else TOL_BF16))
         check_lse(g_lse, r_lse)
+
+
+@pytest.mark.parametrize("fp8", [True, False])
+def test_host_buffer_pipeline_in_chunks(oracle, fp8):
+    """The chunked host-buffer call (copies overlapped with the other chunks' kernels) against the oracle:
+    pinned host inputs in, host outputs back, for a paged fp8 cache and a contiguous bf16 cache."""
+    from gpu_util import to_dev, run_oracle
+    B, H, topk = 8, 128, 256
+    case = synth.make_decode_case(B, H, 1024, topk, fp8=fp8, paged=fp8, pad_frac=0.1, seed=77)
+    d = to_dev(case)
+    for chunks in (2, 4):
+        plan = api.mla_decode_plan_create(B // chunks, H, topk, 1)
+        out = torch.full((B, H, 512), float("nan"), dtype=torch.bfloat16, device="cuda")
+        lse = torch.full((B, H), float("nan"), dtype=torch.float32, device="cuda")
+        q_dev, i_dev = torch.zeros_like(d["q"]), torch.zeros_like(d["indices"])
+        a = api.make_args(q_dev, d["kv"], i_dev, plan, SCALE, out=out, lse=lse, block_table=d["block_table"],
+                          page_block_size=case["page_block_size"], kv_batch_stride_rows=case["kv_batch_stride_rows"])
+        q_host, i_host = d["q"].cpu().pin_memory(), d["indices"].cpu().pin_memory()
+        out_host = torch.zeros(B, H, 512, dtype=torch.bfloat16).pin_memory()
+        lse_host = torch.zeros(B, H, dtype=torch.float32).pin_memory()
+        api.mla_decode_step_host(a, q_host, i_host, out_host, lse_host, num_chunks=chunks)
+        torch.cuda.current_stream().synchronize()
+        r_out, r_lse = run_oracle(oracle, case, SCALE)
+        check_out(out_host.view(torch.int16).numpy().view(np.uint16), r_out, **(TOL_FP8 if fp8 else TOL_BF16))
+        check_lse(lse_host.numpy(), r_lse)

@@ -494,6 +494,8 @@ def cfg4_leg(env, mode, steps, warmup):
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         if ok.item() < 0.5:
             ms_fused = None
+    clocks = env.sampler.summary()
+    pk = peaks()
     ms_step = ms_fused if ms_fused is not None else ms_full
     pairs_total = float(c["B"] * c["s_q"] * c["topk"])
     flops_total = flops_of(pairs_total, c["H"])

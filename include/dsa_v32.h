@@ -194,6 +194,26 @@ int dsa_v32_combine(const dsa_v32_attn_args* args, void* stream);
 int dsa_v32_decode_pipeline(const dsa_v32_attn_args* args, int run_plan, void* stream);
 
 /*
+ * The pipeline with the two features of the reference's v4 prefill kernels
+ * (opus_attn/dsa_v4/common/mla_v4_host.cc:455-532, dsa_v4/README.md "Attention Model"):
+ *   attn_sink   device array [H] of fp32 or NULL: exp(sink[h]) joins the softmax denominator of every query row
+ *               of head h (scaled-score units, as in mla_v4_host.cc:469-472); lse includes it, and a row without
+ *               any valid position gets out = 0, lse = sink[h].  (The running maximum of the scores stays the
+ *               reference of the exponentials: a sink more than ~88 above every score of a row overflows.)
+ *   kv2, pool_split, num_kv2_rows   a second pool of bf16 rows (the v4 "extend" rows: K/V produced by the current
+ *               chunk, next to the cache of earlier state): slots k >= pool_split[q] of query row q hold PHYSICAL
+ *               rows of kv2, the slots before it positions in args->kv as usual.  bf16 caches only.
+ * The work list of a split query must start its first piece at slot 0 (every plan does).
+ */
+typedef struct dsa_v32_v4_ext {
+    const float* attn_sink;
+    const void* kv2;
+    const int32_t* pool_split; /* device array [total_q] */
+    int64_t num_kv2_rows;
+} dsa_v32_v4_ext;
+int dsa_v32_decode_pipeline_v4(const dsa_v32_attn_args* args, const dsa_v32_v4_ext* ext, void* stream);
+
+/*
  * The pipeline fused with the all-gather that follows it when the heads or the sequences are sharded over
  * the GPUs of one box: instead of args->out / args->lse the kernels store every finished output row
  * straight into the gathered buffers of all peers (this GPU's own among them) through peer-mapped

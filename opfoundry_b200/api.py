@@ -44,6 +44,10 @@ class PeerOutputs(C.Structure):
                 ("flags", C.c_void_p * MAX_PEERS), ("lse_stride_row", C.c_int64), ("step", C.c_uint32), ("_pad", C.c_uint32)]
 
 
+class V4Ext(C.Structure):
+    _fields_ = [("attn_sink", C.c_void_p), ("kv2", C.c_void_p), ("pool_split", C.c_void_p), ("num_kv2_rows", C.c_int64)]
+
+
 class AttnArgs(C.Structure):
     _fields_ = [("q", C.c_void_p), ("kv", C.c_void_p), ("out", C.c_void_p), ("lse", C.c_void_p),
                 ("indices", C.c_void_p), ("block_table", C.c_void_p), ("workspace", C.c_void_p),
@@ -63,7 +67,7 @@ EXPORTS = ["dsa_v32_abi_version", "dsa_v32_error_string", "dsa_v32_plan_info_get
            "dsa_v32_plan_host", "dsa_v32_plan_read", "dsa_v32_plan_release", "dsa_v32_decode_bf16", "dsa_v32_decode_fp8",
            "dsa_v32_prefill_bf16", "dsa_v32_combine", "dsa_v32_decode_pipeline", "dsa_v32_device_status",
            "dsa_v32_debug_rows", "dsa_v32_pack_fp8_rows", "dsa_v32_decode_pipeline_host",
-           "dsa_v32_decode_pipeline_static", "dsa_v32_static_scratch_address", "dsa_v32_selftest_wait_expiry", "dsa_v32_decode_pipeline_allgather", "dsa_v32_ipc_export", "dsa_v32_ipc_open", "dsa_v32_ipc_close", "dsa_v32_decode_pipeline_host_chunked"]
+           "dsa_v32_decode_pipeline_static", "dsa_v32_static_scratch_address", "dsa_v32_selftest_wait_expiry", "dsa_v32_decode_pipeline_allgather", "dsa_v32_ipc_export", "dsa_v32_ipc_open", "dsa_v32_ipc_close", "dsa_v32_decode_pipeline_host_chunked", "dsa_v32_decode_pipeline_v4"]
 
 _lib = None
 
@@ -97,6 +101,7 @@ def lib():
         L.dsa_v32_decode_pipeline.argtypes = [C.POINTER(AttnArgs), C.c_int, C.c_void_p]
         L.dsa_v32_decode_pipeline_host.argtypes = [C.POINTER(AttnArgs), C.POINTER(HostIO), C.c_void_p]
         L.dsa_v32_decode_pipeline_static.argtypes = [C.POINTER(AttnArgs), C.c_void_p]
+        L.dsa_v32_decode_pipeline_v4.argtypes = [C.POINTER(AttnArgs), C.POINTER(V4Ext), C.c_void_p]
         L.dsa_v32_decode_pipeline_host_chunked.argtypes = [C.POINTER(AttnArgs), C.POINTER(HostIO), C.c_int32, C.c_void_p]
         L.dsa_v32_decode_pipeline_allgather.argtypes = [C.POINTER(AttnArgs), C.POINTER(PeerOutputs), C.c_void_p]
         L.dsa_v32_ipc_export.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_int64)]
@@ -238,6 +243,32 @@ def mla_decode_launch_pipeline(q, kv, indices, plan, sm_scale, *, block_table=No
     a = make_args(q, kv, indices, plan, sm_scale, out=out, lse=lse, block_table=block_table,
                   page_block_size=page_block_size, kv_batch_stride_rows=kv_batch_stride_rows)
     _check(lib().dsa_v32_decode_pipeline(C.byref(a), 1 if run_metadata else 0, _stream()), "dsa_v32_decode_pipeline")
+    if check:
+        _check(lib().dsa_v32_device_status(C.byref(a), _stream()), "dsa_v32_device_status")
+    return out, lse
+
+
+def mla_v4_launch_pipeline(q, kv, indices, plan, sm_scale, *, attn_sink=None, kv2=None, pool_split=None, block_table=None,
+                           page_block_size=64, kv_batch_stride_rows=0, out=None, lse=None, check=True):
+    """The pipeline with an attention sink per head (fp32 [H]) and / or a second pool of bf16 rows for the
+    slots at or beyond pool_split[q] (int32 [total_q], physical rows of kv2): the two features of the
+    reference's v4 prefill kernels."""
+    total_q, H = q.shape[0], q.shape[1]
+    if out is None:
+        out = torch.empty(total_q, H, D_V, dtype=torch.bfloat16, device=q.device)
+    if lse is None:
+        lse = torch.empty(total_q, H, dtype=torch.float32, device=q.device)
+    a = make_args(q, kv, indices, plan, sm_scale, out=out, lse=lse, block_table=block_table,
+                  page_block_size=page_block_size, kv_batch_stride_rows=kv_batch_stride_rows)
+    ext = V4Ext()
+    if attn_sink is not None:
+        assert attn_sink.dtype == torch.float32 and attn_sink.numel() == H and attn_sink.is_contiguous()
+        ext.attn_sink = attn_sink.data_ptr()
+    if kv2 is not None:
+        assert kv2.dtype == torch.bfloat16 and kv2.is_contiguous() and kv2.shape[-1] == D_QK
+        assert pool_split is not None and pool_split.dtype == torch.int32 and pool_split.numel() == total_q
+        ext.kv2, ext.pool_split, ext.num_kv2_rows = kv2.data_ptr(), pool_split.data_ptr(), kv2.numel() // D_QK
+    _check(lib().dsa_v32_decode_pipeline_v4(C.byref(a), C.byref(ext), _stream()), "dsa_v32_decode_pipeline_v4")
     if check:
         _check(lib().dsa_v32_device_status(C.byref(a), _stream()), "dsa_v32_device_status")
     return out, lse

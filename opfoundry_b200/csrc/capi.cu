@@ -163,6 +163,10 @@ void fill_params(const dsa_v32_attn_args* a, const WorkspaceHeader& h, AttnParam
         p->out_peers[i] = nullptr;
         p->lse_peers[i] = nullptr;
     }
+    p->attn_sink = nullptr;
+    p->kv2 = nullptr;
+    p->pool_split = nullptr;
+    p->num_kv2_rows = 0;
 }
 
 int check_peers(const dsa_v32_peer_outputs* pe) {
@@ -227,7 +231,7 @@ TmapCache& tmap_cache() {
 }
 
 int launch_attention(const dsa_v32_attn_args* a, int want_dtype, cudaStream_t stream, const WorkspaceHeader* known = nullptr,
-                     const dsa_v32_peer_outputs* peers = nullptr) {
+                     const dsa_v32_peer_outputs* peers = nullptr, const dsa_v32_v4_ext* ext = nullptr) {
     WorkspaceHeader h;
     int rc = check_args(a, want_dtype, &h, known);
     if (rc) return rc;
@@ -240,6 +244,16 @@ int launch_attention(const dsa_v32_attn_args* a, int want_dtype, cudaStream_t st
             p.out_peers[i] = peers->out[i];
             p.lse_peers[i] = peers->lse[i];
         }
+    }
+    if (ext) {
+        if (ext->kv2 != nullptr) {
+            if (want_dtype != DSA_V32_KV_BF16) return DSA_V32_ERR_DTYPE;   // the second pool holds bf16 rows
+            if (!ext->pool_split || ext->num_kv2_rows <= 0 || !aligned16(ext->kv2)) return DSA_V32_ERR_SHAPE;
+        }
+        p.attn_sink = ext->attn_sink;
+        p.kv2 = ext->kv2;
+        p.pool_split = ext->kv2 ? ext->pool_split : nullptr;
+        p.num_kv2_rows = ext->num_kv2_rows;
     }
     // bf16 cache: the kernel reads Q and the cache rows with plain loads and takes no tensor map
     CUtensorMap tq, tkv, ttail;
@@ -411,6 +425,13 @@ int dsa_v32_prefill_bf16(const dsa_v32_attn_args* args, void* stream) {
 }
 
 int dsa_v32_combine(const dsa_v32_attn_args* a, void* stream) { return launch_merge(a, (cudaStream_t)stream); }
+
+int dsa_v32_decode_pipeline_v4(const dsa_v32_attn_args* a, const dsa_v32_v4_ext* ext, void* stream) {
+    if (!a || !ext) return DSA_V32_ERR_NULL;
+    int rc = launch_attention(a, a->kv_dtype, (cudaStream_t)stream, nullptr, nullptr, ext);
+    if (rc) return rc;
+    return launch_merge(a, (cudaStream_t)stream);
+}
 
 int dsa_v32_plan_release(const void* workspace) {
     if (!workspace) return DSA_V32_ERR_NULL;

@@ -59,6 +59,12 @@ struct AttnParams {
     int64_t lse_stride_row;   // elements between query rows of lse (H without peers)
     void* out_peers[DSA_V32_MAX_PEERS];
     float* lse_peers[DSA_V32_MAX_PEERS];
+    // v4-style extensions (NULL = off): attention sink per head; second pool of bf16 rows for the slots at or
+    // beyond pool_split[query row], indexed by physical row
+    const float* attn_sink;
+    const void* kv2;
+    const int32_t* pool_split;
+    int64_t num_kv2_rows;
 };
 
 // Destinations of the merge kernel (same convention as AttnParams).

@@ -828,7 +828,15 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     // this team's share of the row sums, for this CTA and for the peer (it holds the other half of
                     // the rows' output columns)
                     m_ref = ctl->m_shared[row];
-                    const float lv = (l_part != 0.0f && l_ref != m_ref) ? l_part * ex2_approx(l_ref - m_ref) : l_part;
+                    float lv = (l_part != 0.0f && l_ref != m_ref) ? l_part * ex2_approx(l_ref - m_ref) : l_part;
+                    if (p.attn_sink != nullptr) {
+                        // attention sink (opus_attn/dsa_v4/common/mla_v4_host.cc:469-472): one more term exp(sink - m) in the
+                        // denominator, counted once per query row and head: by team 0, in the piece that starts the list
+                        const RowMap rs = map_row(wi, row, p.H);
+                        const float sink2 = rs.live ? __ldg(p.attn_sink + rs.head) * 1.4426950408889634f : -INFINITY;
+                        if (m_ref == -INFINITY) m_ref = sink2;                      // no valid score in this piece: the sink is the reference
+                        if (cg == 0 && wi.k_begin == 0 && sink2 > -INFINITY) lv += ex2_approx(sink2 - m_ref);
+                    }
                     ctl->l_part[lp][cg][row] = lv;
                     if (kRowSplit) st_cluster_u32(map_to_cta(smem_u32(&ctl->l_part[lp][cg][row]), peer), __float_as_uint(lv));
                     __syncwarp();
@@ -998,6 +1006,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const int seq = wi.q_row / p.s_q;
                 const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
                 const int32_t* idx_row = p.indices + (size_t)wi.q_row * p.topk;
+                const int pool_split = p.pool_split != nullptr ? __ldg(p.pool_split + wi.q_row) : 0x7FFFFFFF;
                 auto load_slot = [&](int k0) -> int {
                     const int k = k0 + r;
                     return (k < wi.k_end) ? __ldg(idx_row + k) : -1;
@@ -1012,7 +1021,12 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 for (int u = u0; u < n_tiles; u += 2) {
                     const uint32_t it = it_base + u;
                     const int k0 = wi.k_begin + u * kTileRows;
-                    const int row = row_of(idx_a, phys_a, seq, p);
+                    int row = row_of(idx_a, phys_a, seq, p);
+                    const uint8_t* pool = kv_bytes;
+                    if (p.kv2 != nullptr && k0 + r >= pool_split) {   // "extend" slots: physical rows of the second pool
+                        row = (idx_a >= 0 && idx_a < p.num_kv2_rows) ? idx_a : -1;
+                        pool = reinterpret_cast<const uint8_t*>(p.kv2);
+                    }
                     {
                         const int phys_n = block_of(idx_c, seq, p);
                         const int idx_n = load_slot(k0 + 8 * kTileRows);
@@ -1028,7 +1042,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     const uint32_t bar = smem_u32(&ctl->kv_full[s]);
                     if (lane == 0) mask_bytes[(it % kMaskSlots) * 4 + l4] = static_cast<uint8_t>(mask8);
                     // padding / out-of-range rows: nothing is read, the row is filled with zeros
-                    const uint8_t* src = kv_bytes + (size_t)(row >= 0 ? row : 0) * (kDQK * 2) + col0 * 2;
+                    const uint8_t* src = pool + (size_t)(row >= 0 ? row : 0) * (kDQK * 2) + col0 * 2;
                     const uint32_t nbytes = row >= 0 ? 16u : 0u;
                     const uint32_t dst_row = smem_u32(sKV + s * kKvTileBytes) + r * 128;
 #pragma unroll

@@ -15,7 +15,7 @@ import numpy as np
 D_QK, D_V, D_ROPE = 576, 512, 64
 FP8_ROW_BYTES = 656
 
-_TAGS = {"q": 1, "kv": 2, "rope": 3, "indices": 4, "block_table": 5, "share": 6}
+_TAGS = {"q": 1, "kv": 2, "rope": 3, "indices": 4, "block_table": 5, "share": 6, "kv2": 7}
 
 
 def stream(seed, tag, sub=0):

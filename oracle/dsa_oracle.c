@@ -175,6 +175,11 @@ typedef struct {
     int total_q, H;
     const int32_t* subset;
     int n_items;
+    /* v4-style extensions (opus_attn/dsa_v4/common/mla_v4_host.cc:455-532): attention sink, second KV pool */
+    const float* attn_sink;     /* [H] or NULL: joins the row maximum and the denominator (mla_v4_host.cc:469-472) */
+    const uint8_t* kv2;         /* second pool (bf16 rows) or NULL */
+    int64_t num_kv2_rows;
+    const int32_t* pool_split;  /* [total_q]: slots >= pool_split[q] index kv2 directly by physical row */
     /* shared state */
     volatile int next;
     volatile int error;
@@ -215,7 +220,16 @@ static int run_query(job_t* J, int qi, float* kv_dense, float* qT, float* scores
     for (int j = 0; j < topk; ++j) {
         const int32_t i = idx[j];
         int64_t row = -1;
-        if (i != -1) {
+        if (i != -1 && J->kv2 && J->pool_split && j >= J->pool_split[qi]) {
+            /* "extend" rows: physical rows of the second pool (mla_v4_host.cc:524-526) */
+            if (i < -1) return 1;
+            row = i;
+            if (row >= J->num_kv2_rows) return 3;
+            const uint16_t* s16 = (const uint16_t*)(J->kv2 + (size_t)row * D_QK * 2);
+            float* dst = kv_dense + (size_t)n * D_QK;
+            for (int d = 0; d < D_QK; ++d) dst[d] = bf16_to_f32(s16[d]);
+            ++n;
+        } else if (i != -1) {
             if (i < -1) return 1; /* only -1 is padding; anything else negative is a caller error */
             if (J->block_table) {
                 const int blk = i / J->page_block_size;
@@ -243,10 +257,10 @@ static int run_query(job_t* J, int qi, float* kv_dense, float* qT, float* scores
         const int hg = (H - h0 < HEAD_GROUP) ? H - h0 : HEAD_GROUP;
         uint16_t* o_base = J->out + ((size_t)qi * H + h0) * D_V;
         float* lse_base = J->lse + (size_t)qi * H + h0;
-        if (n == 0) { /* host.cc:486-490 */
+        if (n == 0) { /* host.cc:486-490; with a sink the denominator is exp(sink): out 0 (mla_v4_host.cc:507-510), lse = sink */
             for (int g = 0; g < hg; ++g) {
                 memset(o_base + (size_t)g * D_V, 0, D_V * 2);
-                lse_base[g] = INFINITY;
+                lse_base[g] = J->attn_sink ? J->attn_sink[h0 + g] : INFINITY;
             }
             continue;
         }
@@ -261,11 +275,13 @@ static int run_query(job_t* J, int qi, float* kv_dense, float* qT, float* scores
             float m = s[0];
             for (int p = 1; p < n; ++p)
                 if (s[p] > m) m = s[p];
+            if (J->attn_sink && J->attn_sink[h0 + g] > m) m = J->attn_sink[h0 + g]; /* mla_v4_host.cc:469 */
             float sum = 0.0f;
             for (int p = 0; p < n; ++p) {
                 s[p] = expf(s[p] - m);
                 sum += s[p];
             }
+            if (J->attn_sink) sum += expf(J->attn_sink[h0 + g] - m); /* mla_v4_host.cc:472 */
             lse_base[g] = logf(sum) + m;
             for (int p = 0; p < n; ++p) s[p] = bf16_to_f32(f32_to_bf16(s[p] / sum));
             float acc[D_V];
@@ -314,6 +330,45 @@ static void* worker(void* arg) {
  * Returns 0, or a positive code: 1 negative index other than -1, 2 position beyond the block
  * table, 3 physical row out of range, 4 bad subset entry, 100 out of memory.
  */
+static int run_job(job_t* J, int num_threads) {
+    if (num_threads < 1) num_threads = 1;
+    if (num_threads > 256) num_threads = 256;
+    if (num_threads > J->n_items) num_threads = J->n_items > 0 ? J->n_items : 1;
+    pthread_t tids[256];
+    int started = 0;
+    for (int t = 1; t < num_threads; ++t)
+        if (pthread_create(&tids[started], NULL, worker, J) == 0) ++started;
+    worker(J);
+    for (int t = 0; t < started; ++t) pthread_join(tids[t], NULL);
+    return J->error;
+}
+
+/*
+ * The same with the two v4 features (opus_attn/dsa_v4/common/mla_v4_host.cc:455-532, README "Attention
+ * Model"): attn_sink [H] joins every row's maximum and denominator; slots >= pool_split[q] of query q index
+ * the second pool kv2 (bf16 rows) by physical row, the slots before it the first pool as usual.
+ */
+int dsa_oracle_sparse_mla_v4(const uint16_t* q, int64_t q_stride_q, int64_t q_stride_h, const void* kv, int kv_is_fp8,
+                             int64_t kv_row_bytes, int64_t num_kv_rows, int64_t kv_batch_stride_rows,
+                             const int32_t* indices, int topk, const int32_t* block_table, int block_table_stride,
+                             int page_block_size, int s_q, float sm_scale, uint16_t* out, float* lse, int total_q, int H,
+                             const float* attn_sink, const void* kv2, int64_t num_kv2_rows, const int32_t* pool_split,
+                             int num_threads) {
+    job_t J;
+    memset(&J, 0, sizeof(J));
+    J.q = q; J.q_stride_q = q_stride_q; J.q_stride_h = q_stride_h;
+    J.kv = (const uint8_t*)kv; J.kv_is_fp8 = kv_is_fp8; J.kv_row_bytes = kv_row_bytes;
+    J.num_kv_rows = num_kv_rows; J.kv_batch_stride_rows = kv_batch_stride_rows;
+    J.indices = indices; J.topk = topk;
+    J.block_table = block_table; J.block_table_stride = block_table_stride;
+    J.page_block_size = page_block_size > 0 ? page_block_size : 1;
+    J.s_q = s_q > 0 ? s_q : 1;
+    J.sm_scale = sm_scale; J.out = out; J.lse = lse;
+    J.total_q = total_q; J.H = H; J.n_items = total_q;
+    J.attn_sink = attn_sink; J.kv2 = (const uint8_t*)kv2; J.num_kv2_rows = num_kv2_rows; J.pool_split = pool_split;
+    return run_job(&J, num_threads);
+}
+
 int dsa_oracle_sparse_mla(const uint16_t* q, int64_t q_stride_q, int64_t q_stride_h, const void* kv, int kv_is_fp8,
                           int64_t kv_row_bytes, int64_t num_kv_rows, int64_t kv_batch_stride_rows,
                           const int32_t* indices, int topk, const int32_t* block_table, int block_table_stride,
@@ -332,16 +387,7 @@ int dsa_oracle_sparse_mla(const uint16_t* q, int64_t q_stride_q, int64_t q_strid
     J.sm_scale = sm_scale; J.out = out; J.lse = lse; J.rows_dbg = rows_dbg;
     J.total_q = total_q; J.H = H;
     J.subset = subset; J.n_items = subset ? n_subset : total_q;
-    if (num_threads < 1) num_threads = 1;
-    if (num_threads > 256) num_threads = 256;
-    if (num_threads > J.n_items) num_threads = J.n_items > 0 ? J.n_items : 1;
-    pthread_t tids[256];
-    int started = 0;
-    for (int t = 1; t < num_threads; ++t)
-        if (pthread_create(&tids[started], NULL, worker, &J) == 0) ++started;
-    worker(&J);
-    for (int t = 0; t < started; ++t) pthread_join(tids[t], NULL);
-    return J.error;
+    return run_job(&J, num_threads);
 }
 
 /*

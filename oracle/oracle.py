@@ -38,6 +38,11 @@ def lib():
             C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int64,
             C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p, C.c_void_p,
             C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int]
+        L.dsa_oracle_sparse_mla_v4.restype = C.c_int
+        L.dsa_oracle_sparse_mla_v4.argtypes = [
+            C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int64,
+            C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p, C.c_void_p,
+            C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int]
         L.dsa_oracle_merge.restype = None
         L.dsa_oracle_merge.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
         _lib = L
@@ -147,6 +152,40 @@ def sparse_mla(q, kv, indices, sm_scale, *, kv_is_fp8=False, block_table=None, p
     if rc:
         raise ValueError("oracle rejected the inputs, code %d" % rc)
     return (out, lse, rows) if want_rows else (out, lse)
+
+
+def sparse_mla_v4(q, kv, indices, sm_scale, *, attn_sink=None, kv2=None, pool_split=None, kv_is_fp8=False, block_table=None,
+                  page_block_size=1, s_q=1, kv_batch_stride_rows=0, num_threads=None):
+    """sparse_mla with the two v4 features: attn_sink float32 [H]; kv2 uint16 [rows2, 576] + pool_split int32
+    [total_q] (slots >= pool_split[q] index kv2 by physical row)."""
+    q = np.ascontiguousarray(q, dtype=np.uint16)
+    total_q, H, _ = q.shape
+    if kv_is_fp8:
+        kv = np.ascontiguousarray(kv, dtype=np.uint8).reshape(-1, FP8_ROW_BYTES)
+        row_bytes = FP8_ROW_BYTES
+    else:
+        kv = np.ascontiguousarray(kv, dtype=np.uint16).reshape(-1, D_QK)
+        row_bytes = D_QK * 2
+    indices = np.ascontiguousarray(indices, dtype=np.int32)
+    topk = indices.shape[1]
+    bt, bt_stride = None, 0
+    if block_table is not None:
+        bt = np.ascontiguousarray(block_table, dtype=np.int32)
+        bt_stride = bt.shape[1]
+    sink = None if attn_sink is None else np.ascontiguousarray(attn_sink, dtype=np.float32)
+    k2 = None if kv2 is None else np.ascontiguousarray(kv2, dtype=np.uint16).reshape(-1, D_QK)
+    ps = None if pool_split is None else np.ascontiguousarray(pool_split, dtype=np.int32)
+    out = np.zeros((total_q, H, D_V), dtype=np.uint16)
+    lse = np.zeros((total_q, H), dtype=np.float32)
+    if num_threads is None:
+        num_threads = int(os.environ.get("DSA_NUM_THREADS", os.cpu_count() or 1))
+    rc = lib().dsa_oracle_sparse_mla_v4(_p(q), H * D_QK, D_QK, _p(kv), int(kv_is_fp8), row_bytes, kv.shape[0],
+                                        int(kv_batch_stride_rows), _p(indices), topk, _p(bt), bt_stride, int(page_block_size),
+                                        int(s_q), float(sm_scale), _p(out), _p(lse), total_q, H, _p(sink), _p(k2),
+                                        0 if k2 is None else k2.shape[0], _p(ps), int(num_threads))
+    if rc:
+        raise ValueError("oracle rejected the inputs, code %d" % rc)
+    return out, lse
 
 
 def merge(o_parts, lse_parts):

@@ -225,7 +225,10 @@ int dsa_v32_decode_pipeline_v4(const dsa_v32_attn_args* args, const dsa_v32_v4_e
  *   out[r], lse[r]  where THIS rank's slice starts inside peer r's gathered out / lse buffer; the element
  *                   strides are args->stride_o_row / stride_o_head and lse_stride_row for all peers,
  *   flags[r]        peer r's array of DSA_V32_MAX_PEERS uint32 arrival flags (zero before the first step).
- * `step` must grow by one with every call.  No counterpart in the reference, which is single-GPU; the
+ * `step` must grow by one with every call.  When this rank's slice is one contiguous block of whole rows of
+ * more than 64 heads (sequences sharded), the kernels write this GPU's own buffer and the block is pushed to the
+ * peers by device-to-device copies after them: an item's full 128 x 512 output stored to every peer from the
+ * epilogue would hold up the hand-over between items.  No counterpart in the reference, which is single-GPU; the
  * collective it replaces is the NCCL all-gather of the head-sharded decode configuration.
  */
 #define DSA_V32_MAX_PEERS 8
@@ -327,6 +330,17 @@ int dsa_v32_selftest_wait_expiry(void* workspace, int32_t* result_dev, int64_t b
  * same device function as the attention kernel's loader warps.
  */
 int dsa_v32_debug_rows(const dsa_v32_attn_args* args, int32_t* rows_out, void* stream);
+
+/*
+ * Producer of the index lists: for every query row the positions of the `topk` largest scores among the
+ * row's first valid_len[q] positions (all kv_len when valid_len is NULL), written in ascending position
+ * order and padded with -1; ties at the threshold go to the lower positions, NaN scores are never preferred.
+ * scores: fp32 [total_q, kv_len] with row stride `stride_row` elements (the indexer's logits); all pointers
+ * are device pointers.  This is the output stage of the DSA indexer upstream of the attention; the reference
+ * has no counterpart (its harness draws the lists at random, common/host.cc:239-261).
+ */
+int dsa_v32_topk_select(const float* scores, int64_t stride_row, const int32_t* valid_len, int32_t total_q, int32_t kv_len,
+                        int32_t topk, int32_t* indices_out, void* stream);
 
 /*
  * KV-cache write path: quantises [num_rows, 512] fp32 latent values and [num_rows, 64] bf16

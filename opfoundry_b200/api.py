@@ -67,7 +67,7 @@ EXPORTS = ["dsa_v32_abi_version", "dsa_v32_error_string", "dsa_v32_plan_info_get
            "dsa_v32_plan_host", "dsa_v32_plan_read", "dsa_v32_plan_release", "dsa_v32_decode_bf16", "dsa_v32_decode_fp8",
            "dsa_v32_prefill_bf16", "dsa_v32_combine", "dsa_v32_decode_pipeline", "dsa_v32_device_status",
            "dsa_v32_debug_rows", "dsa_v32_pack_fp8_rows", "dsa_v32_decode_pipeline_host",
-           "dsa_v32_decode_pipeline_static", "dsa_v32_static_scratch_address", "dsa_v32_selftest_wait_expiry", "dsa_v32_decode_pipeline_allgather", "dsa_v32_ipc_export", "dsa_v32_ipc_open", "dsa_v32_ipc_close", "dsa_v32_decode_pipeline_host_chunked", "dsa_v32_decode_pipeline_v4"]
+           "dsa_v32_decode_pipeline_static", "dsa_v32_static_scratch_address", "dsa_v32_selftest_wait_expiry", "dsa_v32_decode_pipeline_allgather", "dsa_v32_ipc_export", "dsa_v32_ipc_open", "dsa_v32_ipc_close", "dsa_v32_decode_pipeline_host_chunked", "dsa_v32_decode_pipeline_v4", "dsa_v32_topk_select"]
 
 _lib = None
 
@@ -110,6 +110,7 @@ def lib():
         L.dsa_v32_static_scratch_address.restype = C.c_void_p
         L.dsa_v32_static_scratch_address.argtypes = []
         L.dsa_v32_debug_rows.argtypes = [C.POINTER(AttnArgs), C.c_void_p, C.c_void_p]
+        L.dsa_v32_topk_select.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
         L.dsa_v32_pack_fp8_rows.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]
         _lib = L
     return _lib
@@ -293,6 +294,22 @@ def debug_rows(indices, *, s_q=1, num_kv_rows, block_table=None, page_block_size
     rows = torch.empty_like(indices)
     _check(lib().dsa_v32_debug_rows(C.byref(a), rows.data_ptr(), _stream()), "dsa_v32_debug_rows")
     return rows
+
+
+def topk_select(scores, topk, valid_len=None, out=None):
+    """scores fp32 [total_q, kv_len] (device) -> int32 [total_q, topk]: the positions of the topk largest scores of
+    every row among its first valid_len[q] positions, ascending, -1 padded."""
+    assert scores.dtype == torch.float32 and scores.dim() == 2 and scores.stride(1) == 1
+    total_q, kv_len = scores.shape
+    if out is None:
+        out = torch.empty(total_q, topk, dtype=torch.int32, device=scores.device)
+    vl = None
+    if valid_len is not None:
+        assert valid_len.dtype == torch.int32 and valid_len.numel() == total_q
+        vl = valid_len.data_ptr()
+    _check(lib().dsa_v32_topk_select(scores.data_ptr(), scores.stride(0), vl, total_q, kv_len, topk, out.data_ptr(), _stream()),
+           "dsa_v32_topk_select")
+    return out
 
 
 def pack_fp8_rows(latent, rope, out=None, dst_rows=None):

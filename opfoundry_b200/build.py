@@ -7,7 +7,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libdsa_v32.so")
-SOURCES = ["sparse_mla.cu", "capi.cu"]
+SOURCES = ["sparse_mla.cu", "topk_select.cu", "capi.cu"]
 HEADERS = ["defs.h", "plan.h", "ptx.cuh", "tmap.h", os.path.join("..", "..", "include", "dsa_v32.h")]
 
 

@@ -19,6 +19,8 @@ cudaError_t launch_combine(const float* o_accum, const float* lse_accum, const i
                            const int32_t* reduce_slots, const ReduceDst* reduce_dst, int num_reduce_rows, const OutTargets& tgt,
                            int64_t stride_o_row, int64_t stride_o_head, int H, cudaStream_t stream);
 cudaError_t launch_peer_sync(const PeerSync& s, cudaStream_t stream);
+cudaError_t launch_topk_select(const float* scores, int64_t stride_row, const int32_t* valid_len, int total_q, int kv_len, int topk,
+                               int32_t* indices_out, cudaStream_t stream);
 cudaError_t launch_debug_rows(const AttnParams& p, int total_q, int32_t* rows_out, cudaStream_t stream);
 cudaError_t launch_wait_selftest(int32_t* status, int32_t* result, unsigned long long budget_ns, cudaStream_t stream);
 cudaError_t launch_pack_fp8(const float* latent, const void* rope, const int64_t* dst_rows, void* out, int64_t num_rows,
@@ -460,10 +462,39 @@ int dsa_v32_decode_pipeline_allgather(const dsa_v32_attn_args* a, const dsa_v32_
     int rc = check_peers(peers);
     if (rc) return rc;
     cudaStream_t st = (cudaStream_t)stream;
-    rc = launch_attention(a, a->kv_dtype, st, nullptr, peers);
+    // Stores from the epilogue reach every peer while the attention runs - as long as an item's output is
+    // small (head-sharded: few live rows per item).  When this rank owns whole rows of all heads (sequences
+    // sharded: 128 rows x 512 columns per item to every peer) the remote stores would hold up the epilogue
+    // between items; the slice is one contiguous block then, so the kernels write this GPU's own gathered
+    // buffer and the block is pushed to the peers by copies after them.
+    const bool contiguous_slice = a->stride_o_head == kDV && a->stride_o_row == int64_t(a->H) * kDV &&
+                                  peers->lse_stride_row == a->H;
+    const bool push_after = contiguous_slice && peers->num_peers > 1 && a->H > 64;
+    dsa_v32_peer_outputs own = *peers;
+    if (push_after) {
+        own.num_peers = 1;
+        own.my_rank = 0;
+        own.out[0] = peers->out[peers->my_rank];
+        own.lse[0] = peers->lse[peers->my_rank];
+        own.flags[0] = peers->flags[peers->my_rank];
+    }
+    rc = launch_attention(a, a->kv_dtype, st, nullptr, push_after ? &own : peers);
     if (rc) return rc;
-    rc = launch_merge(a, st, nullptr, peers);
+    rc = launch_merge(a, st, nullptr, push_after ? &own : peers);
     if (rc) return rc;
+    cudaError_t e;
+    if (push_after) {
+        const size_t o_bytes = size_t(a->total_q) * size_t(a->stride_o_row) * 2, l_bytes = size_t(a->total_q) * size_t(a->H) * 4;
+        for (int r = 0; r < peers->num_peers; ++r) {
+            if (r == peers->my_rank) continue;
+            e = cudaMemcpyAsync(peers->out[r], peers->out[peers->my_rank], o_bytes, cudaMemcpyDeviceToDevice, st);
+            if (e != cudaSuccess) return (int)e;
+            if (peers->lse[r] && peers->lse[peers->my_rank]) {
+                e = cudaMemcpyAsync(peers->lse[r], peers->lse[peers->my_rank], l_bytes, cudaMemcpyDeviceToDevice, st);
+                if (e != cudaSuccess) return (int)e;
+            }
+        }
+    }
     PeerSync s;
     std::memset(&s, 0, sizeof(s));
     s.n_peers = peers->num_peers;
@@ -471,7 +502,7 @@ int dsa_v32_decode_pipeline_allgather(const dsa_v32_attn_args* a, const dsa_v32_
     s.step = peers->step;
     for (int i = 0; i < peers->num_peers; ++i) s.flags[i] = peers->flags[i];
     s.status = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(a->workspace) + offsetof(WorkspaceHeader, status));
-    cudaError_t e = launch_peer_sync(s, st);
+    e = launch_peer_sync(s, st);
     return e == cudaSuccess ? DSA_V32_OK : (int)e;
 }
 
@@ -749,6 +780,14 @@ int dsa_v32_debug_rows(const dsa_v32_attn_args* a, int32_t* rows_out, void* stre
     p.block_table_stride = a->block_table_stride;
     set_page(&p, a->page_block_size);
     cudaError_t e = launch_debug_rows(p, a->total_q, rows_out, (cudaStream_t)stream);
+    return e == cudaSuccess ? DSA_V32_OK : (int)e;
+}
+
+int dsa_v32_topk_select(const float* scores, int64_t stride_row, const int32_t* valid_len, int32_t total_q, int32_t kv_len,
+                        int32_t topk, int32_t* indices_out, void* stream) {
+    if (!scores || !indices_out) return DSA_V32_ERR_NULL;
+    if (total_q < 0 || kv_len <= 0 || topk <= 0 || stride_row < kv_len) return DSA_V32_ERR_SHAPE;
+    cudaError_t e = launch_topk_select(scores, stride_row, valid_len, total_q, kv_len, topk, indices_out, (cudaStream_t)stream);
     return e == cudaSuccess ? DSA_V32_OK : (int)e;
 }
 

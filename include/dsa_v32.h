@@ -227,7 +227,7 @@ int dsa_v32_decode_pipeline_v4(const dsa_v32_attn_args* args, const dsa_v32_v4_e
  *   flags[r]        peer r's array of DSA_V32_MAX_PEERS uint32 arrival flags (zero before the first step).
  * `step` must grow by one with every call.  When this rank's slice is one contiguous block of whole rows of
  * more than 64 heads (sequences sharded), the kernels write this GPU's own buffer and the block is pushed to the
- * peers by device-to-device copies after them: an item's full 128 x 512 output stored to every peer from the
+ * peers by one copy kernel after them: an item's full 128 x 512 output stored to every peer from the
  * epilogue would hold up the hand-over between items.  No counterpart in the reference, which is single-GPU; the
  * collective it replaces is the NCCL all-gather of the head-sharded decode configuration.
  */

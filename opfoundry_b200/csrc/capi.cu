@@ -13,12 +13,13 @@
 
 namespace dsa {
 int max_resident_pairs(bool fp8, int* out);
-cudaError_t launch_attn(bool fp8, int num_lists, const CUtensorMap& tq, const CUtensorMap& tkv, const CUtensorMap& ttail,
+cudaError_t launch_attn(bool fp8, bool ext, int num_lists, const CUtensorMap& tq, const CUtensorMap& tkv, const CUtensorMap& ttail,
                         const AttnParams& p, cudaStream_t stream);
 cudaError_t launch_combine(const float* o_accum, const float* lse_accum, const int32_t* reduce_indptr,
                            const int32_t* reduce_slots, const ReduceDst* reduce_dst, int num_reduce_rows, const OutTargets& tgt,
                            int64_t stride_o_row, int64_t stride_o_head, int H, cudaStream_t stream);
 cudaError_t launch_peer_sync(const PeerSync& s, cudaStream_t stream);
+cudaError_t launch_peer_push(int n_peers, int my_rank, const void* src, void* const* dst, int64_t bytes, cudaStream_t stream);
 cudaError_t launch_topk_select(const float* scores, int64_t stride_row, const int32_t* valid_len, int total_q, int kv_len, int topk,
                                int32_t* indices_out, cudaStream_t stream);
 cudaError_t launch_debug_rows(const AttnParams& p, int total_q, int32_t* rows_out, cudaStream_t stream);
@@ -283,7 +284,8 @@ int launch_attention(const dsa_v32_attn_args* a, int want_dtype, cudaStream_t st
         if (tmap_cache().get(&ttail, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, a->kv, dims, str, box_b, CU_TENSOR_MAP_SWIZZLE_NONE))
             return DSA_V32_ERR_DRIVER;
     }
-    cudaError_t e = launch_attn(fp8, h.num_lists, tq, tkv, ttail, p, stream);
+    const bool use_ext = h.has_stacked != 0 || p.attn_sink != nullptr || p.kv2 != nullptr || p.n_peers > 0;
+    cudaError_t e = launch_attn(fp8, use_ext, h.num_lists, tq, tkv, ttail, p, stream);
     return e == cudaSuccess ? DSA_V32_OK : (int)e;
 }
 
@@ -466,7 +468,7 @@ int dsa_v32_decode_pipeline_allgather(const dsa_v32_attn_args* a, const dsa_v32_
     // small (head-sharded: few live rows per item).  When this rank owns whole rows of all heads (sequences
     // sharded: 128 rows x 512 columns per item to every peer) the remote stores would hold up the epilogue
     // between items; the slice is one contiguous block then, so the kernels write this GPU's own gathered
-    // buffer and the block is pushed to the peers by copies after them.
+    // buffer and one copy kernel pushes the block to the peers after them.
     const bool contiguous_slice = a->stride_o_head == kDV && a->stride_o_row == int64_t(a->H) * kDV &&
                                   peers->lse_stride_row == a->H;
     const bool push_after = contiguous_slice && peers->num_peers > 1 && a->H > 64;
@@ -484,13 +486,24 @@ int dsa_v32_decode_pipeline_allgather(const dsa_v32_attn_args* a, const dsa_v32_
     if (rc) return rc;
     cudaError_t e;
     if (push_after) {
-        const size_t o_bytes = size_t(a->total_q) * size_t(a->stride_o_row) * 2, l_bytes = size_t(a->total_q) * size_t(a->H) * 4;
+        const int64_t o_bytes = int64_t(a->total_q) * a->stride_o_row * 2, l_bytes = int64_t(a->total_q) * a->H * 4;
+        void* od[DSA_V32_MAX_PEERS];
+        void* ld[DSA_V32_MAX_PEERS];
+        bool with_lse = true;
         for (int r = 0; r < peers->num_peers; ++r) {
-            if (r == peers->my_rank) continue;
-            e = cudaMemcpyAsync(peers->out[r], peers->out[peers->my_rank], o_bytes, cudaMemcpyDeviceToDevice, st);
+            od[r] = peers->out[r];
+            ld[r] = peers->lse[r];
+            with_lse = with_lse && peers->lse[r] != nullptr;
+        }
+        e = launch_peer_push(peers->num_peers, peers->my_rank, peers->out[peers->my_rank], od, o_bytes, st);
+        if (e != cudaSuccess) return (int)e;
+        if (with_lse && (l_bytes % 16) == 0 && aligned16(peers->lse[peers->my_rank])) {
+            e = launch_peer_push(peers->num_peers, peers->my_rank, peers->lse[peers->my_rank], ld, l_bytes, st);
             if (e != cudaSuccess) return (int)e;
-            if (peers->lse[r] && peers->lse[peers->my_rank]) {
-                e = cudaMemcpyAsync(peers->lse[r], peers->lse[peers->my_rank], l_bytes, cudaMemcpyDeviceToDevice, st);
+        } else if (with_lse) {
+            for (int r = 0; r < peers->num_peers; ++r) {
+                if (r == peers->my_rank) continue;
+                e = cudaMemcpyAsync(peers->lse[r], peers->lse[peers->my_rank], size_t(l_bytes), cudaMemcpyDeviceToDevice, st);
                 if (e != cudaSuccess) return (int)e;
             }
         }

@@ -22,7 +22,7 @@ struct WorkspaceHeader {
     int32_t total_q, H, topk, s_q;
     int32_t num_lists, num_works, num_partials, num_reduce_rows, num_head_blocks;
     int32_t status;  // device status word, 0 = ok
-    int32_t _pad0;
+    int32_t has_stacked;  // 1 when some work item stacks several query rows
     int64_t off_list_indptr, off_works, off_reduce_indptr, off_reduce_slots, off_reduce_dst;
     int64_t off_o_accum, off_lse_accum, total_bytes;
 };

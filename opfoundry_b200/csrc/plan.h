@@ -71,6 +71,9 @@ inline void finish_plan(const dsa_v32_shape& sh, int L, int n_hb, int next_slot,
     h.num_partials = next_slot;
     h.num_reduce_rows = int(P.reduce_dst.size());
     h.num_head_blocks = n_hb;
+    h.has_stacked = 0;
+    for (const auto& w : P.works)
+        if (w.stacked_rows > 1) h.has_stacked = 1;
     int64_t off = 256;
     h.off_list_indptr = off;
     off = align256(off + int64_t(L + 1) * 4);

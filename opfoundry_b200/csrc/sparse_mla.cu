@@ -227,9 +227,10 @@ struct RowMap {
     int q_row, head;
     bool live;
 };
+template <bool kExt>
 __device__ __forceinline__ RowMap map_row(const dsa_v32_work_info& w, int row, int H) {
     RowMap m;
-    if (w.stacked_rows > 1) {
+    if (kExt && w.stacked_rows > 1) {
         const int sub = row / H;
         m.q_row = w.q_row + sub;
         m.head = row - sub * H;
@@ -296,7 +297,9 @@ __device__ __forceinline__ void issue_pv_mmas(uint32_t o_tmem, uint32_t p_tmem, 
 }
 
 // ------------------------------------------------------------------ the kernel
-template <bool kFp8>
+// kExt: the instantiation that also handles stacked query rows, the attention sink and the second KV pool;
+// the plain one keeps those branches out of the loaders and the epilogue.
+template <bool kFp8, bool kExt>
 __global__ void __launch_bounds__(Cfg<kFp8>::kThreads, 1)
 sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
                   const __grid_constant__ CUtensorMap tm_kv_tail, const AttnParams p) {
@@ -443,7 +446,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         uint32_t qreg[kQRegs];
         const int q_ncol = (!kFp8 && half) ? 40 : 32;   // TMEM columns (bf16 pairs) per warp; fp8: latent columns only
         auto q_fetch = [&](const dsa_v32_work_info& wq) {
-            const RowMap rm = map_row(wq, row, p.H);
+            const RowMap rm = map_row<kExt>(wq, row, p.H);
             const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.q) + (size_t)rm.q_row * p.stride_q_row +
                                        (size_t)rm.head * p.stride_q_head + col0 + 2 * cg * q_ncol;
             const bool live = rm.live;
@@ -458,7 +461,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
         };
         auto q_prefetch_l2 = [&](const dsa_v32_work_info& wq) {
-            const RowMap rm = map_row(wq, row, p.H);
+            const RowMap rm = map_row<kExt>(wq, row, p.H);
             if (rm.live) {
                 const char* src = reinterpret_cast<const char*>(reinterpret_cast<const __nv_bfloat16*>(p.q) + (size_t)rm.q_row * p.stride_q_row +
                                                                (size_t)rm.head * p.stride_q_head + col0 + 2 * cg * q_ncol);
@@ -829,10 +832,10 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     // the rows' output columns)
                     m_ref = ctl->m_shared[row];
                     float lv = (l_part != 0.0f && l_ref != m_ref) ? l_part * ex2_approx(l_ref - m_ref) : l_part;
-                    if (p.attn_sink != nullptr) {
+                    if (kExt && p.attn_sink != nullptr) {
                         // attention sink (opus_attn/dsa_v4/common/mla_v4_host.cc:469-472): one more term exp(sink - m) in the
                         // denominator, counted once per query row and head: by team 0, in the piece that starts the list
-                        const RowMap rs = map_row(wi, row, p.H);
+                        const RowMap rs = map_row<kExt>(wi, row, p.H);
                         const float sink2 = rs.live ? __ldg(p.attn_sink + rs.head) * 1.4426950408889634f : -INFINITY;
                         if (m_ref == -INFINITY) m_ref = sink2;                      // no valid score in this piece: the sink is the reference
                         if (cg == 0 && wi.k_begin == 0 && sink2 > -INFINITY) lv += ex2_approx(sink2 - m_ref);
@@ -854,11 +857,11 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (!warp_wait(smem_u32(&ctl->o_full), item_n & 1, abort_flag)) goto done;
                 tc_fence_after();
                 const float inv = (l > 0.0f) ? 1.0f / l : 0.0f;
-                const RowMap rm = map_row(wi, row, p.H);
+                const RowMap rm = map_row<kExt>(wi, row, p.H);
                 const int head = rm.head;
                 const bool live = rm.live;
                 const float lse_nat = (l > 0.0f) ? (m_ref + __log2f(l)) * 0.69314718055994531f : INFINITY;
-                if (wi.partial_slot < 0) {
+                if (wi.partial_slot < 0 && kExt && p.n_peers > 0) {
                     // element offset of the row's 256 columns of this CTA; the same in out and in every peer's
                     // gathered buffer (fused all-gather: plain stores through the peer-mapped pointers)
                     const size_t o_off = (size_t)rm.q_row * p.stride_o_row + (size_t)head * p.stride_o_head + half * kDvHalf;
@@ -895,6 +898,28 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                             p.lse[l_off] = lse_nat;
                         }
                     }
+                } else if (wi.partial_slot < 0) {
+                    __nv_bfloat16* o_dst = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)rm.q_row * p.stride_o_row +
+                                           (size_t)head * p.stride_o_head + half * kDvHalf;
+#pragma unroll 1
+                    for (int oc = cg * OCOLS; oc < (cg + 1) * OCOLS; oc += 32) {
+                        uint32_t o[32];
+                        tmem_ld32(lane_base + kColO + oc, o);
+                        tmem_wait_ld();
+                        if (live) {
+                            uint4* d4 = reinterpret_cast<uint4*>(o_dst + oc);
+#pragma unroll
+                            for (int v = 0; v < 4; ++v) {
+                                uint4 u;
+                                u.x = pack_bf16x2(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
+                                u.y = pack_bf16x2(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
+                                u.z = pack_bf16x2(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
+                                u.w = pack_bf16x2(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
+                                d4[v] = u;
+                            }
+                        }
+                    }
+                    if (live && (kRowSplit ? own : half == 0) && cg == 0 && p.lse != nullptr) p.lse[(size_t)rm.q_row * p.H + head] = lse_nat;
                 } else {
                     float* o_dst = p.o_accum + ((size_t)wi.partial_slot * kHeadsPerBlock + row) * kDV + half * kDvHalf;
 #pragma unroll 1
@@ -1006,7 +1031,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const int seq = wi.q_row / p.s_q;
                 const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
                 const int32_t* idx_row = p.indices + (size_t)wi.q_row * p.topk;
-                const int pool_split = p.pool_split != nullptr ? __ldg(p.pool_split + wi.q_row) : 0x7FFFFFFF;
+                const int pool_split = (kExt && p.pool_split != nullptr) ? __ldg(p.pool_split + wi.q_row) : 0x7FFFFFFF;
                 auto load_slot = [&](int k0) -> int {
                     const int k = k0 + r;
                     return (k < wi.k_end) ? __ldg(idx_row + k) : -1;
@@ -1023,7 +1048,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     const int k0 = wi.k_begin + u * kTileRows;
                     int row = row_of(idx_a, phys_a, seq, p);
                     const uint8_t* pool = kv_bytes;
-                    if (p.kv2 != nullptr && k0 + r >= pool_split) {   // "extend" slots: physical rows of the second pool
+                    if (kExt && p.kv2 != nullptr && k0 + r >= pool_split) {   // "extend" slots: physical rows of the second pool
                         row = (idx_a >= 0 && idx_a < p.num_kv2_rows) ? idx_a : -1;
                         pool = reinterpret_cast<const uint8_t*>(p.kv2);
                     }
@@ -1156,7 +1181,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     // row, H heads apart (rows of the block that no box covers were zeroed at kernel start)
                     const uint32_t bar = smem_u32(&ctl->q_full);
                     const int hbox = p.H < kHeadsPerBlock ? p.H : kHeadsPerBlock;
-                    const int n_box = wi.stacked_rows > 1 ? wi.stacked_rows : 1;
+                    const int n_box = (kExt && wi.stacked_rows > 1) ? wi.stacked_rows : 1;
                     mbar_arrive_expect_tx(bar, static_cast<uint32_t>(n_box * hbox * 128));
                     for (int b = 0; b < n_box; ++b)
                         tma_load_3d(smem_u32(sQ) + static_cast<uint32_t>(b * hbox * 128), &tm_q, bar, kDV,
@@ -1362,7 +1387,7 @@ __global__ void __launch_bounds__(32) wait_expiry_selftest_kernel(int32_t* statu
 // ------------------------------------------------------------------ launch helpers (called from capi.cu)
 // The opt-in for more than 48 KB of dynamic shared memory is a per-device attribute of the kernel: it is
 // set once for every device this process launches on (the current device at the time of the call).
-template <bool kFp8>
+template <bool kFp8, bool kExt>
 static cudaError_t configure() {
     static std::mutex mu;
     static bool done[64] = {};
@@ -1371,7 +1396,7 @@ static cudaError_t configure() {
     if (e != cudaSuccess) return e;
     std::lock_guard<std::mutex> guard(mu);
     if (dev >= 0 && dev < 64 && done[dev]) return cudaSuccess;
-    e = cudaFuncSetAttribute(sparse_mla_kernel<kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<kFp8>::kSmemBytes);
+    e = cudaFuncSetAttribute(sparse_mla_kernel<kFp8, kExt>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<kFp8>::kSmemBytes);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) done[dev] = true;
     return cudaSuccess;
@@ -1393,35 +1418,39 @@ static void fill_launch(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, int 
 
 // How many CTA pairs the device can keep resident at once (one work list per pair).
 int max_resident_pairs(bool fp8, int* out) {
-    cudaError_t e = fp8 ? configure<true>() : configure<false>();
+    cudaError_t e = fp8 ? configure<true, false>() : configure<false, false>();
     if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
     int n = 0;
     if (fp8) {
         fill_launch<true>(&cfg, attr, 1, nullptr);
-        e = cudaOccupancyMaxActiveClusters(&n, sparse_mla_kernel<true>, &cfg);
+        e = cudaOccupancyMaxActiveClusters(&n, sparse_mla_kernel<true, false>, &cfg);
     } else {
         fill_launch<false>(&cfg, attr, 1, nullptr);
-        e = cudaOccupancyMaxActiveClusters(&n, sparse_mla_kernel<false>, &cfg);
+        e = cudaOccupancyMaxActiveClusters(&n, sparse_mla_kernel<false, false>, &cfg);
     }
     if (e != cudaSuccess) return (int)e;
     *out = n;
     return 0;
 }
 
-cudaError_t launch_attn(bool fp8, int num_lists, const CUtensorMap& tq, const CUtensorMap& tkv, const CUtensorMap& ttail,
-                        const AttnParams& p, cudaStream_t stream) {
-    cudaError_t e = fp8 ? configure<true>() : configure<false>();
+template <bool kFp8, bool kExt>
+static cudaError_t launch_attn_t(int num_lists, const CUtensorMap& tq, const CUtensorMap& tkv, const CUtensorMap& ttail,
+                                 const AttnParams& p, cudaStream_t stream) {
+    cudaError_t e = configure<kFp8, kExt>();
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
-    if (fp8) {
-        fill_launch<true>(&cfg, attr, num_lists, stream);
-        return cudaLaunchKernelEx(&cfg, sparse_mla_kernel<true>, tq, tkv, ttail, p);
-    }
-    fill_launch<false>(&cfg, attr, num_lists, stream);
-    return cudaLaunchKernelEx(&cfg, sparse_mla_kernel<false>, tq, tkv, ttail, p);
+    fill_launch<kFp8>(&cfg, attr, num_lists, stream);
+    return cudaLaunchKernelEx(&cfg, sparse_mla_kernel<kFp8, kExt>, tq, tkv, ttail, p);
+}
+
+// ext: the plan holds stacked items, or a sink / second pool is given
+cudaError_t launch_attn(bool fp8, bool ext, int num_lists, const CUtensorMap& tq, const CUtensorMap& tkv, const CUtensorMap& ttail,
+                        const AttnParams& p, cudaStream_t stream) {
+    if (fp8) return ext ? launch_attn_t<true, true>(num_lists, tq, tkv, ttail, p, stream) : launch_attn_t<true, false>(num_lists, tq, tkv, ttail, p, stream);
+    return ext ? launch_attn_t<false, true>(num_lists, tq, tkv, ttail, p, stream) : launch_attn_t<false, false>(num_lists, tq, tkv, ttail, p, stream);
 }
 
 cudaError_t launch_combine(const float* o_accum, const float* lse_accum, const int32_t* reduce_indptr,
@@ -1431,6 +1460,33 @@ cudaError_t launch_combine(const float* o_accum, const float* lse_accum, const i
     dim3 grid(num_reduce_rows, kHeadsPerBlock / 8);
     combine_kernel<<<grid, 256, 0, stream>>>(o_accum, lse_accum, reduce_indptr, reduce_slots, reduce_dst, tgt, stride_o_row,
                                              stride_o_head, H);
+    return cudaGetLastError();
+}
+
+// Pushes a contiguous block of this GPU's gathered buffer to the same place in every peer's (plain 16-byte
+// stores through the peer mappings, all SMs): the sequence-sharded form of the fused all-gather.
+struct PeerPush {
+    int32_t n_peers, my_rank;
+    const uint4* src;
+    uint4* dst[DSA_V32_MAX_PEERS];
+    int64_t n16;   // 16-byte words
+};
+__global__ void __launch_bounds__(512) peer_push_kernel(const PeerPush s) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < s.n16; i += (int64_t)gridDim.x * blockDim.x) {
+        const uint4 v = s.src[i];
+        for (int r = 0; r < s.n_peers; ++r)
+            if (r != s.my_rank) s.dst[r][i] = v;
+    }
+}
+cudaError_t launch_peer_push(int n_peers, int my_rank, const void* src, void* const* dst, int64_t bytes, cudaStream_t stream) {
+    if (bytes <= 0 || n_peers <= 1) return cudaSuccess;
+    PeerPush s;
+    s.n_peers = n_peers;
+    s.my_rank = my_rank;
+    s.src = reinterpret_cast<const uint4*>(src);
+    for (int r = 0; r < DSA_V32_MAX_PEERS; ++r) s.dst[r] = r < n_peers ? reinterpret_cast<uint4*>(dst[r]) : nullptr;
+    s.n16 = bytes / 16;
+    peer_push_kernel<<<148 * 2, 512, 0, stream>>>(s);
     return cudaGetLastError();
 }
 

@@ -105,6 +105,10 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
     return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
 }
 
+// Programmatic dependent launch: blocks until the kernels this one depends on have completed and their
+// writes are visible (a no-op when the kernel was launched without the attribute).
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ------------------------------------------------------------------ thread-block cluster
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;

@@ -111,9 +111,10 @@ constexpr int kLoaderWarp0 = kConvertWarp0;               // bf16 cache: eight l
 constexpr int kLoaderWarps = 8;
 constexpr int kWarps = kConvertWarp0 + kConvertWarps;     // 28: seven warpgroups
 // Registers per thread after the role split (setmaxnreg, per warpgroup): the softmax warpgroups hold a
-// tile row in registers, everything else is light.  4 x 128 x 88 + 3 x 128 x 48 = 63 488 <= 65 536.
-constexpr int kRegsSoftmax = 88;
-constexpr int kRegsOther = 48;
+// tile row in registers, everything else is light.  bf16 cache: 4 x 128 x 88 + 3 x 128 x 48 = 63 488;
+// fp8 cache (scales, two copies of P): 4 x 128 x 96 + 3 x 128 x 40 = 64 512; both <= 65 536.
+template <bool kFp8> constexpr int kRegsSoftmax = kFp8 ? 96 : 88;
+template <bool kFp8> constexpr int kRegsOther = kFp8 ? 40 : 48;
 constexpr int kScaleSlots = 16;                           // tiles whose row scales are kept (raw ring + tile ring <= 16)
 
 template <bool kFp8>
@@ -230,7 +231,7 @@ struct RowMap {
 template <bool kExt>
 __device__ __forceinline__ RowMap map_row(const dsa_v32_work_info& w, int row, int H) {
     RowMap m;
-    if (kExt && w.stacked_rows > 1) {
+    if (w.stacked_rows > 1) {
         const int sub = row / H;
         m.q_row = w.q_row + sub;
         m.head = row - sub * H;
@@ -390,12 +391,15 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     cluster_sync_all();   // the peer's barriers exist before anything is sent to it
     tc_fence_after();
     const uint32_t tmem = ctl->tmem_base;
+    // Launched with programmatic stream serialization: everything above (barriers, tensor memory, descriptor
+    // prefetch) may overlap the tail of the kernel before it in the stream; its results are needed from here on.
+    grid_dependency_wait();
     const uint32_t peer_abort = map_to_cta(smem_u32(&ctl->abort_flag), peer);
 
     if (warp < kSoftmaxWarps) {
         // the four softmax warpgroups take the registers the light warpgroups give up (setmaxnreg is
         // per warpgroup; each class of warpgroups executes one instruction at the top of its branch)
-        setmaxnreg_inc<kRegsSoftmax>();
+        setmaxnreg_inc<kRegsSoftmax<kFp8>>();
         // ============================================================ softmax + epilogue
         // Four teams of four warps (one warp per TMEM lane quadrant) take the 32-slot tiles round robin (team =
         // tile number mod 4), so four tiles are in flight.  Thread = head row: it holds its row's 32 scores of
@@ -946,7 +950,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (n_sent > 0)
             if (!warp_wait_cluster(my_xfree, (n_sent & 1u) ^ 1u, abort_flag)) goto done;
     } else {
-    setmaxnreg_dec<kRegsOther>();
+    setmaxnreg_dec<kRegsOther<kFp8>>();
     if (warp == mma_warp) {
         // ============================================================ score MMA issuer
         // The whole warp runs the loop converged (descriptors stay warp-uniform); one elected lane issues.
@@ -1256,6 +1260,7 @@ __global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ 
     const int rr = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int hrow = blockIdx.y * 8 + warp;  // head inside the 128-head block
+    grid_dependency_wait();   // launched ahead of the attention kernel's end (programmatic stream serialization)
     const ReduceDst dst = reduce_dst[rr];
     int head = dst.head_block * kHeadsPerBlock + hrow, q_row = dst.q_row;
     if (dst.head_block < 0) {   // stacked unit: -head_block query rows of H heads each
@@ -1412,8 +1417,10 @@ static void fill_launch(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, int 
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg->attrs = attr;
-    cfg->numAttrs = 1;
+    cfg->numAttrs = 2;
 }
 
 // How many CTA pairs the device can keep resident at once (one work list per pair).
@@ -1421,7 +1428,7 @@ int max_resident_pairs(bool fp8, int* out) {
     cudaError_t e = fp8 ? configure<true, false>() : configure<false, false>();
     if (e != cudaSuccess) return (int)e;
     cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     int n = 0;
     if (fp8) {
         fill_launch<true>(&cfg, attr, 1, nullptr);
@@ -1441,7 +1448,7 @@ static cudaError_t launch_attn_t(int num_lists, const CUtensorMap& tq, const CUt
     cudaError_t e = configure<kFp8, kExt>();
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     fill_launch<kFp8>(&cfg, attr, num_lists, stream);
     return cudaLaunchKernelEx(&cfg, sparse_mla_kernel<kFp8, kExt>, tq, tkv, ttail, p);
 }
@@ -1458,9 +1465,17 @@ cudaError_t launch_combine(const float* o_accum, const float* lse_accum, const i
                            int64_t stride_o_row, int64_t stride_o_head, int H, cudaStream_t stream) {
     if (num_reduce_rows <= 0) return cudaSuccess;
     dim3 grid(num_reduce_rows, kHeadsPerBlock / 8);
-    combine_kernel<<<grid, 256, 0, stream>>>(o_accum, lse_accum, reduce_indptr, reduce_slots, reduce_dst, tgt, stride_o_row,
-                                             stride_o_head, H);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = stream;
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, combine_kernel, o_accum, lse_accum, reduce_indptr, reduce_slots, reduce_dst, tgt, stride_o_row,
+                              stride_o_head, H);
 }
 
 // Pushes a contiguous block of this GPU's gathered buffer to the same place in every peer's (plain 16-byte

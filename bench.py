@@ -523,13 +523,20 @@ def cfg4_leg(env, mode, steps, warmup):
 
 
 # --------------------------------------------------------------------------- host-buffer leg of the headline
-def e2e_leg(env, W, out, lse, K, num_chunks):
+def e2e_leg(env, W, out, lse, K, num_chunks, num_lanes=1):
     """K steps through the host-buffer C-ABI call: pinned host q / index lists in, out / lse back, the caller
     synchronising on every step's result.  num_chunks > 1: the call that cuts the batch into groups of
-    sequences whose PCIe copies overlap the other groups' kernels (its plan is for one group's shape)."""
+    sequences whose PCIe copies overlap the other groups' kernels (its plan is for one group's shape);
+    num_lanes > 1: that many groups' kernels side by side, each on its share of the SMs."""
     api, torch = env.api, env.torch
     B, H = W["B"], W["H"]
-    plan = api.mla_decode_plan_create(B // num_chunks, H, W["topk"], 1, valid_len_hint=[W["n_valid"]] * (B // num_chunks))
+    hint = [W["n_valid"]] * (B // num_chunks)
+    plan = api.mla_decode_plan_create(B // num_chunks, H, W["topk"], 1, valid_len_hint=hint)
+    lane_plans = None
+    if num_lanes > 1:
+        sms = torch.cuda.get_device_properties(0).multi_processor_count // num_lanes // 2 * 2
+        lane_plans = [api.mla_decode_plan_create(B // num_chunks, H, W["topk"], 1, valid_len_hint=hint, num_sms=sms)
+                      for _ in range(num_lanes)]
     q_host = [q.cpu().pin_memory() for (q, _) in W["steps"]]
     i_host = [idx.cpu().pin_memory() for (_, idx) in W["steps"]]
     out_host = torch.empty(B, H, D_V, dtype=torch.bfloat16).pin_memory()
@@ -539,14 +546,16 @@ def e2e_leg(env, W, out, lse, K, num_chunks):
     a_e2e = api.make_args(q_dev, W["cache"], i_dev, plan, SM_SCALE, out=out, lse=lse, block_table=W["block_table"],
                           page_block_size=W["page"])
     for i in range(3):
-        api.mla_decode_step_host(a_e2e, q_host[i % len(q_host)], i_host[i % len(i_host)], out_host, lse_host, num_chunks)
+        api.mla_decode_step_host(a_e2e, q_host[i % len(q_host)], i_host[i % len(i_host)], out_host, lse_host, num_chunks,
+                                 lane_plans=lane_plans)
     torch.cuda.synchronize()
     api._check(env.L.dsa_v32_device_status(C.byref(a_e2e), env.stream()), "device status (host-buffer leg)")
     g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     env.barrier()
     g0.record()
     for i in range(K):
-        api.mla_decode_step_host(a_e2e, q_host[i % len(q_host)], i_host[i % len(i_host)], out_host, lse_host, num_chunks)
+        api.mla_decode_step_host(a_e2e, q_host[i % len(q_host)], i_host[i % len(i_host)], out_host, lse_host, num_chunks,
+                                 lane_plans=lane_plans)
         torch.cuda.current_stream().synchronize()   # the caller reads the step's result before the next step
     g1.record()
     env.barrier()
@@ -590,7 +599,17 @@ def headline_leg(env, args):
     stream = env.stream()
     env.barrier()
     env.sampler.start()
+    # the timed region: K steps of the pipeline call a user makes (attention + merge, launched back to back)
     e0.record()
+    for i in range(K):
+        rc = L.dsa_v32_decode_pipeline(C.byref(arg_sets[i % len(arg_sets)]), 0, stream)
+        if rc:
+            raise api.DsaError(rc, "decode step")
+    e1.record()
+    env.barrier()
+    # the same K steps once more with an event pair around every attention launch: the kernel's own duration
+    # for the roofline (events between the launches keep the merge kernel from overlapping the attention
+    # kernel's tail, so this pass is a little slower than the timed one and is not the reported step time)
     for i in range(K):
         a = arg_sets[i % len(arg_sets)]
         ev_a[i].record()
@@ -599,7 +618,6 @@ def headline_leg(env, args):
         rc = rc or L.dsa_v32_combine(C.byref(a), stream)
         if rc:
             raise api.DsaError(rc, "decode step")
-    e1.record()
     env.barrier()
     env.sampler.stop()
     total_ms = e0.elapsed_time(e1)
@@ -609,9 +627,14 @@ def headline_leg(env, args):
 
     e2e_ms, e2e1_ms, h2d, d2h = float("nan"), float("nan"), 0, 0
     e2e_chunks = 4 if B % 4 == 0 and B >= 16 else 1
+    e2e_lanes = 1
     if not args.no_e2e:
         e2e1_ms, h2d, d2h = e2e_leg(env, W, out, lse, K, 1)
         e2e_ms = e2e_leg(env, W, out, lse, K, e2e_chunks)[0] if e2e_chunks > 1 else e2e1_ms
+        if e2e_chunks > 1:   # two groups' kernels side by side on half the SMs each; the faster form is reported
+            e2e2_ms = e2e_leg(env, W, out, lse, K, e2e_chunks, 2)[0]
+            if e2e2_ms < e2e_ms:
+                e2e_ms, e2e_lanes = e2e2_ms, 2
 
     t = torch.tensor([total_ms, attn_ms, e2e_ms, e2e1_ms], dtype=torch.float64, device="cuda")
     if env.world > 1:
@@ -621,6 +644,11 @@ def headline_leg(env, args):
     pk = peaks()
     ms_per_step = total_ms / K
     value = world * step_flops / (ms_per_step * 1e-3) / 1e12
+    # The attention kernel's duration: the event pairs of the second pass keep the next launch's set-up from
+    # overlapping the kernel before it, so a launch there takes longer than a whole step of the timed region;
+    # the step time (attention + merge when the plan splits items) is then the tighter upper bound of the two.
+    attn_events_ms = attn_ms
+    attn_ms = min(attn_ms, ms_per_step)
     attn_tf = step_flops / (attn_ms * 1e-3) / 1e12
     gathered = pairs * 656.0
     line = dict(metric="sparse_mla_decode_fp8_tflops", value=value, unit="TFLOP/s", n_gpus=world, steps=K,
@@ -630,14 +658,18 @@ def headline_leg(env, args):
                 roofline=dict(bound="tensor", achieved=attn_tf, peak=pk["bf16_tflops"], unit="TFLOP/s",
                               frac=attn_tf / pk["bf16_tflops"], traffic=measured_traffic(B),
                               peak_source=pk["source"], kernel="sparse_mla_kernel<fp8>", kernel_us=attn_ms * 1e3,
+                              kernel_us_between_events=attn_events_ms * 1e3,
                               flops_per_launch=step_flops, gathered_bytes_per_launch=gathered,
                               gathered_gbs=gathered / (attn_ms * 1e-3) / 1e9, hbm_peak_gbs=pk["hbm_gbs"],
                               t_flop_us=step_flops / (pk["bf16_tflops"] * 1e12) * 1e6,
                               t_mem_us=gathered / (pk["hbm_gbs"] * 1e9) * 1e6),
                 e2e=None if args.no_e2e else dict(value=world * step_flops / (e2e_ms / K * 1e-3) / 1e12, unit="TFLOP/s",
                                                   ms_per_step=e2e_ms / K, h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
-                                                  call="dsa_v32_decode_pipeline_host_chunked, %d groups of sequences "
-                                                       "(copies overlap the other groups' kernels)" % e2e_chunks,
+                                                  call=("dsa_v32_decode_pipeline_host_chunked, %d groups of sequences "
+                                                        "(copies overlap the other groups' kernels)" % e2e_chunks)
+                                                  if e2e_lanes == 1 else
+                                                  ("dsa_v32_decode_pipeline_host_lanes, %d groups of sequences, the kernels "
+                                                   "of %d groups side by side" % (e2e_chunks, e2e_lanes)),
                                                   ms_per_step_unchunked=e2e1_ms / K),
                 gpu_launches=K * (2 if plan.info.num_partials > 0 else 1), clocks=clocks)
     del W, plan, out, lse, arg_sets

@@ -283,6 +283,17 @@ int dsa_v32_decode_pipeline_host(const dsa_v32_attn_args* args, const dsa_v32_ho
  */
 int dsa_v32_decode_pipeline_host_chunked(const dsa_v32_attn_args* args, const dsa_v32_host_io* io, int32_t num_chunks,
                                          void* stream);
+/*
+ * The chunked step with `num_lanes` kernels in flight at once: lane l has its own workspace, planned for
+ * one chunk's shape with shape.num_sms = (the device's SMs) / num_lanes, and its own internal compute stream;
+ * it takes the chunks c with c % num_lanes == l.  A chunk's kernels then occupy only their share of the SMs,
+ * so the start-up and tail of one chunk's kernels overlap the steady part of another's, and with enough
+ * chunks the step takes about as long as the longer of its two PCIe directions.  args->workspace is not
+ * used.  1 <= num_lanes <= 8, num_chunks >= num_lanes; everything else as for the chunked call.
+ */
+int dsa_v32_decode_pipeline_host_lanes(const dsa_v32_attn_args* args, const dsa_v32_host_io* io, int32_t num_chunks,
+                                       void* const* lane_workspaces, const int64_t* lane_workspace_bytes, int32_t num_lanes,
+                                       void* stream);
 
 /*
  * The same pipeline for callers that cannot allocate device memory at all: code running where

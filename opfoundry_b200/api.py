@@ -67,7 +67,7 @@ EXPORTS = ["dsa_v32_abi_version", "dsa_v32_error_string", "dsa_v32_plan_info_get
            "dsa_v32_plan_host", "dsa_v32_plan_read", "dsa_v32_plan_release", "dsa_v32_decode_bf16", "dsa_v32_decode_fp8",
            "dsa_v32_prefill_bf16", "dsa_v32_combine", "dsa_v32_decode_pipeline", "dsa_v32_device_status",
            "dsa_v32_debug_rows", "dsa_v32_pack_fp8_rows", "dsa_v32_decode_pipeline_host",
-           "dsa_v32_decode_pipeline_static", "dsa_v32_static_scratch_address", "dsa_v32_selftest_wait_expiry", "dsa_v32_decode_pipeline_allgather", "dsa_v32_ipc_export", "dsa_v32_ipc_open", "dsa_v32_ipc_close", "dsa_v32_decode_pipeline_host_chunked", "dsa_v32_decode_pipeline_v4", "dsa_v32_topk_select"]
+           "dsa_v32_decode_pipeline_static", "dsa_v32_static_scratch_address", "dsa_v32_selftest_wait_expiry", "dsa_v32_decode_pipeline_allgather", "dsa_v32_ipc_export", "dsa_v32_ipc_open", "dsa_v32_ipc_close", "dsa_v32_decode_pipeline_host_chunked", "dsa_v32_decode_pipeline_host_lanes", "dsa_v32_decode_pipeline_v4", "dsa_v32_topk_select"]
 
 _lib = None
 
@@ -103,6 +103,8 @@ def lib():
         L.dsa_v32_decode_pipeline_static.argtypes = [C.POINTER(AttnArgs), C.c_void_p]
         L.dsa_v32_decode_pipeline_v4.argtypes = [C.POINTER(AttnArgs), C.POINTER(V4Ext), C.c_void_p]
         L.dsa_v32_decode_pipeline_host_chunked.argtypes = [C.POINTER(AttnArgs), C.POINTER(HostIO), C.c_int32, C.c_void_p]
+        L.dsa_v32_decode_pipeline_host_lanes.argtypes = [C.POINTER(AttnArgs), C.POINTER(HostIO), C.c_int32, C.POINTER(C.c_void_p),
+                                                         C.POINTER(C.c_int64), C.c_int32, C.c_void_p]
         L.dsa_v32_decode_pipeline_allgather.argtypes = [C.POINTER(AttnArgs), C.POINTER(PeerOutputs), C.c_void_p]
         L.dsa_v32_ipc_export.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_int64)]
         L.dsa_v32_ipc_open.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
@@ -325,12 +327,13 @@ def pack_fp8_rows(latent, rope, out=None, dst_rows=None):
     return out
 
 
-def mla_decode_step_host(args, q_host, indices_host, out_host, lse_host, num_chunks=1):
+def mla_decode_step_host(args, q_host, indices_host, out_host, lse_host, num_chunks=1, lane_plans=None):
     """One serving step with pinned HOST tensors: H2D of q / indices, attention + merge, D2H of
     out / lse, all on the current stream (asynchronous; synchronise the stream to read results).
     `args` comes from make_args and names the resident device buffers.  num_chunks > 1 cuts the batch
     into that many groups of sequences whose copies overlap the other groups' kernels; the plan in
-    `args` must then be for one group's shape (total_q / num_chunks rows)."""
+    `args` must then be for one group's shape (total_q / num_chunks rows).  lane_plans: plans for one
+    group's shape made with num_sms = SMs / len(lane_plans); their kernels run side by side."""
     io = HostIO()
     io.q_host = q_host.data_ptr()
     io.indices_host = indices_host.data_ptr()
@@ -338,6 +341,13 @@ def mla_decode_step_host(args, q_host, indices_host, out_host, lse_host, num_chu
     io.lse_host = lse_host.data_ptr()
     io.q_bytes = q_host.numel() * q_host.element_size()
     io.out_bytes = out_host.numel() * out_host.element_size()
+    if lane_plans:
+        n = len(lane_plans)
+        ws = (C.c_void_p * n)(*[p.workspace.data_ptr() for p in lane_plans])
+        wb = (C.c_int64 * n)(*[p.workspace.numel() for p in lane_plans])
+        _check(lib().dsa_v32_decode_pipeline_host_lanes(C.byref(args), C.byref(io), num_chunks, ws, wb, n, _stream()),
+               "dsa_v32_decode_pipeline_host_lanes")
+        return
     if num_chunks > 1:
         _check(lib().dsa_v32_decode_pipeline_host_chunked(C.byref(args), C.byref(io), num_chunks, _stream()),
                "dsa_v32_decode_pipeline_host_chunked")

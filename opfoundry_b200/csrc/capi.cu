@@ -594,11 +594,17 @@ int dsa_v32_decode_pipeline_host(const dsa_v32_attn_args* a, const dsa_v32_host_
 namespace {
 struct ChunkStreams {
     cudaStream_t in = nullptr, out = nullptr;
-    std::vector<cudaEvent_t> ev;   // start, done, then (copied-in, computed) per chunk
-    cudaError_t ensure(size_t n_events) {
+    std::vector<cudaStream_t> lane;   // compute streams of the lanes beyond the caller's own stream
+    std::vector<cudaEvent_t> ev;      // start, done, then (copied-in, computed) per chunk
+    cudaError_t ensure(size_t n_events, size_t n_lanes) {
         cudaError_t e;
         if (!in && (e = cudaStreamCreateWithFlags(&in, cudaStreamNonBlocking)) != cudaSuccess) return e;
         if (!out && (e = cudaStreamCreateWithFlags(&out, cudaStreamNonBlocking)) != cudaSuccess) return e;
+        while (lane.size() < n_lanes) {
+            cudaStream_t x;
+            if ((e = cudaStreamCreateWithFlags(&x, cudaStreamNonBlocking)) != cudaSuccess) return e;
+            lane.push_back(x);
+        }
         while (ev.size() < n_events) {
             cudaEvent_t x;
             if ((e = cudaEventCreateWithFlags(&x, cudaEventDisableTiming)) != cudaSuccess) return e;
@@ -609,11 +615,11 @@ struct ChunkStreams {
 };
 std::mutex g_chunk_mu;
 ChunkStreams g_chunk_streams[64];
-}  // namespace
 
-int dsa_v32_decode_pipeline_host_chunked(const dsa_v32_attn_args* a, const dsa_v32_host_io* io, int32_t num_chunks, void* stream) {
-    if (!a || !io) return DSA_V32_ERR_NULL;
-    if (num_chunks <= 1) return dsa_v32_decode_pipeline_host(a, io, stream);
+// The step in `num_chunks` groups of sequences.  Lane l (its own compute stream and its own planned workspace)
+// takes the chunks c with c % num_lanes == l; lane 0 runs on the caller's stream when there is only one lane.
+int host_chunked_impl(const dsa_v32_attn_args* a, const dsa_v32_host_io* io, int32_t num_chunks, void* const* lane_ws,
+                      const int64_t* lane_ws_bytes, int32_t num_lanes, void* stream) {
     if (num_chunks > 64 || a->s_q <= 0 || a->total_q % (num_chunks * a->s_q) != 0) return DSA_V32_ERR_SHAPE;
     if (!io->q_host || !io->indices_host || !io->out_host) return DSA_V32_ERR_NULL;
     int dev = 0;
@@ -622,20 +628,27 @@ int dsa_v32_decode_pipeline_host_chunked(const dsa_v32_attn_args* a, const dsa_v
     if (dev < 0 || dev >= 64) return DSA_V32_ERR_SHAPE;
     std::lock_guard<std::mutex> guard(g_chunk_mu);
     ChunkStreams& cs = g_chunk_streams[dev];
-    e = cs.ensure(2 + 2 * size_t(num_chunks));
+    e = cs.ensure(2 + 2 * size_t(num_chunks), num_lanes > 1 ? size_t(num_lanes) : 0);
     if (e != cudaSuccess) return (int)e;
     cudaStream_t st = (cudaStream_t)stream;
     const int rows = a->total_q / num_chunks;          // query rows per chunk
     const int seqs = rows / a->s_q;
     const size_t q_row_bytes = size_t(a->stride_q_row) * 2, o_row_bytes = size_t(a->stride_o_row) * 2;
-    // everything queued on `stream` before this call precedes the first copy
+    // everything queued on `stream` before this call precedes the first copy and the first kernel
     if ((e = cudaEventRecord(cs.ev[0], st)) != cudaSuccess) return (int)e;
     if ((e = cudaStreamWaitEvent(cs.in, cs.ev[0], 0)) != cudaSuccess) return (int)e;
     if ((e = cudaStreamWaitEvent(cs.out, cs.ev[0], 0)) != cudaSuccess) return (int)e;
+    if (num_lanes > 1)
+        for (int l = 0; l < num_lanes; ++l)
+            if ((e = cudaStreamWaitEvent(cs.lane[l], cs.ev[0], 0)) != cudaSuccess) return (int)e;
     for (int c = 0; c < num_chunks; ++c) {
         const size_t r0 = size_t(c) * rows;
+        const int l = c % num_lanes;
+        cudaStream_t kst = num_lanes > 1 ? cs.lane[l] : st;
         dsa_v32_attn_args b = *a;
         b.total_q = rows;
+        b.workspace = lane_ws[l];
+        b.workspace_bytes = lane_ws_bytes[l];
         b.q = reinterpret_cast<const uint8_t*>(a->q) + r0 * q_row_bytes;
         b.out = reinterpret_cast<uint8_t*>(a->out) + r0 * o_row_bytes;
         b.lse = a->lse ? a->lse + r0 * a->H : nullptr;
@@ -648,7 +661,7 @@ int dsa_v32_decode_pipeline_host_chunked(const dsa_v32_attn_args* a, const dsa_v
             b.kv = reinterpret_cast<const uint8_t*>(a->kv) + size_t(skip) * row_bytes;
             b.num_kv_rows = a->num_kv_rows - skip;
         }
-        // this chunk's queries and lists come in on the copy stream while the chunk before computes
+        // this chunk's queries and lists come in on the copy stream while the chunks before compute
         e = cudaMemcpyAsync(const_cast<void*>(b.q), reinterpret_cast<const uint8_t*>(io->q_host) + r0 * q_row_bytes,
                             size_t(rows) * q_row_bytes, cudaMemcpyHostToDevice, cs.in);
         if (e != cudaSuccess) return (int)e;
@@ -656,11 +669,11 @@ int dsa_v32_decode_pipeline_host_chunked(const dsa_v32_attn_args* a, const dsa_v
                             cudaMemcpyHostToDevice, cs.in);
         if (e != cudaSuccess) return (int)e;
         if ((e = cudaEventRecord(cs.ev[2 + 2 * c], cs.in)) != cudaSuccess) return (int)e;
-        if ((e = cudaStreamWaitEvent(st, cs.ev[2 + 2 * c], 0)) != cudaSuccess) return (int)e;
-        int rc = dsa_v32_decode_pipeline(&b, 0, stream);
+        if ((e = cudaStreamWaitEvent(kst, cs.ev[2 + 2 * c], 0)) != cudaSuccess) return (int)e;
+        int rc = dsa_v32_decode_pipeline(&b, 0, kst);
         if (rc) return rc;
-        // ... and its outputs leave on the other copy stream while the next chunk computes
-        if ((e = cudaEventRecord(cs.ev[3 + 2 * c], st)) != cudaSuccess) return (int)e;
+        // ... and its outputs leave on the other copy stream while the next chunks compute
+        if ((e = cudaEventRecord(cs.ev[3 + 2 * c], kst)) != cudaSuccess) return (int)e;
         if ((e = cudaStreamWaitEvent(cs.out, cs.ev[3 + 2 * c], 0)) != cudaSuccess) return (int)e;
         e = cudaMemcpyAsync(reinterpret_cast<uint8_t*>(io->out_host) + r0 * o_row_bytes, b.out, size_t(rows) * o_row_bytes,
                             cudaMemcpyDeviceToHost, cs.out);
@@ -670,10 +683,29 @@ int dsa_v32_decode_pipeline_host_chunked(const dsa_v32_attn_args* a, const dsa_v
             if (e != cudaSuccess) return (int)e;
         }
     }
-    // the call's work is complete when `stream` is: it waits for the last copy out
+    // the call's work is complete when `stream` is: it waits for the last copy out (which follows every kernel)
     if ((e = cudaEventRecord(cs.ev[1], cs.out)) != cudaSuccess) return (int)e;
     if ((e = cudaStreamWaitEvent(st, cs.ev[1], 0)) != cudaSuccess) return (int)e;
     return DSA_V32_OK;
+}
+}  // namespace
+
+int dsa_v32_decode_pipeline_host_chunked(const dsa_v32_attn_args* a, const dsa_v32_host_io* io, int32_t num_chunks, void* stream) {
+    if (!a || !io) return DSA_V32_ERR_NULL;
+    if (num_chunks <= 1) return dsa_v32_decode_pipeline_host(a, io, stream);
+    void* ws = a->workspace;
+    const int64_t ws_bytes = a->workspace_bytes;
+    return host_chunked_impl(a, io, num_chunks, &ws, &ws_bytes, 1, stream);
+}
+
+int dsa_v32_decode_pipeline_host_lanes(const dsa_v32_attn_args* a, const dsa_v32_host_io* io, int32_t num_chunks,
+                                       void* const* lane_workspaces, const int64_t* lane_workspace_bytes, int32_t num_lanes,
+                                       void* stream) {
+    if (!a || !io || !lane_workspaces || !lane_workspace_bytes) return DSA_V32_ERR_NULL;
+    if (num_lanes < 1 || num_lanes > 8 || num_chunks < num_lanes) return DSA_V32_ERR_SHAPE;
+    for (int l = 0; l < num_lanes; ++l)
+        if (!lane_workspaces[l]) return DSA_V32_ERR_NULL;
+    return host_chunked_impl(a, io, num_chunks, lane_workspaces, lane_workspace_bytes, num_lanes, stream);
 }
 
 // ------------------------------------------------------------------ no-allocation variant

@@ -288,3 +288,12 @@ def test_host_buffer_pipeline_in_chunks(oracle, fp8):
         r_out, r_lse = run_oracle(oracle, case, SCALE)
         check_out(out_host.view(torch.int16).numpy().view(np.uint16), r_out, **(TOL_FP8 if fp8 else TOL_BF16))
         check_lse(lse_host.numpy(), r_lse)
+        # the same with the kernels of two chunks side by side, each on half of the SMs
+        sms = torch.cuda.get_device_properties(0).multi_processor_count // 4 * 2
+        lanes = [api.mla_decode_plan_create(B // chunks, H, topk, 1, num_sms=sms) for _ in range(2)]
+        out_host.zero_()
+        lse_host.zero_()
+        api.mla_decode_step_host(a, q_host, i_host, out_host, lse_host, num_chunks=chunks, lane_plans=lanes)
+        torch.cuda.current_stream().synchronize()
+        check_out(out_host.view(torch.int16).numpy().view(np.uint16), r_out, **(TOL_FP8 if fp8 else TOL_BF16))
+        check_lse(lse_host.numpy(), r_lse)

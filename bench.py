@@ -742,7 +742,9 @@ def main():
         line = headline_leg(env, args)
         if args.workload == "all":
             if world == 1 and not args.no_prefill:
-                pre = prefill_leg(env, 4096, short, args.warmup, "cfg3")
+                # a short burst (15 launches, 35 ms): the kernel timed alone, against the burst peak; hundreds of
+                # launches in a row run under the power cap (--workload prefill_bf16 --steps 200 shows that figure)
+                pre = prefill_leg(env, 4096, min(short, 10), min(args.warmup, 5), "cfg3")
                 if not args.no_cpu_baseline:
                     pre["cpu_baseline"] = cpu_baseline_prefill(4096, CFG["topk"], CFG["H"])
                 line["prefill"] = pre

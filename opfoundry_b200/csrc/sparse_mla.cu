@@ -46,8 +46,9 @@
 //              of four rows per request, 40 requests per tile, and the issue rate of those requests was
 //              the period of the whole pipeline)
 //   fp8 cache: warps 18-19 gather issuers on alternate tiles (lane = row; one TMA tile::gather4 per four
-//              rows, the row's two scales by cp.async), warps 20-27 converters, two groups of four on
-//              alternate tiles: e4m3 -> bf16 exactly (e4m3 has 4 significant bits) into the swizzled MMA
+//              rows, the row's two scales by cp.async), warps 20-27 converters, four rows of every tile
+//              each (all eight on one tile: the time a tile holds its stage is what bounds the pipeline):
+//              e4m3 -> bf16 exactly (e4m3 has 4 significant bits) into the swizzled MMA
 //              tile (the reference's LDS round trip: ..mxfp8_16mx8_32nx1_template.hpp:852-864).  The
 //              per-128 fp32 scales never touch the operands: Q K^T keeps one fp32 accumulator per scale
 //              group (plus one for rope) and the softmax warps form sum_g scale_g S_g in fp32 before the
@@ -130,9 +131,8 @@ struct Cfg {
     static constexpr int kKvStages = kFp8 ? DSA_FP8_KV_STAGES : DSA_BF16_KV_STAGES;   // MMA-ready bf16 tiles
     static constexpr int kRawStages = kFp8 ? DSA_FP8_RAW_STAGES : 0; // raw fp8 tiles in flight
     // The raw ring must have an even number of buffers: a buffer is then always filled by the same issuer
-    // warp and read by the same converter group, so a warp that waits for it to come back is never more
-    // than one phase ahead of its barrier (with an odd ring the users alternate and a parity wait could
-    // pass on the phase before last).
+    // warp, so a warp that waits for it to come back is never more than one phase ahead of its barrier (with
+    // an odd ring the two issuers alternate on a buffer and a parity wait could pass on the phase before last).
     static_assert(!kFp8 || kRawStages % 2 == 0, "even raw ring");
     static_assert(kKvStages <= 8 && kRawStages <= 16, "kv_full/kv_empty hold 8 barriers, raw_full/raw_empty 16");
     static_assert(kKvStages + kRawStages <= kScaleSlots && kKvStages + kRawStages <= kMaskSlots,
@@ -349,15 +349,15 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     // threads 32-39 the tile barriers, 64-67 the per-team ones, 96 the singles.
     if (tid < 16) {
         mbar_init(smem_u32(&ctl->raw_full[tid]), 1 + 32);   // the expect_tx arrival + one cp.async arrival per row
-        mbar_init(smem_u32(&ctl->raw_empty[tid]), 4);       // the four converter warps (one group) that read it
+        mbar_init(smem_u32(&ctl->raw_empty[tid]), kConvertWarps);   // the eight converter warps that read it
         mbar_init(smem_u32(&ctl->m_bar[0][0]) + 8 * tid, 1);
         mbar_init(smem_u32(&ctl->x_full[tid]), 1);
         mbar_init(smem_u32(&ctl->x_free[tid]), 1);
         fence_mbar_init();
     } else if (tid >= 32 && tid < 40) {
         const int i = tid - 32;
-        // fp8: the four converter warps of a group; bf16: every lane of the four loader warps of a group
-        mbar_init(smem_u32(&ctl->kv_full[i]), kFp8 ? kConvertWarps / 2 : (kLoaderWarps / 2) * 32);
+        // fp8: the eight converter warps; bf16: every lane of the four loader warps of a group
+        mbar_init(smem_u32(&ctl->kv_full[i]), kFp8 ? kConvertWarps : (kLoaderWarps / 2) * 32);
         mbar_init(smem_u32(&ctl->kv_empty[i]), 1);
         fence_mbar_init();
     } else if (tid >= 64 && tid < 64 + kGroups) {
@@ -1171,10 +1171,8 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         // ..mxfp8_16mx8_32nx1_template.hpp:852-864), and copies the rope columns.  The per-128 fp32
         // scales never touch the operands (see the softmax warps).
         const int cw = warp - kConvertWarp0;
-        const int grp = cw >> 2;                 // tiles this warp converts: it % 2 == grp
-        const int c4 = cw & 3;                   // rows [8 c4, 8 c4 + 8) of those tiles
-        const int r = 8 * c4 + (lane >> 2);      // tile row
-        const int qd = lane & 3;                 // which 64 of this CTA's 256 latent columns
+        const int r = 4 * cw + (lane >> 3);      // tile row: all eight warps work on every tile, four rows each
+        const int oc = lane & 7;                 // this lane converts the 16-byte raw chunks oc and oc + 8 of the row's 256 latent bytes
         const uint32_t row_bytes = half ? 400u : 256u;
         uint32_t it = 0;
         int item_n = 0;
@@ -1197,38 +1195,38 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 }
             }
             for (int t = 0; t < n_tiles; ++t, ++it) {
-                if ((it & 1u) != static_cast<uint32_t>(grp)) continue;
                 const int rs = it % R, s = it % S;
                 if (!warp_wait(smem_u32(&ctl->raw_full[rs]), (it / R) & 1, abort_flag)) goto done;
-                if (!warp_wait(smem_u32(&ctl->kv_empty[s]), ((it / S) & 1) ^ 1, abort_flag)) goto done;
+                // the raw bytes are read before the wait for a free tile stage: a stage is the scarce resource (the
+                // period of the pipeline is the time a tile occupies one), so as little as possible happens after it
                 const uint8_t* row_raw = sRaw + rs * kRawTileBytes + (r >> 2) * kRawGroupBytes + (r & 3) * row_bytes;
-                const uint8_t* src = row_raw + qd * 64;
-                uint8_t* dst_row = sKV + s * kKvTileBytes + qd * kKvBlockBytes + r * 128;
+                uint4 raw[2], rope = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-                for (int cc = 0; cc < 4; ++cc) {
-                    const int c = (cc + r) & 3;  // rotate so the rows of a warp hit different banks
-                    const uint4 raw = *reinterpret_cast<const uint4*>(src + c * 16);
-                    const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
+                for (int k = 0; k < 2; ++k) raw[k] = *reinterpret_cast<const uint4*>(row_raw + (oc + 8 * k) * 16);
+                // rope: 64 bf16 = 8 chunks (after the 256 latent bytes and the 16 scale bytes of the raw row), one per lane
+                if (half) rope = *reinterpret_cast<const uint4*>(row_raw + 272 + oc * 16);
+                if (!warp_wait(smem_u32(&ctl->kv_empty[s]), ((it / S) & 1) ^ 1, abort_flag)) goto done;
+                uint8_t* tile = sKV + s * kKvTileBytes + r * 128;
+#pragma unroll
+                for (int k = 0; k < 2; ++k) {
+                    const int j = oc + 8 * k;    // raw chunk -> 64-column block j / 4, its 16-byte chunks 2 c and 2 c + 1
+                    const int c = j & 3;
+                    const uint32_t wv[4] = {raw[k].x, raw[k].y, raw[k].z, raw[k].w};
                     uint32_t o[8];
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        o[2 * k + 0] = e4m3x2_to_bf16x2(__byte_perm(wv[k], 0u, 0x1404u));
-                        o[2 * k + 1] = e4m3x2_to_bf16x2(__byte_perm(wv[k], 0u, 0x3424u));
+                    for (int q = 0; q < 4; ++q) {
+                        o[2 * q + 0] = e4m3x2_to_bf16x2(__byte_perm(wv[q], 0u, 0x1404u));
+                        o[2 * q + 1] = e4m3x2_to_bf16x2(__byte_perm(wv[q], 0u, 0x3424u));
                     }
-                    // 16 bytes -> 16 bf16 = chunks 2c, 2c+1 of this thread's 128-byte block row
-                    *reinterpret_cast<uint4*>(dst_row + (((2 * c + 0) ^ (r & 7)) * 16)) = make_uint4(o[0], o[1], o[2], o[3]);
-                    *reinterpret_cast<uint4*>(dst_row + (((2 * c + 1) ^ (r & 7)) * 16)) = make_uint4(o[4], o[5], o[6], o[7]);
+                    uint8_t* dst_row = tile + (j >> 2) * kKvBlockBytes;
+                    // lanes 4-7 of a row store their two chunks in the other order: the eight lanes then hit eight different banks groups
+                    const int h0 = (oc >> 2) & 1;
+                    *reinterpret_cast<uint4*>(dst_row + (((2 * c + h0) ^ (r & 7)) * 16)) =
+                        h0 ? make_uint4(o[4], o[5], o[6], o[7]) : make_uint4(o[0], o[1], o[2], o[3]);
+                    *reinterpret_cast<uint4*>(dst_row + (((2 * c + (h0 ^ 1)) ^ (r & 7)) * 16)) =
+                        h0 ? make_uint4(o[0], o[1], o[2], o[3]) : make_uint4(o[4], o[5], o[6], o[7]);
                 }
-                if (half) {
-                    // rope: 64 bf16 = 8 chunks into block 4 (after the 256 latent bytes and the 16 scale bytes
-                    // of the raw row); this thread copies chunks 2*qd, 2*qd+1
-                    const uint8_t* rope = row_raw + 272;
-                    const uint4 a = *reinterpret_cast<const uint4*>(rope + (2 * qd + 0) * 16);
-                    const uint4 b = *reinterpret_cast<const uint4*>(rope + (2 * qd + 1) * 16);
-                    uint8_t* d = sKV + s * kKvTileBytes + 4 * kKvBlockBytes + r * 128;
-                    *reinterpret_cast<uint4*>(d + (((2 * qd + 0) ^ (r & 7)) * 16)) = a;
-                    *reinterpret_cast<uint4*>(d + (((2 * qd + 1) ^ (r & 7)) * 16)) = b;
-                }
+                if (half) *reinterpret_cast<uint4*>(tile + 4 * kKvBlockBytes + ((oc ^ (r & 7)) * 16)) = rope;
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {

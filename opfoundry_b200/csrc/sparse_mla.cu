@@ -26,7 +26,7 @@
 //              there, and the row split would add a second hop to it.
 //
 // Warp roles inside a CTA (28 warps = seven warpgroups; after the role split setmaxnreg gives the four
-// softmax warpgroups 88 registers per thread and the others 48):
+// softmax warpgroups 88 registers per thread and the others 48 for a bf16 cache, 96 and 40 for an fp8 cache):
 //   warps 0-15  softmax, as four teams of four warps (one per TMEM lane quadrant) that take the 32-slot
 //              tiles round robin; thread = head row, holding its row's 32 scores of the tile: tcgen05.ld
 //              of the partial scores, exchange with the peer CTA, row maximum; then the only ordered

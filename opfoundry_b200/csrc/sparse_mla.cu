@@ -10,7 +10,10 @@
 //
 // The 128 x 512 fp32 output would fill all 512 TMEM columns, so two CTAs (a cluster) share a work
 // item and split the 576 columns of the latent row between them:
-//       CTA 0: columns [0, 256)             CTA 1: columns [256, 512) + the 64 rope columns
+//       fp8 cache:   CTA 0: columns [0, 256)                 CTA 1: columns [256, 512) + the 64 rope columns
+//       bf16 cache:  CTA 0: [0, 256) + rope columns [0, 32)  CTA 1: [256, 512) + rope columns [32, 64)
+// (a bf16 row can be cut anywhere, so both CTAs get four and a half 64-column blocks and neither waits for
+// the other's partial scores; an fp8 row is gathered in one contiguous piece per CTA).
 // Each CTA loads only its columns of Q, gathers only its columns of every selected row, computes
 // the partial scores Q_c K_c^T over its columns and owns the 256 output columns that are the
 // first 256 of its slice (V is a prefix of K), so no byte of the cache is fetched or converted
@@ -170,7 +173,7 @@ struct Ctl {
 static_assert(sizeof(Ctl) <= 12288 - 256, "control block");
 
 // TMEM columns (512 allocated).
-//   bf16 cache: O [0,256) | Q slice [256,416) (packed bf16 pairs, 128 or 160 used) | S 2 x 32 | P 2 x 16
+//   bf16 cache: O [0,256) | Q slice [256,416) (packed bf16 pairs: 128 latent + 16 rope columns used) | S 2 x 32 | P 2 x 16
 //   fp8 cache:  O [0,256) | latent Q slice [256,384) | one score buffer of 3 accumulators x 32 (scale
 //               group a, scale group b, rope) | one P buffer of 2 variants x 16.  Single buffers: the
 //               scores are drained into registers right after they complete, and P is rewritten right
@@ -279,6 +282,12 @@ __device__ __forceinline__ void issue_qk_mmas(uint32_t d0, uint64_t q_rope_desc,
             umma_ss_x4_el(d0 + 64, static_cast<uint32_t>(q_rope_desc), static_cast<uint32_t>(q_rope_desc >> 32), b_lo, k_hi,
                           idesc, 0u, el);
     }
+    if (!kFp8) {
+        // bf16 cache: this CTA's half of the rope columns, the first two K steps of block 4 (A: TMEM columns 128-143 of the slice)
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks)
+            umma_ts_el(d0, q_tmem + 128 + ks * 8, k_desc + static_cast<uint64_t>(((4 * kKvBlockBytes) >> 4) + ks * 2), idesc, 1u, el);
+    }
 }
 
 // O_c (+)= P V_c for one 32-row tile: two K=16 steps; V_c is the first 256 columns of the tile seen
@@ -339,8 +348,12 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int mma_warp = (half || !DSA_ROLE_SWAP) ? kMmaWarp : kMmaWarp + 2;
     const int pv_warp = mma_warp + 1;
     const int gather_warp0 = (half || !DSA_ROLE_SWAP) ? kGatherWarp0 : kMmaWarp;
-    const int nkb = half ? 5 : 4;                 // 64-column blocks of this CTA's slice
+    // Columns of the latent row this CTA works on: latent [256 half, 256 half + 256) (also its output columns) and
+    //   bf16 cache: rope columns [32 half, 32 half + 32) - both CTAs get four and a half 64-column blocks, so
+    //               neither waits for the other's partial scores;
+    //   fp8 cache:  CTA 1 the whole rope (its raw row is one contiguous piece: latent half, scales, rope).
     const int col0 = half ? 256 : 0;              // first latent column of the slice
+    const int rope0 = half ? 32 : 0;              // bf16 cache: first rope column of the slice
     const int w_begin = __ldg(p.list_indptr + list);
     const int w_end = __ldg(p.list_indptr + list + 1);
 
@@ -450,31 +463,41 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
         // this thread's share of an item's Q slice (its head row, a quarter of the slice's columns), read from
         // global memory one item ahead and stored into TMEM when the item starts.
-        constexpr int kQRegs = kFp8 ? 32 : 40;
+        // The slice in TMEM: [latent 128 columns (256 bf16) | bf16 cache: this CTA's half of the rope, 16 columns].
+        // A team stores a quarter of each part: 32 latent columns and (bf16 cache) 4 rope columns.
+        constexpr int kQRegs = kFp8 ? 32 : 36;
         uint32_t qreg[kQRegs];
-        const int q_ncol = (!kFp8 && half) ? 40 : 32;   // TMEM columns (bf16 pairs) per warp; fp8: latent columns only
         auto q_fetch = [&](const dsa_v32_work_info& wq) {
             const RowMap rm = map_row<kExt>(wq, row, p.H);
-            const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.q) + (size_t)rm.q_row * p.stride_q_row +
-                                       (size_t)rm.head * p.stride_q_head + col0 + 2 * cg * q_ncol;
+            const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(p.q) + (size_t)rm.q_row * p.stride_q_row +
+                                        (size_t)rm.head * p.stride_q_head;
+            const __nv_bfloat16* src = base + col0 + 64 * cg;
             const bool live = rm.live;
 #pragma unroll
-            for (int j = 0; j < kQRegs / 4; ++j) {
+            for (int j = 0; j < 8; ++j) {
                 uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (live && 4 * j < q_ncol) v = __ldg(reinterpret_cast<const uint4*>(src) + j);
+                if (live) v = __ldg(reinterpret_cast<const uint4*>(src) + j);
                 qreg[4 * j + 0] = v.x;
                 qreg[4 * j + 1] = v.y;
                 qreg[4 * j + 2] = v.z;
                 qreg[4 * j + 3] = v.w;
             }
+            if (!kFp8) {
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (live) v = __ldg(reinterpret_cast<const uint4*>(base + kDV + rope0 + 8 * cg));
+                qreg[32] = v.x;
+                qreg[33] = v.y;
+                qreg[34] = v.z;
+                qreg[35] = v.w;
+            }
         };
         auto q_prefetch_l2 = [&](const dsa_v32_work_info& wq) {
             const RowMap rm = map_row<kExt>(wq, row, p.H);
             if (rm.live) {
-                const char* src = reinterpret_cast<const char*>(reinterpret_cast<const __nv_bfloat16*>(p.q) + (size_t)rm.q_row * p.stride_q_row +
-                                                               (size_t)rm.head * p.stride_q_head + col0 + 2 * cg * q_ncol);
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(src + 2 * q_ncol * 2 - 16));
+                const char* base = reinterpret_cast<const char*>(reinterpret_cast<const __nv_bfloat16*>(p.q) + (size_t)rm.q_row * p.stride_q_row +
+                                                                (size_t)rm.head * p.stride_q_head);
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(base + (col0 + 64 * cg) * 2));
+                if (!kFp8) asm volatile("prefetch.global.L2 [%0];" ::"l"(base + (kDV + rope0 + 8 * cg) * 2));
             }
         };
 
@@ -489,14 +512,16 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 q_fetch(wq);
                 if (!warp_wait(smem_u32(&ctl->q_empty), (n & 1) ^ 1, abort_flag)) return false;
                 tc_fence_after();
-                const uint32_t qcol = lane_base + kColQ + cg * q_ncol;
+                const uint32_t qcol = lane_base + kColQ + cg * 32;
 #pragma unroll
-                for (int j = 0; j < kQRegs / 8; ++j) {
-                    if (8 * j < q_ncol) {
-                        const uint32_t v[8] = {qreg[8 * j + 0], qreg[8 * j + 1], qreg[8 * j + 2], qreg[8 * j + 3],
-                                               qreg[8 * j + 4], qreg[8 * j + 5], qreg[8 * j + 6], qreg[8 * j + 7]};
-                        tmem_st_n<8>(qcol + 8 * j, v);
-                    }
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t v[8] = {qreg[8 * j + 0], qreg[8 * j + 1], qreg[8 * j + 2], qreg[8 * j + 3],
+                                           qreg[8 * j + 4], qreg[8 * j + 5], qreg[8 * j + 6], qreg[8 * j + 7]};
+                    tmem_st_n<8>(qcol + 8 * j, v);
+                }
+                if (!kFp8) {
+                    const uint32_t v[4] = {qreg[32], qreg[33], qreg[34], qreg[35]};
+                    tmem_st_n<4>(lane_base + kColQ + 128 + cg * 4, v);
                 }
                 tmem_wait_st();
                 tc_fence_before();
@@ -981,8 +1006,8 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 tc_fence_after();
                 const uint64_t k_desc = k_desc0 + static_cast<uint64_t>((s * kKvTileBytes) >> 4);
                 const uint32_t d0 = tmem + s_col_of<kFp8>(it);
-                if (half) issue_qk_mmas<kFp8, 5>(d0, q_desc, tmem + kColQ, k_desc, el);
-                else issue_qk_mmas<kFp8, 4>(d0, q_desc, tmem + kColQ, k_desc, el);
+                if (kFp8 && half) issue_qk_mmas<kFp8, 5>(d0, q_desc, tmem + kColQ, k_desc, el);
+                else issue_qk_mmas<kFp8, 4>(d0, q_desc, tmem + kColQ, k_desc, el);   // bf16 cache: four blocks + half a block
                 tc_commit_el(smem_u32(&ctl->s_full[sb]), el);
                 if (t + 1 == n_tiles) tc_commit_el(smem_u32(&ctl->q_empty), el);
             }
@@ -1032,7 +1057,6 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             const int c4 = lane & 3;                 // its 16-byte chunks: c4, c4 + 4, ...
             uint8_t* mask_bytes = reinterpret_cast<uint8_t*>(ctl->tile_mask);
             const uint8_t* kv_bytes = reinterpret_cast<const uint8_t*>(p.kv);
-            const int n_chunks = nkb * 8;            // 16-byte chunks of a row's slice
             uint32_t it_base = 0;
             for (int w = w_begin; w < w_end; ++w) {
                 const dsa_v32_work_info wi = p.works[w];
@@ -1075,15 +1099,17 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     const uint32_t bar = smem_u32(&ctl->kv_full[s]);
                     if (lane == 0) mask_bytes[(it % kMaskSlots) * 4 + l4] = static_cast<uint8_t>(mask8);
                     // padding / out-of-range rows: nothing is read, the row is filled with zeros
-                    const uint8_t* src = pool + (size_t)(row >= 0 ? row : 0) * (kDQK * 2) + col0 * 2;
+                    const uint8_t* src_row = pool + (size_t)(row >= 0 ? row : 0) * (kDQK * 2);
+                    const uint8_t* src = src_row + col0 * 2;
                     const uint32_t nbytes = row >= 0 ? 16u : 0u;
                     const uint32_t dst_row = smem_u32(sKV + s * kKvTileBytes) + r * 128;
 #pragma unroll
-                    for (int j = 0; j < 10; ++j) {
-                        const int cc = c4 + 4 * j;           // chunk of the slice: block cc / 8, chunk cc % 8 of its row
-                        if (cc < n_chunks)
-                            cp_async_16(dst_row + (cc >> 3) * kKvBlockBytes + (((cc & 7) ^ (r & 7)) << 4), src + cc * 16, nbytes);
+                    for (int j = 0; j < 8; ++j) {
+                        const int cc = c4 + 4 * j;           // latent chunk of the slice: block cc / 8, chunk cc % 8 of its row
+                        cp_async_16(dst_row + (cc >> 3) * kKvBlockBytes + (((cc & 7) ^ (r & 7)) << 4), src + cc * 16, nbytes);
                     }
+                    // this CTA's half of the rope columns: chunks 0-3 of block 4 (the score MMAs take two K steps of it)
+                    cp_async_16(dst_row + 4 * kKvBlockBytes + ((c4 ^ (r & 7)) << 4), src_row + (kDV + rope0) * 2 + c4 * 16, nbytes);
                     cp_async_mbar_arrive_noinc(bar);
                 }
                 it_base += n_tiles;

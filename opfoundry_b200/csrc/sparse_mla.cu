@@ -382,7 +382,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         fence_mbar_init();
     } else if (tid == 96) {
         mbar_init(smem_u32(&ctl->q_full), kSoftmaxWarps + ((kFp8 && half) ? 1 : 0));   // + the rope block's TMA
-        mbar_init(smem_u32(&ctl->q_empty), 1);
+        mbar_init(smem_u32(&ctl->q_empty), kFp8 ? 1 : 2);   // bf16 cache: two score issuers
         mbar_init(smem_u32(&ctl->o_free), kSoftmaxWarps);
         mbar_init(smem_u32(&ctl->l_bar), kSoftmaxWarps);
         mbar_init(smem_u32(&ctl->e_bar), kSoftmaxWarps);
@@ -980,11 +980,18 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             if (!warp_wait_cluster(my_xfree, (n_sent & 1u) ^ 1u, abort_flag)) goto done;
     } else {
     setmaxnreg_dec<kRegsOther<kFp8>>();
-    if (warp == mma_warp) {
-        // ============================================================ score MMA issuer
+    if (warp == mma_warp || (!kFp8 && warp == gather_warp0)) {
+        // ============================================================ score MMA issuer(s)
         // The whole warp runs the loop converged (descriptors stay warp-uniform); one elected lane issues.
-        // Scores and P V products are issued by two different warps, each blocking on its own inputs, so
+        // Scores and P V products are issued by different warps, each blocking on its own inputs, so
         // neither waits behind the other's barrier round trips; the tensor pipe runs them in issue order.
+        // bf16 cache: two score issuers on alternate tiles (warp 18 has no gathers to issue there).  An issuer's
+        // turn per tile - tile barrier, proxy fence, score-buffer barrier, tcgen05 fence, 18 instructions, commit -
+        // takes about as long as the whole pipeline's period, so one issuer alone was the bound.  Even tiles use
+        // score buffer 0 and teams 0, 2, odd tiles buffer 1 and teams 1, 3, so the two never share a buffer or a
+        // team barrier; both wait on every tile's landing barrier, in order, so that neither ever waits on a
+        // phase whose predecessor it has not seen complete.
+        const uint32_t par = (!kFp8 && warp != mma_warp) ? 1u : 0u;
         const uint32_t el = elect_one() ? 1u : 0u;
         const uint64_t q_desc = make_smem_desc_sw128(smem_u32(sQ), 16, 1024);
         const uint64_t k_desc0 = make_smem_desc_sw128(smem_u32(sKV), 16, 1024);            // K-major view
@@ -998,6 +1005,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const int s = it % S;
                 const uint32_t sb = buf_of<kFp8>(it);
                 if (!warp_wait(smem_u32(&ctl->kv_full[s]), (it / S) & 1, abort_flag)) goto done;
+                if (!kFp8 && (it & 1u) != par) continue;   // the other issuer's tile
                 if (!kFp8) fence_proxy_async_smem();   // the tile was written by cp.async (generic proxy)
                 // the softmax warps have drained the tile that used this score buffer last
                 if (it >= kBufReuse<kFp8>)
@@ -1009,8 +1017,9 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (kFp8 && half) issue_qk_mmas<kFp8, 5>(d0, q_desc, tmem + kColQ, k_desc, el);
                 else issue_qk_mmas<kFp8, 4>(d0, q_desc, tmem + kColQ, k_desc, el);   // bf16 cache: four blocks + half a block
                 tc_commit_el(smem_u32(&ctl->s_full[sb]), el);
-                if (t + 1 == n_tiles) tc_commit_el(smem_u32(&ctl->q_empty), el);
             }
+            // the item's Q may be replaced once this issuer's products of the item are complete (bf16 cache: and the other's)
+            tc_commit_el(smem_u32(&ctl->q_empty), el);
         }
     } else if (warp == pv_warp) {
         // ============================================================ P V MMA issuer

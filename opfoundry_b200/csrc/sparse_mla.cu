@@ -43,7 +43,8 @@
 //              accumulator in TMEM; fp8 cache: the 64 rope columns of Q stay in shared memory)
 //   warp 17    P V MMA issuer: O_c += P V_c (A = P in TMEM, B = the same gathered tile described
 //              MN-major).  Two issuers so that neither stream waits behind the other's barriers.
-//   bf16 cache: warps 20-27 loaders, two groups of four on alternate tiles, 8 rows of the tile per warp:
+//   bf16 cache: warp 18 second score issuer (alternate tiles), warp 19 asks the next item's Q into L2 near the end of
+//              an item; warps 20-27 loaders, two groups of four on alternate tiles, 8 rows of the tile per warp:
 //              top-k slots -> block table -> the row's bytes of this CTA's slice as 16-byte cp.async copies
 //              straight into the 128-byte swizzled MMA tile (a TMA tile::gather4 moves one 128-byte block
 //              of four rows per request, 40 requests per tile, and the issue rate of those requests was
@@ -541,7 +542,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             if (item_n == 0) {
                 if (!q_store(wi, 0)) goto done;
             }
-            if (w + 1 < w_end) q_prefetch_l2(p.works[w + 1]);   // on its way to L2 while this item runs
+            if (kFp8 && w + 1 < w_end) q_prefetch_l2(p.works[w + 1]);   // on its way to L2 while this item runs (bf16 cache: the Q prefetcher warp asks later)
             float l_part = 0.0f;        // this thread's share of the row sum, expressed against l_ref
             float l_ref = 0.0f;
             for (uint32_t it = it_base + ((team - it_base) & (G - 1u)); it < it_end; it += G) {
@@ -1067,7 +1068,36 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         // takes a request only every ~25-37 cycles whatever the number of issuing warps (measured): that
         // was the period of the whole bf16 pipeline.  (The fp8 path, 8 requests per tile, keeps gather4.)
         const int lw = warp - kLoaderWarp0;
-        if (lw >= 0 && lw < kLoaderWarps) {
+        if (warp == kGatherWarp0 + 1) {
+            // ======================================================== Q prefetcher (the warp left over for a bf16 cache)
+            // The softmax warps load the next item's Q in their epilogue, and the score MMAs of that item wait
+            // for it.  This warp follows the tiles (it waits on every tile's landing barrier, in order) and asks
+            // for this CTA's slice of the next item's Q eight tiles before the item ends: late enough that the
+            // lines are still in L2 when they are loaded, early enough to be there.
+            uint32_t it = 0;
+            for (int w = w_begin; w < w_end; ++w) {
+                const dsa_v32_work_info wi = p.works[w];
+                const int n_tiles = (wi.k_end - wi.k_begin + kTileRows - 1) / kTileRows;
+                const int t_ask = n_tiles > 8 ? n_tiles - 8 : 0;
+                for (int t = 0; t < n_tiles; ++t, ++it) {
+                    if (t == t_ask && w + 1 < w_end) {
+                        const dsa_v32_work_info wn = p.works[w + 1];
+#pragma unroll 1
+                        for (int r = lane; r < kHeadsPerBlock; r += 32) {
+                            const RowMap rn = map_row<kExt>(wn, r, p.H);
+                            if (rn.live) {
+                                const char* qb = reinterpret_cast<const char*>(reinterpret_cast<const __nv_bfloat16*>(p.q) +
+                                                                               (size_t)rn.q_row * p.stride_q_row + (size_t)rn.head * p.stride_q_head);
+#pragma unroll
+                                for (int c = 0; c < 4; ++c) asm volatile("prefetch.global.L2 [%0];" ::"l"(qb + col0 * 2 + 128 * c));
+                                asm volatile("prefetch.global.L2 [%0];" ::"l"(qb + (kDV + rope0) * 2));
+                            }
+                        }
+                    }
+                    if (!tile_wait<kFp8>(smem_u32(&ctl->kv_full[it % S]), (it / S) & 1, abort_flag)) goto done;
+                }
+            }
+        } else if (lw >= 0 && lw < kLoaderWarps) {
             const int grp = lw >> 2;                 // tiles this warp loads: it % 2 == grp
             const int l4 = lw & 3;
             const int rloc = lane >> 2;              // row of the warp's eight this lane copies

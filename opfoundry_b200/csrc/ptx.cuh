@@ -109,6 +109,13 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
 // writes are visible (a no-op when the kernel was launched without the attribute).
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// 32-byte read-only global load (sm_100: one request per lane where two 16-byte loads would make two).
+__device__ __forceinline__ void ldg_nc_256(const void* p, uint32_t (&r)[8]) {
+    asm volatile("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "l"(p));
+}
+
 // ------------------------------------------------------------------ thread-block cluster
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;

@@ -483,14 +483,14 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                                         (size_t)rm.head * p.stride_q_head;
             const __nv_bfloat16* src = base + col0 + 64 * cg;
             const bool live = rm.live;
+            // thread = row: a warp's load touches 32 different lines, so the number of load instructions is what the
+            // L1 pays for (all sixteen warps do this at once in the epilogue): 32-byte loads, four per thread
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (live) v = __ldg(reinterpret_cast<const uint4*>(src) + j);
-                qreg[4 * j + 0] = v.x;
-                qreg[4 * j + 1] = v.y;
-                qreg[4 * j + 2] = v.z;
-                qreg[4 * j + 3] = v.w;
+            for (int j = 0; j < 4; ++j) {
+                uint32_t v[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+                if (live) ldg_nc_256(reinterpret_cast<const char*>(src) + 32 * j, v);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) qreg[8 * j + k] = v[k];
             }
             if (!kFp8) {
                 uint4 v = make_uint4(0u, 0u, 0u, 0u);

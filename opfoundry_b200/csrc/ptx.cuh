@@ -116,6 +116,12 @@ __device__ __forceinline__ void ldg_nc_256(const void* p, uint32_t (&r)[8]) {
                  : "l"(p));
 }
 
+// 32-byte global store (sm_100).
+__device__ __forceinline__ void stg_256(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t e, uint32_t f, uint32_t g, uint32_t h) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d), "r"(e), "r"(f), "r"(g), "r"(h)
+                 : "memory");
+}
+
 // ------------------------------------------------------------------ thread-block cluster
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;

@@ -950,16 +950,12 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         tmem_ld32(lane_base + kColO + oc, o);
                         tmem_wait_ld();
                         if (live) {
-                            uint4* d4 = reinterpret_cast<uint4*>(o_dst + oc);
+                            // thread = row, so a store touches 32 lines whatever its width: 32-byte stores, two per round
+                            uint32_t u[16];
 #pragma unroll
-                            for (int v = 0; v < 4; ++v) {
-                                uint4 u;
-                                u.x = pack_bf16x2(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
-                                u.y = pack_bf16x2(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
-                                u.z = pack_bf16x2(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
-                                u.w = pack_bf16x2(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
-                                d4[v] = u;
-                            }
+                            for (int v = 0; v < 16; ++v) u[v] = pack_bf16x2(__uint_as_float(o[2 * v]) * inv, __uint_as_float(o[2 * v + 1]) * inv);
+                            stg_256(o_dst + oc, u[0], u[1], u[2], u[3], u[4], u[5], u[6], u[7]);
+                            stg_256(o_dst + oc + 16, u[8], u[9], u[10], u[11], u[12], u[13], u[14], u[15]);
                         }
                     }
                     if (live && (kRowSplit ? own : half == 0) && cg == 0 && p.lse != nullptr) p.lse[(size_t)rm.q_row * p.H + head] = lse_nat;
@@ -970,11 +966,12 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         uint32_t o[32];
                         tmem_ld32(lane_base + kColO + oc, o);
                         tmem_wait_ld();
-                        float4* d4 = reinterpret_cast<float4*>(o_dst + oc);
 #pragma unroll
-                        for (int v = 0; v < 8; ++v)
-                            d4[v] = make_float4(__uint_as_float(o[4 * v + 0]) * inv, __uint_as_float(o[4 * v + 1]) * inv,
-                                                __uint_as_float(o[4 * v + 2]) * inv, __uint_as_float(o[4 * v + 3]) * inv);
+                        for (int v = 0; v < 4; ++v)
+                            stg_256(o_dst + oc + 8 * v, __float_as_uint(__uint_as_float(o[8 * v + 0]) * inv), __float_as_uint(__uint_as_float(o[8 * v + 1]) * inv),
+                                    __float_as_uint(__uint_as_float(o[8 * v + 2]) * inv), __float_as_uint(__uint_as_float(o[8 * v + 3]) * inv),
+                                    __float_as_uint(__uint_as_float(o[8 * v + 4]) * inv), __float_as_uint(__uint_as_float(o[8 * v + 5]) * inv),
+                                    __float_as_uint(__uint_as_float(o[8 * v + 6]) * inv), __float_as_uint(__uint_as_float(o[8 * v + 7]) * inv));
                     }
                     if ((kRowSplit ? own : half == 0) && cg == 0)
                         p.lse_accum[(size_t)wi.partial_slot * kHeadsPerBlock + row] = (l > 0.0f) ? lse_nat : -FLT_MAX;

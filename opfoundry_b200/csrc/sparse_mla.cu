@@ -926,9 +926,8 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll 1
                             for (int d = 0; d < n_dst; ++d) {
                                 __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.n_peers > 0 ? p.out_peers[d] : p.out);
-                                uint4* d4 = reinterpret_cast<uint4*>(base + o_off + oc);
-#pragma unroll
-                                for (int v = 0; v < 4; ++v) d4[v] = u[v];
+                                stg_256(base + o_off + oc, u[0].x, u[0].y, u[0].z, u[0].w, u[1].x, u[1].y, u[1].z, u[1].w);
+                                stg_256(base + o_off + oc + 16, u[2].x, u[2].y, u[2].z, u[2].w, u[3].x, u[3].y, u[3].z, u[3].w);
                             }
                         }
                     }

@@ -866,6 +866,9 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 // row's reference maximum is final.  (A per-item barrier and not the last tile's p_full: a parity
                 // wait is only safe when the barrier's previous phase has already completed, which a warp that
                 // finished early cannot know of another team's barrier.)
+                // the next work item is read before the barrier: its Q is fetched right after the row sums below, and
+                // the addresses of those loads should not wait for this one
+                const dsa_v32_work_info wnext = p.works[w + 1 < w_end ? w + 1 : w];
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&ctl->e_bar));
                 if (!tile_wait<kFp8>(smem_u32(&ctl->e_bar), item_n & 1, abort_flag)) goto done;
@@ -892,7 +895,7 @@ sparse_mla_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     }
                 }
                 if (w + 1 < w_end)
-                    if (!q_store(p.works[w + 1], item_n + 1)) goto done;
+                    if (!q_store(wnext, item_n + 1)) goto done;
                 if (!warp_wait_cluster(smem_u32(&ctl->l_bar), item_n & 1, abort_flag)) goto done;
                 float l = 0.0f;
 #pragma unroll
